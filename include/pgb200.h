@@ -1,0 +1,207 @@
+/*
+ * pgb200 — C ABI of the B200 (sm_100a) kernels that sit behind pequegrad's
+ * `ADPrimitive::dispatch_cuda` seam (reference: csrc/ad_primitives.hpp:37-38,
+ * type switch csrc/dispatch.hpp:38-44).
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; no C++ or torch types cross this boundary;
+ *   - tensors are described the way the reference's `View` describes them
+ *     (csrc/tensor.hpp:263-273): base pointer (storage + byte offset), shape,
+ *     strides in BYTES (0 = broadcast, any permutation, negative not allowed);
+ *   - outputs are allocated by the caller (the reference's dispatch functions
+ *     call `view_ptr()->allocate()` first, csrc/cuda/binary.cu:59) and must be
+ *     contiguous in the logical order of their shape;
+ *   - every call only enqueues work on `stream` and returns; nothing synchronises;
+ *   - the return value is a pgb_status; on failure `pgb_last_error()` holds a
+ *     message in the reference's wording where one exists
+ *     ("<name> not implemented for <dtype>", csrc/dispatch.hpp:22-24);
+ *   - there is no CPU fallback: without a CUDA device every compute entry
+ *     point returns PGB_ERR_CUDA.
+ */
+#ifndef PGB200_H
+#define PGB200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#if defined(__GNUC__)
+#define PGB_API __attribute__((visibility("default")))
+#else
+#define PGB_API
+#endif
+
+#define PGB_MAX_DIMS 8
+#define PGB_MAX_INPUTS 6
+#define PGB_MAX_INSTRS 32
+#define PGB_MAX_OUTPUTS 4
+
+/* dtype codes: 0..3 follow the reference enum order (csrc/dtype.hpp:9-14);
+ * 4 and 5 are additions the int8 and bf16 paths need. */
+typedef enum {
+  PGB_I32 = 0,
+  PGB_F16 = 1,
+  PGB_F32 = 2,
+  PGB_F64 = 3,
+  PGB_I8 = 4,
+  PGB_BF16 = 5
+} pgb_dtype;
+
+typedef enum {
+  PGB_OK = 0,
+  PGB_ERR_INVALID_ARG = -1, /* reference: std::invalid_argument (PG_CHECK_ARG, csrc/utils.hpp:10-25) */
+  PGB_ERR_UNSUPPORTED = -2, /* reference: "... not implemented for <dtype>" runtime_error */
+  PGB_ERR_CUDA = -3,        /* reference: CHECK_CUDA runtime_error (csrc/cuda/cuda_utils.cuh:14-23) */
+  PGB_ERR_TIMEOUT = -4,     /* a bounded device-side wait gave up */
+  PGB_ERR_WORKSPACE = -5    /* caller-provided workspace too small */
+} pgb_status;
+
+typedef struct {
+  void *data;      /* device pointer to element [0,...,0] of the view */
+  int32_t dtype;   /* pgb_dtype */
+  int32_t ndim;    /* 0..PGB_MAX_DIMS; 0 = scalar */
+  int64_t shape[PGB_MAX_DIMS];
+  int64_t stride_bytes[PGB_MAX_DIMS];
+} pgb_tensor;
+
+/* Expression programs: a flat SSA list; instruction i defines value i and may
+ * only read values < i. The op set is the reference fuser's linear IR
+ * (csrc/compiler/ir.hpp:72 unary, :93 binary, :140 ternary) plus the eager
+ * comparison/unary kernels the IR lacks (csrc/cuda/binary.cu:12-47,
+ * csrc/cuda/unary.cu:152-177) and explicit casts.
+ * All values are held in the region's compute type: f64 if any operand is
+ * f64, i32 if all are i32, f32 otherwise (f16/bf16 are widened on load). */
+typedef enum {
+  PGB_OP_LOAD = 0, /* a = index of the input tensor (element at this position) */
+  PGB_OP_IMM = 1,  /* imm; the reference folds Fill constants the same way (csrc/compiler/ir.cpp:235-255) */
+  PGB_OP_ACC = 2,  /* epilogue only: the reduction result for this output element */
+  /* unary: a */
+  PGB_OP_LOG = 8,
+  PGB_OP_EXP = 9,
+  PGB_OP_SIN = 10,
+  PGB_OP_COS = 11,
+  PGB_OP_CAST_F16 = 12, /* round to half and widen again */
+  PGB_OP_CAST_F32 = 13,
+  PGB_OP_CAST_I32 = 14, /* C truncation toward zero, as astype does (csrc/cuda/unary.cuh:104-117) */
+  PGB_OP_CAST_BF16 = 15,
+  /* binary: a, b. Comparisons yield 0/1 in the compute type (csrc/cuda/binary.cu:24-41) */
+  PGB_OP_ADD = 16,
+  PGB_OP_MUL = 17,
+  PGB_OP_MAX = 18, /* x > y ? x : y (csrc/cuda/binary.cu:42-44) */
+  PGB_OP_SUB = 19,
+  PGB_OP_DIV = 20, /* C division; truncating for i32 */
+  PGB_OP_GT = 21,
+  PGB_OP_LT = 22,
+  PGB_OP_MOD = 23,
+  PGB_OP_EQ = 24,
+  PGB_OP_POW = 25,
+  PGB_OP_LTE = 26,
+  PGB_OP_NEQ = 27,
+  PGB_OP_GTE = 28,
+  /* ternary: a ? b : c (csrc/cuda/ternary.cu:10-12) */
+  PGB_OP_WHERE = 32
+} pgb_opcode;
+
+typedef struct {
+  uint8_t op; /* pgb_opcode */
+  uint8_t reserved;
+  int16_t a, b, c; /* value indices (or the input index for LOAD) */
+  double imm;
+} pgb_instr;
+
+typedef enum {
+  PGB_REDUCE_SUM = 0,   /* Sum::dispatch_cuda, csrc/cuda/reduce.cu:11-47 */
+  PGB_REDUCE_MAX = 1,   /* MaxReduce::dispatch_cuda, csrc/cuda/reduce.cu:87-125 */
+  PGB_REDUCE_MEAN = 2,  /* Mean::dispatch_cuda, csrc/cuda/reduce.cu:49-85: sum, then one divide by the count */
+  PGB_REDUCE_ARGMAX = 3 /* first index of the maximum along ONE axis, int32 out; the reference only has
+                           the Python composite pequegrad/ops.py:968-978 (float index, ties summed) */
+} pgb_reduce_op;
+
+PGB_API const char *pgb_status_string(int status);
+/* Message of the last failing call made by this thread ("" if none). */
+PGB_API const char *pgb_last_error(void);
+PGB_API const char *pgb_version(void);
+/* Number of kernels this library has launched in this process (all threads). */
+PGB_API uint64_t pgb_launch_count(void);
+
+/*
+ * Fused elementwise kernel. Replaces the JIT `elementwise_kernel`
+ * (csrc/compiler/ir.cpp:1395-1403, launched by Compiled::dispatch_cuda,
+ * csrc/compiler/ir.cpp:1560-1606) and, with one-instruction programs, the
+ * eager binary / unary / where / astype kernels (csrc/cuda/binary.cu:51-79,
+ * csrc/cuda/unary.cu:11-149, csrc/cuda/ternary.cu:16-45,
+ * csrc/cuda/view_helpers.cu:282-302).
+ *   in[0..n_in)     same shape as the outputs, arbitrary byte strides
+ *   out[0..n_out)   contiguous, same shape; out_vals[j] = program value stored to out[j]
+ */
+PGB_API int pgb_fused_elementwise(const pgb_tensor *in, int n_in, const pgb_tensor *out,
+                          int n_out, const pgb_instr *prog, int n_instr,
+                          const int16_t *out_vals, void *stream);
+
+/*
+ * Fused prologue -> reduce -> epilogue kernel. Replaces the JIT
+ * `reduce_kernel` (csrc/compiler/ir.cpp:839-1151, sample README.md:93-119)
+ * and, with a one-LOAD prologue and empty epilogue, the eager
+ * Sum / MaxReduce / Mean kernels (csrc/cuda/reduce.cu:11-125).
+ *   in[0..n_in)          all of the pre-reduce shape (stride-0 dims allowed)
+ *   prologue             last value is what gets accumulated
+ *   axes                 reduced axes, negative allowed (csrc/cuda/reduce.cu:22-25)
+ *   out                  contiguous, keepdims shape (reduced dims = 1) or the
+ *                        squeezed shape; dtype i32 for ARGMAX
+ *   epi_in[0..n_epi_in)  tensors broadcastable to out's keepdims shape (same ndim as in[0]), LOAD k in the
+ *                        epilogue reads epi_in[k]
+ *   epilogue             may be empty (n_epi = 0): the result is stored as is
+ *   workspace            scratch for split reductions; if NULL the library
+ *                        allocates and frees it stream-ordered
+ *                        (cudaMallocAsync, as the reference allocates outputs,
+ *                        csrc/cuda/mem.cu:184-192). Query the size with
+ *                        pgb_fused_reduce_workspace().
+ */
+PGB_API int pgb_fused_reduce(const pgb_tensor *in, int n_in, const pgb_tensor *out,
+                     int reduce_op, const int32_t *axes, int n_axes,
+                     const pgb_instr *prologue, int n_pro,
+                     const pgb_tensor *epi_in, int n_epi_in,
+                     const pgb_instr *epilogue, int n_epi, void *workspace,
+                     size_t workspace_bytes, void *stream);
+
+/* Bytes of workspace the call above would use for these arguments (0 = none). */
+PGB_API int pgb_fused_reduce_workspace(const pgb_tensor *in, int n_in,
+                               const pgb_tensor *out, int reduce_op,
+                               const int32_t *axes, int n_axes,
+                               size_t *bytes_out);
+
+/* Which kernel family and launch geometry the planner picks; written as a short
+ * human-readable line ("row g=32 vec=4 split=1 grid=..."). For tests and bench. */
+PGB_API int pgb_fused_reduce_describe(const pgb_tensor *in, int n_in,
+                              const pgb_tensor *out, int reduce_op,
+                              const int32_t *axes, int n_axes,
+                              const pgb_instr *prologue, int n_pro,
+                              char *buf, size_t buf_len);
+
+/*
+ * Row softmax over the last axis, one kernel. Replaces the composite
+ * pequegrad/ops.py:259-267 (max_reduce, sub, exp, sum, div) and the mask
+ * `where(mask, s, -1e9)` of pequegrad/ops.py:807-814 when causal != 0
+ * (column j > row i of the last two dims is excluded; excluded outputs are 0).
+ * x, y: same shape, last dim contiguous, dtype f16 / bf16 / f32; math in f32.
+ */
+PGB_API int pgb_softmax_rows(const pgb_tensor *x, const pgb_tensor *y, int causal,
+                     void *stream);
+
+/*
+ * LayerNorm over the last axis, one kernel. Replaces the composite
+ * pequegrad/ops.py:515-551 (mean; biased variance via pequegrad/ops.py:480-501
+ * with correction 0; (x-mean)/sqrt(var+eps); *gamma; +beta).
+ * gamma / beta may be NULL. f32 or f16 io, math in f32.
+ */
+PGB_API int pgb_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma,
+                       const pgb_tensor *beta, float eps, const pgb_tensor *y,
+                       void *stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* PGB200_H */

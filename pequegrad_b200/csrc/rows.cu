@@ -1,0 +1,308 @@
+// Single-kernel row softmax and LayerNorm.
+//
+// The reference computes both as chains of separate kernels with full-size
+// intermediates: softmax = max_reduce, sub, exp, (again sub, exp), sum, div
+// (pequegrad/ops.py:259-267); layer_norm = mean, var (mean, sub, pow, sum,
+// div), add eps, pow 0.5, sub, div, mul, add (pequegrad/ops.py:515-551,
+// 480-501). Here a warp keeps its row in registers: one read and one write of
+// the tensor. The arithmetic follows the composites step by step (true
+// division, biased variance, eps added before the square root).
+#include "reduce_common.cuh"
+#include "vec.cuh"
+
+namespace pgb {
+
+struct RowsParams {
+  const void *x;
+  void *y;
+  const void *gamma, *beta;
+  int64_t rows, C;
+  int64_t causal_rows;  // > 0: causal mask with this many rows per matrix
+  float eps;
+};
+
+__device__ __forceinline__ float warp_max(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v = fmaxf(v, __shfl_xor_sync(0xffffffffu, v, m));
+  return v;
+}
+__device__ __forceinline__ float warp_sum(float v) {
+#pragma unroll
+  for (int m = 16; m > 0; m >>= 1) v += __shfl_xor_sync(0xffffffffu, v, m);
+  return v;
+}
+
+// One warp per row, the row held in NV vectors of V elements per lane.
+template <typename IoT, int V, int NV>
+__global__ void __launch_bounds__(256) softmax_warp_kernel(const __grid_constant__ RowsParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const IoT *xr = (const IoT *)p.x + row * p.C;
+  IoT *yr = (IoT *)p.y + row * p.C;
+  // number of columns that take part (the rest are masked out)
+  int64_t L = p.C;
+  if (p.causal_rows > 0) L = min(p.C, (row % p.causal_rows) + 1);
+  float v[NV][V];
+  float m = -INFINITY;
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int64_t c = ((int64_t)u * 32 + lane) * V;
+    if (c < L) {
+      load_vec<float, IoT, V>(xr + c, v[u]);
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        if (c + e >= L) v[u][e] = -INFINITY;
+        m = fmaxf(m, v[u][e]);
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) v[u][e] = -INFINITY;
+    }
+  }
+  m = warp_max(m);
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < NV; ++u)
+#pragma unroll
+    for (int e = 0; e < V; ++e) {
+      const float ex = (v[u][e] == -INFINITY) ? 0.f : expf(v[u][e] - m);
+      v[u][e] = ex;
+      s += ex;
+    }
+  s = warp_sum(s);
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int64_t c = ((int64_t)u * 32 + lane) * V;
+    if (c < p.C) {
+      float o[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = v[u][e] / s;
+      store_vec<IoT, float, V>(yr + c, o);
+    }
+  }
+}
+
+// Any row length / alignment: one CTA per row, three passes over the row
+// (the repeats are served by L1/L2).
+template <typename IoT>
+__global__ void __launch_bounds__(256) softmax_cta_kernel(const __grid_constant__ RowsParams p) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int64_t row = blockIdx.x;
+  const IoT *xr = (const IoT *)p.x + row * p.C;
+  IoT *yr = (IoT *)p.y + row * p.C;
+  int64_t L = p.C;
+  if (p.causal_rows > 0) L = min(p.C, (row % p.causal_rows) + 1);
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  float m = -INFINITY;
+  for (int64_t c = threadIdx.x; c < L; c += 256) m = fmaxf(m, to_compute<float, IoT>(xr[c]));
+  m = warp_max(m);
+  if (lane == 0) red[warp] = m;
+  __syncthreads();
+  if (threadIdx.x == 0) { float t = red[0]; for (int i = 1; i < 8; ++i) t = fmaxf(t, red[i]); bc = t; }
+  __syncthreads();
+  m = bc;
+  float s = 0.f;
+  for (int64_t c = threadIdx.x; c < L; c += 256) {
+    const float xv = to_compute<float, IoT>(xr[c]);
+    s += (xv == -INFINITY) ? 0.f : expf(xv - m);
+  }
+  s = warp_sum(s);
+  __syncthreads();
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) { float t = 0.f; for (int i = 0; i < 8; ++i) t += red[i]; bc = t; }
+  __syncthreads();
+  s = bc;
+  for (int64_t c = threadIdx.x; c < p.C; c += 256) {
+    float o = 0.f;
+    if (c < L) {
+      const float xv = to_compute<float, IoT>(xr[c]);
+      o = ((xv == -INFINITY) ? 0.f : expf(xv - m)) / s;
+    }
+    yr[c] = from_compute<IoT, float>(o);
+  }
+}
+
+template <typename IoT, int V, int NV>
+__global__ void __launch_bounds__(256) layernorm_warp_kernel(const __grid_constant__ RowsParams p) {
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const IoT *xr = (const IoT *)p.x + row * p.C;
+  IoT *yr = (IoT *)p.y + row * p.C;
+  float v[NV][V];
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int64_t c = ((int64_t)u * 32 + lane) * V;
+    if (c < p.C) {
+      load_vec<float, IoT, V>(xr + c, v[u]);
+#pragma unroll
+      for (int e = 0; e < V; ++e) s += v[u][e];
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) v[u][e] = 0.f;
+    }
+  }
+  const float n = (float)p.C;
+  const float mean = warp_sum(s) / n;
+  float q = 0.f;
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int64_t c = ((int64_t)u * 32 + lane) * V;
+    if (c < p.C) {
+#pragma unroll
+      for (int e = 0; e < V; ++e) {
+        v[u][e] = v[u][e] - mean;
+        q += v[u][e] * v[u][e];
+      }
+    }
+  }
+  const float var = warp_sum(q) / n;
+  const float sd = sqrtf(var + p.eps);
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int64_t c = ((int64_t)u * 32 + lane) * V;
+    if (c < p.C) {
+      float o[V];
+#pragma unroll
+      for (int e = 0; e < V; ++e) o[e] = v[u][e] / sd;
+      if (p.gamma) {
+        float g[V];
+        load_vec_cached<float, IoT, V>((const IoT *)p.gamma + c, g);
+#pragma unroll
+        for (int e = 0; e < V; ++e) o[e] = o[e] * g[e];
+      }
+      if (p.beta) {
+        float b[V];
+        load_vec_cached<float, IoT, V>((const IoT *)p.beta + c, b);
+#pragma unroll
+        for (int e = 0; e < V; ++e) o[e] = o[e] + b[e];
+      }
+      store_vec<IoT, float, V>(yr + c, o);
+    }
+  }
+}
+
+template <typename IoT>
+__global__ void __launch_bounds__(256) layernorm_cta_kernel(const __grid_constant__ RowsParams p) {
+  __shared__ float red[8];
+  __shared__ float bc;
+  const int64_t row = blockIdx.x;
+  const IoT *xr = (const IoT *)p.x + row * p.C;
+  IoT *yr = (IoT *)p.y + row * p.C;
+  const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5;
+  const float n = (float)p.C;
+  float s = 0.f;
+  for (int64_t c = threadIdx.x; c < p.C; c += 256) s += to_compute<float, IoT>(xr[c]);
+  s = warp_sum(s);
+  if (lane == 0) red[warp] = s;
+  __syncthreads();
+  if (threadIdx.x == 0) { float t = 0.f; for (int i = 0; i < 8; ++i) t += red[i]; bc = t / n; }
+  __syncthreads();
+  const float mean = bc;
+  float q = 0.f;
+  for (int64_t c = threadIdx.x; c < p.C; c += 256) { const float d = to_compute<float, IoT>(xr[c]) - mean; q += d * d; }
+  q = warp_sum(q);
+  __syncthreads();
+  if (lane == 0) red[warp] = q;
+  __syncthreads();
+  if (threadIdx.x == 0) { float t = 0.f; for (int i = 0; i < 8; ++i) t += red[i]; bc = sqrtf(t / n + p.eps); }
+  __syncthreads();
+  const float sd = bc;
+  for (int64_t c = threadIdx.x; c < p.C; c += 256) {
+    float o = (to_compute<float, IoT>(xr[c]) - mean) / sd;
+    if (p.gamma) o = o * to_compute<float, IoT>(((const IoT *)p.gamma)[c]);
+    if (p.beta) o = o + to_compute<float, IoT>(((const IoT *)p.beta)[c]);
+    yr[c] = from_compute<IoT, float>(o);
+  }
+}
+
+// ---------------------------------------------------------------------------
+static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
+
+template <typename IoT, bool SOFTMAX>
+static int rows_launch(const RowsParams &p, cudaStream_t stream) {
+  constexpr int V = 16 / (int)sizeof(IoT);
+  const bool vec = (p.C % V) == 0 && aligned16(p.x) && aligned16(p.y) && (!p.gamma || aligned16(p.gamma)) && (!p.beta || aligned16(p.beta));
+  const int64_t per_lane_vecs = (p.C + 32 * V - 1) / (32 * V);
+  const unsigned wgrid = (unsigned)((p.rows + 7) / 8);
+  if (p.rows > 2147483647LL * 8) return PGB_ERR_UNSUPPORTED;
+  const char *name = SOFTMAX ? "softmax_warp_kernel" : "layernorm_warp_kernel";
+#define PGB_ROWS_CASE(NV)                                                                   \
+  if (SOFTMAX) softmax_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p);               \
+  else layernorm_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p)
+  if (vec && per_lane_vecs <= 16) {
+    if (per_lane_vecs <= 1) { PGB_ROWS_CASE(1); }
+    else if (per_lane_vecs <= 2) { PGB_ROWS_CASE(2); }
+    else if (per_lane_vecs <= 4) { PGB_ROWS_CASE(4); }
+    else if (per_lane_vecs <= 6) { PGB_ROWS_CASE(6); }
+    else if (per_lane_vecs <= 8) { PGB_ROWS_CASE(8); }
+    else { PGB_ROWS_CASE(16); }
+  } else {
+    name = SOFTMAX ? "softmax_cta_kernel" : "layernorm_cta_kernel";
+    if (SOFTMAX) softmax_cta_kernel<IoT><<<(unsigned)p.rows, 256, 0, stream>>>(p);
+    else layernorm_cta_kernel<IoT><<<(unsigned)p.rows, 256, 0, stream>>>(p);
+  }
+#undef PGB_ROWS_CASE
+  count_launch();
+  return check_launch(name);
+}
+
+static int rows_common(const pgb_tensor *x, const pgb_tensor *y, const char *what, RowsParams &p) {
+  if (!x || !y) { set_error(std::string(what) + ": null tensor"); return PGB_ERR_INVALID_ARG; }
+  if (x->ndim < 1 || x->ndim > PGB_MAX_DIMS || y->ndim != x->ndim) { set_error(std::string(what) + ": bad rank"); return PGB_ERR_INVALID_ARG; }
+  for (int d = 0; d < x->ndim; ++d)
+    if (x->shape[d] != y->shape[d]) { set_error(std::string(what) + ": input and output shapes differ"); return PGB_ERR_INVALID_ARG; }
+  if (x->dtype != y->dtype) { set_error(std::string(what) + ": input and output dtypes differ"); return PGB_ERR_INVALID_ARG; }
+  if (x->dtype != PGB_F32 && x->dtype != PGB_F16 && x->dtype != PGB_BF16) {
+    set_error(std::string(what) + " not implemented for " + dtype_name(x->dtype));
+    return PGB_ERR_UNSUPPORTED;
+  }
+  if (!is_contiguous(*x) || !is_contiguous(*y)) { set_error(std::string(what) + ": tensors must be contiguous"); return PGB_ERR_UNSUPPORTED; }
+  p = RowsParams{};
+  p.x = x->data;
+  p.y = y->data;
+  p.C = x->shape[x->ndim - 1];
+  p.rows = p.C ? numel_of(*x) / p.C : 0;
+  return PGB_OK;
+}
+
+int run_softmax_rows(const pgb_tensor *x, const pgb_tensor *y, int causal, cudaStream_t stream) {
+  RowsParams p;
+  int st = rows_common(x, y, "softmax", p);
+  if (st != PGB_OK) return st;
+  if (causal) {
+    if (x->ndim < 2) { set_error("softmax: a causal mask needs at least 2 dims"); return PGB_ERR_INVALID_ARG; }
+    p.causal_rows = x->shape[x->ndim - 2];
+  }
+  if (p.rows == 0 || p.C == 0) return PGB_OK;
+  if (x->dtype == PGB_F32) return rows_launch<float, true>(p, stream);
+  if (x->dtype == PGB_F16) return rows_launch<__half, true>(p, stream);
+  return rows_launch<__nv_bfloat16, true>(p, stream);
+}
+
+int run_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma, const pgb_tensor *beta, float eps, const pgb_tensor *y,
+                       cudaStream_t stream) {
+  RowsParams p;
+  int st = rows_common(x, y, "layer_norm", p);
+  if (st != PGB_OK) return st;
+  for (const pgb_tensor *t : {gamma, beta}) {
+    if (!t) continue;
+    if (t->dtype != x->dtype || numel_of(*t) != p.C || !is_contiguous(*t)) {
+      set_error("layer_norm: weight and bias must be contiguous, of the input dtype and of the normalised length");
+      return PGB_ERR_INVALID_ARG;
+    }
+  }
+  p.gamma = gamma ? gamma->data : nullptr;
+  p.beta = beta ? beta->data : nullptr;
+  p.eps = eps;
+  if (p.rows == 0 || p.C == 0) return PGB_OK;
+  if (x->dtype == PGB_F32) return rows_launch<float, false>(p, stream);
+  if (x->dtype == PGB_F16) return rows_launch<__half, false>(p, stream);
+  return rows_launch<__nv_bfloat16, false>(p, stream);
+}
+
+}  // namespace pgb

@@ -1,0 +1,141 @@
+"""Calls into the C ABI with torch CUDA tensors as device memory.
+
+torch is plumbing here: it owns allocations and the current stream. Every
+function below builds `pgb_tensor` descriptors (pointer, shape, BYTE strides —
+the reference's `View`, csrc/tensor.hpp:263-273) and enqueues exactly the
+kernels of `libpgb200.so`; nothing is computed by torch.
+"""
+from __future__ import annotations
+
+import ctypes as C
+from typing import Sequence
+
+import torch
+
+from . import _lib as L
+
+_TORCH2PGB = {
+    torch.int32: L.I32, torch.float16: L.F16, torch.float32: L.F32,
+    torch.float64: L.F64, torch.int8: L.I8, torch.bfloat16: L.BF16,
+}
+
+
+def pgb_dtype(dt: torch.dtype) -> int:
+    try:
+        return _TORCH2PGB[dt]
+    except KeyError:
+        raise RuntimeError(f"dtype {dt} is not supported by pgb200") from None
+
+
+def desc(t: torch.Tensor) -> L.PgbTensor:
+    """Descriptor of a (possibly permuted / expanded / sliced) CUDA tensor view."""
+    if not t.is_cuda:
+        raise RuntimeError("pgb200 kernels need CUDA tensors: there is no CPU path")
+    es = t.element_size()
+    return L.make_tensor(t.data_ptr(), pgb_dtype(t.dtype), t.shape, [s * es for s in t.stride()])
+
+
+def _arr(descs: Sequence[L.PgbTensor]):
+    a = (L.PgbTensor * max(len(descs), 1))()
+    for i, d in enumerate(descs):
+        a[i] = d
+    return a
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def reduced_shape(shape, axes, keepdims):
+    nd = len(shape)
+    ax = sorted({a + nd if a < 0 else a for a in axes})
+    if keepdims:
+        return tuple(1 if i in ax else s for i, s in enumerate(shape))
+    return tuple(s for i, s in enumerate(shape) if i not in ax)
+
+
+def fused_reduce(inputs: Sequence[torch.Tensor], op: int, axes: Sequence[int], keepdims: bool = False,
+                 prologue=(), epilogue=(), epi_inputs: Sequence[torch.Tensor] = (), out_dtype=None,
+                 out: torch.Tensor | None = None, workspace: torch.Tensor | None = None) -> torch.Tensor:
+    """prologue / epilogue: lists of (opname, a, b, c, imm); see include/pgb200.h."""
+    x0 = inputs[0]
+    axes = list(axes)
+    if out is None:
+        if out_dtype is None:
+            out_dtype = torch.int32 if op == L.ARGMAX else x0.dtype
+        out = torch.empty(reduced_shape(x0.shape, axes, keepdims), dtype=out_dtype, device=x0.device)
+    ins = _arr([desc(t) for t in inputs])
+    eins = _arr([desc(t) for t in epi_inputs])
+    pro, npro = L.make_program(list(prologue))
+    epi, nepi = L.make_program(list(epilogue))
+    ax = (C.c_int32 * max(len(axes), 1))(*axes)
+    od = desc(out)
+    ws_ptr, ws_bytes = (None, 0) if workspace is None else (workspace.data_ptr(), workspace.numel() * workspace.element_size())
+    with torch.cuda.device(x0.device):
+        st = L.lib().pgb_fused_reduce(ins, len(inputs), C.byref(od), op, ax, len(axes), pro, npro, eins, len(epi_inputs), epi, nepi,
+                                      ws_ptr, ws_bytes, _stream())
+    L.check(st)
+    return out
+
+
+def reduce_workspace_bytes(x_desc_or_tensor, out_shape, op: int, axes: Sequence[int], out_dtype=torch.float32) -> int:
+    d = x_desc_or_tensor if isinstance(x_desc_or_tensor, L.PgbTensor) else desc(x_desc_or_tensor)
+    es = torch.empty((), dtype=out_dtype).element_size()
+    strides, acc = [], es
+    for s in reversed(out_shape):
+        strides.append(acc)
+        acc *= s
+    od = L.make_tensor(256, pgb_dtype(out_dtype), out_shape, list(reversed(strides)))
+    ax = (C.c_int32 * max(len(axes), 1))(*axes)
+    n = C.c_size_t(0)
+    L.check(L.lib().pgb_fused_reduce_workspace(_arr([d]), 1, C.byref(od), op, ax, len(axes), C.byref(n)))
+    return int(n.value)
+
+
+def describe_reduce(in_descs: Sequence[L.PgbTensor], out_desc: L.PgbTensor, op: int, axes: Sequence[int], prologue=()) -> str:
+    """The planner's choice for these arguments; needs no GPU."""
+    pro, npro = L.make_program(list(prologue))
+    ax = (C.c_int32 * max(len(axes), 1))(*axes)
+    buf = C.create_string_buffer(512)
+    L.check(L.lib().pgb_fused_reduce_describe(_arr(list(in_descs)), len(in_descs), C.byref(out_desc), op, ax, len(axes), pro, npro, buf, 512))
+    return buf.value.decode()
+
+
+def fused_elementwise(inputs: Sequence[torch.Tensor], prog, shape=None, out_dtypes=None, out_vals=None) -> list:
+    """Evaluate `prog` per element; inputs must already be views of `shape`."""
+    if shape is None:
+        shape = tuple(inputs[0].shape)
+    n = len(prog)
+    if out_vals is None:
+        out_vals = [n - 1]
+    if out_dtypes is None:
+        out_dtypes = [inputs[0].dtype] * len(out_vals)
+    dev = inputs[0].device if inputs else torch.device("cuda")
+    outs = [torch.empty(shape, dtype=dt, device=dev) for dt in out_dtypes]
+    p, n = L.make_program(list(prog))
+    ov = (C.c_int16 * len(out_vals))(*out_vals)
+    with torch.cuda.device(dev):
+        st = L.lib().pgb_fused_elementwise(_arr([desc(t) for t in inputs]), len(inputs), _arr([desc(o) for o in outs]), len(outs), p, n, ov,
+                                           _stream())
+    L.check(st)
+    return outs
+
+
+def softmax_rows(x: torch.Tensor, causal: bool = False) -> torch.Tensor:
+    y = torch.empty_like(x, memory_format=torch.contiguous_format)
+    xd, yd = desc(x), desc(y)
+    with torch.cuda.device(x.device):
+        st = L.lib().pgb_softmax_rows(C.byref(xd), C.byref(yd), 1 if causal else 0, _stream())
+    L.check(st)
+    return y
+
+
+def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor | None, beta: torch.Tensor | None, eps: float = 1e-5) -> torch.Tensor:
+    y = torch.empty_like(x, memory_format=torch.contiguous_format)
+    xd, yd = desc(x), desc(y)
+    gd = desc(gamma) if gamma is not None else None
+    bd = desc(beta) if beta is not None else None
+    with torch.cuda.device(x.device):
+        st = L.lib().pgb_layernorm_rows(C.byref(xd), C.byref(gd) if gd else None, C.byref(bd) if bd else None, eps, C.byref(yd), _stream())
+    L.check(st)
+    return y
