@@ -139,3 +139,47 @@ def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor | None, beta: torch.Tens
         st = L.lib().pgb_layernorm_rows(C.byref(xd), C.byref(gd) if gd else None, C.byref(bd) if bd else None, eps, C.byref(yd), _stream())
     L.check(st)
     return y
+
+
+class PreparedReduce:
+    """A fused reduce with its descriptors and programs built once, so that a
+    call is one C-ABI invocation (what the reference's `Compiled` primitive
+    does by baking shapes into the kernel, csrc/compiler/ir.cpp:975-985)."""
+
+    def __init__(self, inputs: Sequence[torch.Tensor], op: int, axes: Sequence[int], keepdims: bool = False, prologue=(),
+                 epilogue=(), out: torch.Tensor | None = None, out_dtype=None, workspace: torch.Tensor | None = None):
+        x0 = inputs[0]
+        self.inputs = list(inputs)
+        self.device = x0.device
+        axes = list(axes)
+        if out is None:
+            if out_dtype is None:
+                out_dtype = torch.int32 if op == L.ARGMAX else x0.dtype
+            out = torch.empty(reduced_shape(x0.shape, axes, keepdims), dtype=out_dtype, device=x0.device)
+        self.out = out
+        self._ins = _arr([desc(t) for t in inputs])
+        self._n_in = len(inputs)
+        self._od = desc(out)
+        self._op = op
+        self._ax = (C.c_int32 * max(len(axes), 1))(*axes)
+        self._n_ax = len(axes)
+        self._pro, self._npro = L.make_program(list(prologue))
+        self._epi, self._nepi = L.make_program(list(epilogue))
+        self._none = _arr([])
+        n = C.c_size_t(0)
+        L.check(L.lib().pgb_fused_reduce_workspace(self._ins, self._n_in, C.byref(self._od), op, self._ax, self._n_ax, C.byref(n)))
+        self.workspace_bytes = int(n.value)
+        if workspace is None and self.workspace_bytes:
+            workspace = torch.empty(self.workspace_bytes, dtype=torch.uint8, device=x0.device)
+        self.workspace = workspace
+        self._fn = L.lib().pgb_fused_reduce
+        self.plan = describe_reduce([desc(t) for t in inputs], self._od, op, axes, prologue)
+
+    def __call__(self, stream: int | None = None) -> torch.Tensor:
+        ws = self.workspace
+        st = self._fn(self._ins, self._n_in, C.byref(self._od), self._op, self._ax, self._n_ax, self._pro, self._npro, self._none, 0,
+                      self._epi, self._nepi, ws.data_ptr() if ws is not None else None, ws.numel() if ws is not None else 0,
+                      _stream() if stream is None else stream)
+        if st != L.OK:
+            L.check(st)
+        return self.out
