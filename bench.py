@@ -166,6 +166,7 @@ def main():
     ap.add_argument("--impl", default="pgb200", choices=["pgb200", "reference"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--only", default="", help="comma-separated tensor names (A,B,Bp) to restrict the sweep, for profiling")
+    ap.add_argument("--bare", action="store_true", help="diagnostic: no prologue / epilogue (not the benchmark workload)")
     args = ap.parse_args()
     rank = int(os.environ.get("RANK", "0"))
     local_rank = int(os.environ.get("LOCAL_RANK", "0"))
@@ -189,14 +190,21 @@ def main():
 
     # per-rank synthetic tensors (rank-seeded; rank 0 uses the configured seed 2)
     g = torch.Generator(device=dev).manual_seed(2 + rank)
-    T = {"A": torch.randn(SHAPES["A"], generator=g, device=dev), "B": torch.randn(SHAPES["B"], generator=g, device=dev)}
-    T["Bp"] = T["B"].permute(0, 2, 1)
     only = set(filter(None, args.only.split(",")))
+    T = {}
+    if not only or "A" in only:
+        T["A"] = torch.randn(SHAPES["A"], generator=g, device=dev)
+    if not only or only & {"B", "Bp"}:
+        T["B"] = torch.randn(SHAPES["B"], generator=g, device=dev)
+        T["Bp"] = T["B"].permute(0, 2, 1)
     cases = [c for c in case_list() if not only or c[0] in only]
     opcode = {"sum": L.SUM, "max": L.MAX, "mean": L.MEAN, "argmax": L.ARGMAX}
     prepared = []
     for name, op, ax, nbytes in cases:
-        pr = K.PreparedReduce([T[name]], opcode[op], [ax], False, AFFINE, () if op == "argmax" else EXP_EPI)
+        if args.bare:
+            pr = K.PreparedReduce([T[name]], opcode[op], [ax], False)
+        else:
+            pr = K.PreparedReduce([T[name]], opcode[op], [ax], False, AFFINE, () if op == "argmax" else EXP_EPI)
         prepared.append((name, op, ax, nbytes, pr))
     bytes_per_step = sum(c[3] for c in cases)
     stream = torch.cuda.current_stream().cuda_stream
@@ -246,11 +254,11 @@ def main():
     clocks = sampler.stop()
 
     # end to end through the public call: pinned host inputs -> device, sweep, results -> host
-    host_in = {k: torch.empty(SHAPES[k], dtype=torch.float32).pin_memory() for k in ("A", "B")}
+    host_in = {k: torch.empty(SHAPES[k], dtype=torch.float32).pin_memory() for k in ("A", "B") if k in T}
     for k in host_in:
         host_in[k].copy_(T[k])
     host_out = [torch.empty(pr.out.shape, dtype=pr.out.dtype).pin_memory() for *_, pr in prepared]
-    h2d = sum(v.numel() * 4 for k, v in host_in.items() if not only or k in only or (k == "B" and "Bp" in only))
+    h2d = sum(v.numel() * 4 for v in host_in.values())
     d2h = sum(o.numel() * o.element_size() for o in host_out)
 
     def e2e_step():
@@ -303,7 +311,8 @@ def main():
             "metric": "fused-reduce HBM GB/s", "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps,
             "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
             "vs_baseline": None, "dtype": "f32", "data": "synthetic",
-            "config": {"workload": WORKLOAD, "cases": len(cases), "bytes_per_step": bytes_per_step,
+            "config": {"workload": WORKLOAD + (" [diagnostic run: prologue and epilogue left out]" if args.bare else ""),
+                       "cases": len(cases), "bytes_per_step": bytes_per_step,
                        "l2": "inputs (268 MB and 1074 MB) are larger than the 126 MB L2; consecutive launches alternate tensors"},
             "clocks": clocks,
             "e2e": {"value": round(e2e_value, 2), "unit": "GB/s", "h2d_bytes_per_step": h2d, "d2h_bytes_per_step": d2h,

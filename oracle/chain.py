@@ -70,3 +70,25 @@ def fused_reduce_oracle(inputs, op, axes, keepdims, prologue=(), epilogue=(), im
     if epilogue:
         r = eval_program(epilogue, [], acc=r, impl=impl)[-1]
     return np.asarray(r)
+
+
+def fused_reduce_truth(inputs, op, axes, keepdims, prologue=(), impl="port"):
+    """fp64-accumulating twin of a sum / mean: the prologue is evaluated by the same
+    fp32 eager kernels, the accumulation is exact to fp64. A long fp32 serial sum
+    (what the reference CPU path does) drifts by more than 1e-5 relative, so this
+    is the ground truth the 1e-5 bound is checked against; the reference's own
+    distance from it is reported by `reference_sum_error`."""
+    x = eval_program(prologue, inputs, impl=impl)[-1] if prologue else inputs[0]
+    x64 = np.asarray(x, dtype=np.float64)
+    ax = tuple(a % x64.ndim for a in axes)
+    r = x64.sum(axis=ax, keepdims=keepdims)
+    if op == "mean":
+        r = r / np.prod([x64.shape[a] for a in ax])
+    return r
+
+
+def reference_sum_error(inputs, op, axes, prologue=(), impl="port"):
+    """max relative distance of the reference's fp32 serial sum from the fp64 truth."""
+    ref = fused_reduce_oracle(inputs, op, axes, False, prologue, impl=impl).astype(np.float64)
+    tru = fused_reduce_truth(inputs, op, axes, False, prologue, impl=impl)
+    return float(np.max(np.abs(ref - tru) / np.maximum(np.abs(tru), 1e-30)))

@@ -41,7 +41,7 @@ template <typename T>
 struct ChainProg {
   int n_steps;
   int identity;  // 1: the program is exactly LOAD 0
-  int lite;      // 1: only cheap ops occur (see chain_eval)
+  int lite;      // 1: at most kFastSteps steps, all cheap binary ops (see chain_eval_fast)
   uint8_t first_kind, first_idx;
   T first_imm;
   // step s: run = op(x, y[, z]) where exactly one of x/y/z is LEAF_RUN
@@ -285,6 +285,71 @@ __device__ __forceinline__ void chain_eval(const ChainProg<T> &pr, const T (&w)[
 // Reduction state: value plus (for argmax) the position along the reduced axis.
 // ---------------------------------------------------------------------------
 enum { ROP_SUM = 0, ROP_MAX = 1, ROP_ARGMAX = 2 };
+
+// ---------------------------------------------------------------------------
+// Fast chains: at most kFastSteps cheap binary steps (no where, no unary).
+// The program is decoded ONCE per thread into registers, so the per-batch
+// loop has no dependent constant-bank loads left in it; the step loop is
+// fully unrolled and predicated on the step count.
+// ---------------------------------------------------------------------------
+constexpr int kFastSteps = 6;
+
+template <typename T>
+struct ChainRegs {
+  int n;
+  int first;  // bit 0: 1 = immediate, 0 = load; bits 4..: input index
+  T first_imm;
+  int op[kFastSteps];
+  int leaf[kFastSteps];  // bit 0: running value is the first operand; bit 1: leaf is an immediate; bits 4..: input index
+  T imm[kFastSteps];
+};
+
+template <typename T>
+__device__ __forceinline__ void chain_decode(const ChainProg<T> &pr, ChainRegs<T> &r) {
+  r.n = pr.n_steps;
+  r.first = (pr.first_kind == LEAF_IMM ? 1 : 0) | ((int)pr.first_idx << 4);
+  r.first_imm = pr.first_imm;
+#pragma unroll
+  for (int s = 0; s < kFastSteps; ++s) {
+    const bool run_first = pr.kind[s][0] == LEAF_RUN;
+    const int q = run_first ? 1 : 0;
+    r.op[s] = pr.op[s];
+    r.leaf[s] = (run_first ? 1 : 0) | (pr.kind[s][q] == LEAF_IMM ? 2 : 0) | ((int)pr.idx[s][q] << 4);
+    r.imm[s] = pr.imm[s][q];
+  }
+}
+
+template <typename T, int NIN, int N>
+__device__ __forceinline__ void chain_eval_fast(const ChainRegs<T> &r, const T (&w)[NIN][N], T (&run)[N]) {
+  if (r.first & 1) {
+#pragma unroll
+    for (int e = 0; e < N; ++e) run[e] = r.first_imm;
+  } else {
+#pragma unroll
+    for (int k = 0; k < NIN; ++k)
+      if (k == (r.first >> 4) || k == NIN - 1) {
+#pragma unroll
+        for (int e = 0; e < N; ++e) run[e] = w[k][e];
+        break;
+      }
+  }
+#pragma unroll
+  for (int s = 0; s < kFastSteps; ++s) {
+    if (s < r.n) {
+      const int op = r.op[s];
+      const bool run_first = r.leaf[s] & 1;
+      if (r.leaf[s] & 2) {
+        const T imm = r.imm[s];
+        chain_binary<T, N, true>(op, run_first, run, [&](int) { return imm; });
+      } else {
+        const int idx = r.leaf[s] >> 4;
+#pragma unroll
+        for (int k = 0; k < NIN; ++k)
+          if (k == idx) chain_binary<T, N, true>(op, run_first, run, [&](int e) { return w[k][e]; });
+      }
+    }
+  }
+}
 
 template <typename T> __device__ __forceinline__ T lowest_of();
 template <> __device__ __forceinline__ float lowest_of<float>() { return -INFINITY; }

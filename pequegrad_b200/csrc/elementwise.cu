@@ -85,7 +85,13 @@ __global__ void __launch_bounds__(256) ew_fast_kernel(const __grid_constant__ Ew
     }
   }
   T run[B];
-  chain_eval<T, NIN, B, LITE>(p.pro, w, run);
+  if (LITE) {
+    ChainRegs<T> cr;
+    chain_decode<T>(p.pro, cr);
+    chain_eval_fast<T, NIN, B>(cr, w, run);
+  } else {
+    chain_eval<T, NIN, B, false>(p.pro, w, run);
+  }
 #pragma unroll
   for (int u = 0; u < U; ++u) {
     const int64_t vid = v0 + (int64_t)u * 256;

@@ -115,8 +115,9 @@ inline bool to_chain(const pgb_instr *p, int n, ChainProg<T> &o) {
   o.lite = 1;
   for (int s = 0; s < ns; ++s) {
     const int op = steps[s].op;
-    if (op_is_unary(op) || op == PGB_OP_POW || op == PGB_OP_MOD) o.lite = 0;
+    if (!op_is_binary(op) || op == PGB_OP_POW || op == PGB_OP_MOD) o.lite = 0;
   }
+  if (ns > kFastSteps) o.lite = 0;
   for (int s = 0; s < ns; ++s) {
     const Step &st = steps[ns - 1 - s];
     o.op[s] = st.op;

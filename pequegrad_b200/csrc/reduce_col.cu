@@ -22,9 +22,11 @@ namespace pgb {
 
 template <typename T, typename InT, int NIN, int ROP, int MODE, int V>
 __global__ void __launch_bounds__(256, NIN == 1 ? PGB_COL_MINB : 2) reduce_col_kernel(const __grid_constant__ ColParams<T, NIN> p) {
-  // MODE 0: no prologue; 1: cheap-op chain over a 16-element batch; 2: any chain, one small batch at a time
+  // MODE 0: no prologue; 1: short chain of cheap binary ops, decoded into registers, 16-element batches; 2: any chain, one small batch at a time
   constexpr int B = (MODE == 2) ? (V > 4 ? V : 4) : kBatch;
   constexpr int U = B / V;
+  ChainRegs<T> cr;
+  if (MODE == 1) chain_decode<T>(p.pro, cr);
   constexpr int TY = 8;
   constexpr int TILE = 32 * V;
   const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
@@ -79,7 +81,8 @@ __global__ void __launch_bounds__(256, NIN == 1 ? PGB_COL_MINB : 2) reduce_col_k
 #pragma unroll
         for (int e = 0; e < B; ++e) run[e] = w[0][e];
       } else {
-        chain_eval<T, NIN, B, MODE == 1>(p.pro, w, run);
+        if (MODE == 1) chain_eval_fast<T, NIN, B>(cr, w, run);
+          else chain_eval<T, NIN, B, false>(p.pro, w, run);
       }
 #pragma unroll
       for (int u = 0; u < U; ++u) {

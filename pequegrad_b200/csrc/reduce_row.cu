@@ -17,9 +17,11 @@ namespace pgb {
 
 template <typename T, typename InT, int NIN, int ROP, int MODE, int V, int G>
 __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__ RowParams<T, NIN> p) {
-  // MODE 0: no prologue; 1: cheap-op chain over a 16-element batch; 2: any chain, one small batch at a time
+  // MODE 0: no prologue; 1: short chain of cheap binary ops, decoded into registers, 16-element batches; 2: any chain, one small batch at a time
   constexpr int B = (MODE == 2) ? (V > 4 ? V : 4) : kBatch;
   constexpr int U = B / V;
+  ChainRegs<T> cr;
+  if (MODE == 1) chain_decode<T>(p.pro, cr);
   constexpr int GPB = 256 / G;
   const int g = threadIdx.x / G, t = threadIdx.x % G;
   const int64_t item = (int64_t)blockIdx.x * GPB + g;
@@ -79,7 +81,8 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
 #pragma unroll
           for (int e = 0; e < B; ++e) run[e] = w[0][e];
         } else {
-          chain_eval<T, NIN, B, MODE == 1>(p.pro, w, run);
+          if (MODE == 1) chain_eval_fast<T, NIN, B>(cr, w, run);
+          else chain_eval<T, NIN, B, false>(p.pro, w, run);
         }
 #pragma unroll
         for (int u = 0; u < U; ++u) {
