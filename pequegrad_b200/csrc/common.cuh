@@ -174,64 +174,81 @@ __device__ __forceinline__ void vm_eval(const VmProg<T> &pr, T *v, T acc, Loader
 // ---------------------------------------------------------------------------
 // Chain evaluation over a batch of N elements held in registers.
 // w[k][e] = element e of input k (already widened to T).
+//
+// In a chain the running value is always the FIRST operand of a binary step;
+// where the program had it second, the host swaps the operands of commutative
+// ops, mirrors comparisons, and uses the reversed opcodes below for the rest.
 // ---------------------------------------------------------------------------
+enum { IOP_RSUB = 40, IOP_RDIV = 41, IOP_RPOW = 42, IOP_RMOD = 43 };
+
 template <typename T, int NIN, int N>
-__device__ __forceinline__ void chain_leaf(const ChainProg<T> &pr, int kind, int idx, T imm,
-                                           const T (&w)[NIN][N], const T (&run)[N], T (&o)[N]) {
-  if (kind == LEAF_RUN) {
+__device__ __forceinline__ void chain_first(int is_imm, int idx, T imm, const T (&w)[NIN][N], T (&run)[N]) {
+  if (is_imm) {
 #pragma unroll
-    for (int e = 0; e < N; ++e) o[e] = run[e];
-  } else if (kind == LEAF_IMM) {
-#pragma unroll
-    for (int e = 0; e < N; ++e) o[e] = imm;
+    for (int e = 0; e < N; ++e) run[e] = imm;
   } else {
 #pragma unroll
     for (int k = 0; k < NIN; ++k)
       if (k == idx || k == NIN - 1) {
 #pragma unroll
-        for (int e = 0; e < N; ++e) o[e] = w[k][e];
+        for (int e = 0; e < N; ++e) run[e] = w[k][e];
         break;
       }
   }
 }
 
-// LITE: the host guarantees that only add/mul/sub/max/div, comparisons and
-// where occur, which keeps the batch in few registers. Otherwise every op is
-// allowed (transcendentals, casts, pow, mod) and callers use a small batch.
-template <typename T>
-__device__ __forceinline__ T apply_binary_lite(int op, T x, T y) {
+// One binary step over the batch. The op is chosen by ONE uniform branch with
+// the element loop inside each case (a per-element switch gets if-converted
+// into "compute every op, then select", which multiplies the instruction count).
+// `y(e)` yields the leaf operand of element e without materialising an array.
+template <typename T, int N, bool FULL, typename Y>
+__device__ __forceinline__ void chain_binary(int op, T (&run)[N], Y y) {
+#define PGB_STEP(EXPR)                         \
+  {                                            \
+    _Pragma("unroll") for (int e = 0; e < N; ++e) { \
+      const T a = run[e];                      \
+      const T b = y(e);                        \
+      run[e] = (EXPR);                         \
+    }                                          \
+  }                                            \
+  break;
   switch (op) {
-    case PGB_OP_ADD: return x + y;
-    case PGB_OP_MUL: return x * y;
-    case PGB_OP_MAX: return x > y ? x : y;
-    case PGB_OP_SUB: return x - y;
-    case PGB_OP_DIV: return t_div<T>(x, y);
-    case PGB_OP_GT: return (T)(x > y);
-    case PGB_OP_LT: return (T)(x < y);
-    case PGB_OP_EQ: return (T)(x == y);
-    case PGB_OP_LTE: return (T)(x <= y);
-    case PGB_OP_NEQ: return (T)(x != y);
-    default: return (T)(x >= y);
+    case PGB_OP_ADD: PGB_STEP(a + b)
+    case PGB_OP_MUL: PGB_STEP(a * b)
+    case PGB_OP_SUB: PGB_STEP(a - b)
+    case IOP_RSUB: PGB_STEP(b - a)
+    case PGB_OP_MAX: PGB_STEP(a > b ? a : b)
+    case PGB_OP_DIV: PGB_STEP(t_div<T>(a, b))
+    case IOP_RDIV: PGB_STEP(t_div<T>(b, a))
+    case PGB_OP_GT: PGB_STEP((T)(a > b))
+    case PGB_OP_LT: PGB_STEP((T)(a < b))
+    case PGB_OP_EQ: PGB_STEP((T)(a == b))
+    case PGB_OP_NEQ: PGB_STEP((T)(a != b))
+    case PGB_OP_LTE: PGB_STEP((T)(a <= b))
+    case PGB_OP_GTE: PGB_STEP((T)(a >= b))
+    default:
+      if (FULL) {
+        switch (op) {
+          case PGB_OP_POW: PGB_STEP(t_pow<T>(a, b))
+          case IOP_RPOW: PGB_STEP(t_pow<T>(b, a))
+          case PGB_OP_MOD: PGB_STEP(t_mod<T>(a, b))
+          case IOP_RMOD: PGB_STEP(t_mod<T>(b, a))
+          default: break;
+        }
+      }
+      break;
   }
+#undef PGB_STEP
 }
 
-// One binary step over the batch; `y(e)` yields the leaf operand of element e
-// without materialising it as an array.
-template <typename T, int N, bool LITE, typename Y>
-__device__ __forceinline__ void chain_binary(int op, bool run_first, T (&run)[N], Y y) {
-  // the two ops of nearly every prologue get their own loops
-  if (op == PGB_OP_ADD) {
-#pragma unroll
-    for (int e = 0; e < N; ++e) run[e] = run[e] + y(e);
-  } else if (op == PGB_OP_MUL) {
-#pragma unroll
-    for (int e = 0; e < N; ++e) run[e] = run[e] * y(e);
-  } else if (run_first) {
-#pragma unroll
-    for (int e = 0; e < N; ++e) run[e] = LITE ? apply_binary_lite<T>(op, run[e], y(e)) : apply_binary<T>(op, run[e], y(e));
+template <typename T, int NIN, int N, bool FULL>
+__device__ __forceinline__ void chain_step_binary(int op, int leaf_is_imm, int idx, T imm, const T (&w)[NIN][N], T (&run)[N]) {
+  if (leaf_is_imm) {
+    chain_binary<T, N, FULL>(op, run, [&](int) { return imm; });
   } else {
 #pragma unroll
-    for (int e = 0; e < N; ++e) run[e] = LITE ? apply_binary_lite<T>(op, y(e), run[e]) : apply_binary<T>(op, y(e), run[e]);
+    for (int k = 0; k < NIN; ++k)
+      if (k == idx) chain_binary<T, N, FULL>(op, run, [&](int e) { return w[k][e]; });
   }
 }
 
@@ -246,29 +263,32 @@ __device__ __forceinline__ T leaf_val(int kind, int idx, T imm, const T (&w)[NIN
   return (kind == LEAF_RUN) ? run[e] : v;
 }
 
-template <typename T, int NIN, int N, bool LITE>
+// General chain: any op, any length up to kChainSteps; the program is read
+// from the kernel parameters step by step. Callers use a small batch.
+template <typename T, int NIN, int N>
 __device__ __forceinline__ void chain_eval(const ChainProg<T> &pr, const T (&w)[NIN][N], T (&run)[N]) {
-  chain_leaf<T, NIN, N>(pr, pr.first_kind, pr.first_idx, pr.first_imm, w, run, run);
+  chain_first<T, NIN, N>(pr.first_kind == LEAF_IMM, pr.first_idx, pr.first_imm, w, run);
   for (int s = 0; s < pr.n_steps; ++s) {
     const int op = pr.op[s];
     if (op < PGB_OP_ADD) {
-      if (!LITE) {
-#pragma unroll
-        for (int e = 0; e < N; ++e) run[e] = apply_unary<T>(op, run[e]);
+      switch (op) {
+#define PGB_UN(OPC, EXPR)                                              \
+  case OPC: {                                                          \
+    _Pragma("unroll") for (int e = 0; e < N; ++e) run[e] = (EXPR);   \
+  } break;
+        PGB_UN(PGB_OP_LOG, t_log<T>(run[e]))
+        PGB_UN(PGB_OP_EXP, t_exp<T>(run[e]))
+        PGB_UN(PGB_OP_SIN, t_sin<T>(run[e]))
+        PGB_UN(PGB_OP_COS, t_cos<T>(run[e]))
+        PGB_UN(PGB_OP_CAST_F16, t_round_f16<T>(run[e]))
+        PGB_UN(PGB_OP_CAST_F32, t_round_f32<T>(run[e]))
+        PGB_UN(PGB_OP_CAST_I32, t_trunc_i32<T>(run[e]))
+        PGB_UN(PGB_OP_CAST_BF16, t_round_bf16<T>(run[e]))
+#undef PGB_UN
+        default: break;
       }
-    } else if (op < PGB_OP_WHERE) {
-      // one side is the running value, the other a leaf
-      const bool run_first = pr.kind[s][0] == LEAF_RUN;
-      const int q = run_first ? 1 : 0;
-      if (pr.kind[s][q] == LEAF_IMM) {
-        const T imm = pr.imm[s][q];
-        chain_binary<T, N, LITE>(op, run_first, run, [&](int) { return imm; });
-      } else {
-        const int idx = pr.idx[s][q];
-#pragma unroll
-        for (int k = 0; k < NIN; ++k)
-          if (k == idx) chain_binary<T, N, LITE>(op, run_first, run, [&](int e) { return w[k][e]; });
-      }
+    } else if (op != PGB_OP_WHERE) {
+      chain_step_binary<T, NIN, N, true>(op, pr.kind[s][1] == LEAF_IMM, pr.idx[s][1], pr.imm[s][1], w, run);
     } else {
 #pragma unroll
       for (int e = 0; e < N; ++e) {
@@ -282,15 +302,9 @@ __device__ __forceinline__ void chain_eval(const ChainProg<T> &pr, const T (&w)[
 }
 
 // ---------------------------------------------------------------------------
-// Reduction state: value plus (for argmax) the position along the reduced axis.
-// ---------------------------------------------------------------------------
-enum { ROP_SUM = 0, ROP_MAX = 1, ROP_ARGMAX = 2 };
-
-// ---------------------------------------------------------------------------
-// Fast chains: at most kFastSteps cheap binary steps (no where, no unary).
-// The program is decoded ONCE per thread into registers, so the per-batch
-// loop has no dependent constant-bank loads left in it; the step loop is
-// fully unrolled and predicated on the step count.
+// Fast chains: at most kFastSteps cheap binary steps (no where, no unary, no
+// pow / mod). The program is decoded ONCE per thread into registers and the
+// step loop is fully unrolled and predicated on the step count.
 // ---------------------------------------------------------------------------
 constexpr int kFastSteps = 6;
 
@@ -300,7 +314,7 @@ struct ChainRegs {
   int first;  // bit 0: 1 = immediate, 0 = load; bits 4..: input index
   T first_imm;
   int op[kFastSteps];
-  int leaf[kFastSteps];  // bit 0: running value is the first operand; bit 1: leaf is an immediate; bits 4..: input index
+  int leaf[kFastSteps];  // bit 0: leaf is an immediate; bits 4..: input index
   T imm[kFastSteps];
 };
 
@@ -311,45 +325,26 @@ __device__ __forceinline__ void chain_decode(const ChainProg<T> &pr, ChainRegs<T
   r.first_imm = pr.first_imm;
 #pragma unroll
   for (int s = 0; s < kFastSteps; ++s) {
-    const bool run_first = pr.kind[s][0] == LEAF_RUN;
-    const int q = run_first ? 1 : 0;
     r.op[s] = pr.op[s];
-    r.leaf[s] = (run_first ? 1 : 0) | (pr.kind[s][q] == LEAF_IMM ? 2 : 0) | ((int)pr.idx[s][q] << 4);
-    r.imm[s] = pr.imm[s][q];
+    r.leaf[s] = (pr.kind[s][1] == LEAF_IMM ? 1 : 0) | ((int)pr.idx[s][1] << 4);
+    r.imm[s] = pr.imm[s][1];
   }
 }
 
 template <typename T, int NIN, int N>
 __device__ __forceinline__ void chain_eval_fast(const ChainRegs<T> &r, const T (&w)[NIN][N], T (&run)[N]) {
-  if (r.first & 1) {
-#pragma unroll
-    for (int e = 0; e < N; ++e) run[e] = r.first_imm;
-  } else {
-#pragma unroll
-    for (int k = 0; k < NIN; ++k)
-      if (k == (r.first >> 4) || k == NIN - 1) {
-#pragma unroll
-        for (int e = 0; e < N; ++e) run[e] = w[k][e];
-        break;
-      }
-  }
+  chain_first<T, NIN, N>(r.first & 1, r.first >> 4, r.first_imm, w, run);
 #pragma unroll
   for (int s = 0; s < kFastSteps; ++s) {
-    if (s < r.n) {
-      const int op = r.op[s];
-      const bool run_first = r.leaf[s] & 1;
-      if (r.leaf[s] & 2) {
-        const T imm = r.imm[s];
-        chain_binary<T, N, true>(op, run_first, run, [&](int) { return imm; });
-      } else {
-        const int idx = r.leaf[s] >> 4;
-#pragma unroll
-        for (int k = 0; k < NIN; ++k)
-          if (k == idx) chain_binary<T, N, true>(op, run_first, run, [&](int e) { return w[k][e]; });
-      }
-    }
+    if (s < r.n) chain_step_binary<T, NIN, N, false>(r.op[s], r.leaf[s] & 1, r.leaf[s] >> 4, r.imm[s], w, run);
   }
 }
+
+// ---------------------------------------------------------------------------
+// Reduction state: value plus (for argmax) the position along the reduced axis.
+// ---------------------------------------------------------------------------
+enum { ROP_SUM = 0, ROP_MAX = 1, ROP_ARGMAX = 2 };
+
 
 template <typename T> __device__ __forceinline__ T lowest_of();
 template <> __device__ __forceinline__ float lowest_of<float>() { return -INFINITY; }

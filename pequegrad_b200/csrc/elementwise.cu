@@ -90,7 +90,7 @@ __global__ void __launch_bounds__(256) ew_fast_kernel(const __grid_constant__ Ew
     chain_decode<T>(p.pro, cr);
     chain_eval_fast<T, NIN, B>(cr, w, run);
   } else {
-    chain_eval<T, NIN, B, false>(p.pro, w, run);
+    chain_eval<T, NIN, B>(p.pro, w, run);
   }
 #pragma unroll
   for (int u = 0; u < U; ++u) {

@@ -93,7 +93,23 @@ inline bool to_chain(const pgb_instr *p, int n, ChainProg<T> &o) {
     } else if (op_is_binary(op)) {
       const int a = p[cur].a, b = p[cur].b;
       if (is_leaf(b)) { s.kind[0] = LEAF_RUN; leaf(s, 1, b); steps[ns++] = s; cur = a; }
-      else if (is_leaf(a)) { leaf(s, 0, a); s.kind[1] = LEAF_RUN; steps[ns++] = s; cur = b; }
+      else if (is_leaf(a)) {
+        // the running value becomes the first operand: swap, mirror or use the reversed opcode
+        int rop = op;
+        switch (op) {
+          case PGB_OP_SUB: rop = IOP_RSUB; break;
+          case PGB_OP_DIV: rop = IOP_RDIV; break;
+          case PGB_OP_POW: rop = IOP_RPOW; break;
+          case PGB_OP_MOD: rop = IOP_RMOD; break;
+          case PGB_OP_GT: rop = PGB_OP_LT; break;
+          case PGB_OP_LT: rop = PGB_OP_GT; break;
+          case PGB_OP_LTE: rop = PGB_OP_GTE; break;
+          case PGB_OP_GTE: rop = PGB_OP_LTE; break;
+          default: break;  // add, mul, max, eq, neq commute
+        }
+        s.op = (uint8_t)rop;
+        s.kind[0] = LEAF_RUN; leaf(s, 1, a); steps[ns++] = s; cur = b;
+      }
       else return false;
     } else {  // where
       const int v[3] = {p[cur].a, p[cur].b, p[cur].c};
@@ -115,7 +131,8 @@ inline bool to_chain(const pgb_instr *p, int n, ChainProg<T> &o) {
   o.lite = 1;
   for (int s = 0; s < ns; ++s) {
     const int op = steps[s].op;
-    if (!op_is_binary(op) || op == PGB_OP_POW || op == PGB_OP_MOD) o.lite = 0;
+    const bool cheap = (op_is_binary(op) && op != PGB_OP_POW && op != PGB_OP_MOD) || op == IOP_RSUB || op == IOP_RDIV;
+    if (!cheap) o.lite = 0;
   }
   if (ns > kFastSteps) o.lite = 0;
   for (int s = 0; s < ns; ++s) {

@@ -1,236 +1,13 @@
-// Column reduce: a KEPT dim is the memory-contiguous one and the reduced dims
-// are strided (axis 0 of a matrix, the middle axis of a 3-D tensor, permuted
-// views of either). The reference handles these with the same one-block-per-
-// output kernel, whose consecutive threads then read addresses a whole row
-// apart (csrc/cuda/reduce.cuh:52-71).
-//
-// A CTA is 32 x 8 threads: x owns V consecutive columns (one 128-bit load),
-// y strides over the reduced rows, kBatch/V rows in flight per thread. The 8
-// partial rows are combined through shared memory and written with one
-// coalesced store per column tile. When the contiguous kept dim is not the
-// innermost dim of the OUTPUT (a permuted view), `jout` carries its output
-// stride and the stores scatter; L2 merges them.
-#include <type_traits>
+// Dispatcher of the col reduce family; the kernels are instantiated in reduce_col_*.cu
+// (one translation unit per input type and input count, so they compile in parallel).
+#include "reduce_col.cuh"
 
-#include "reduce_common.cuh"
-#include "vec.cuh"
-
-#ifndef PGB_COL_MINB
-#define PGB_COL_MINB 4
-#endif
 namespace pgb {
 
-template <typename T, typename InT, int NIN, int ROP, int MODE, int V>
-__global__ void __launch_bounds__(256, NIN == 1 ? PGB_COL_MINB : 2) reduce_col_kernel(const __grid_constant__ ColParams<T, NIN> p) {
-  // MODE 0: no prologue; 1: short chain of cheap binary ops, decoded into registers, 16-element batches; 2: any chain, one small batch at a time
-  constexpr int B = (MODE == 2) ? (V > 4 ? V : 4) : kBatch;
-  constexpr int U = B / V;
-  ChainRegs<T> cr;
-  if (MODE == 1) chain_decode<T>(p.pro, cr);
-  constexpr int TY = 8;
-  constexpr int TILE = 32 * V;
-  const int x = threadIdx.x & 31, y = threadIdx.x >> 5;
-  int64_t bid = blockIdx.x;
-  const int64_t tile = bid % p.ntiles;
-  bid /= p.ntiles;
-  const int64_t s = bid % p.S;
-  const int64_t batch = bid / p.S;
-  const int64_t b1 = batch % p.bsize1, b0 = batch / p.bsize1;
-  const int64_t j = tile * TILE + (int64_t)x * V;
-  const bool col_ok = j < p.J;
-
-  Acc<T, ROP> acc[V];
-#pragma unroll
-  for (int e = 0; e < V; ++e) acc[e].init();
-
-  const int64_t r_lo = s * p.rows_per_split;
-  const int64_t r_hi = min(p.R, r_lo + p.rows_per_split);
-  if (col_ok) {
-    const InT *base[NIN];
-#pragma unroll
-    for (int k = 0; k < NIN; ++k)
-      base[k] = (const InT *)p.in[k] + b0 * p.bstr[k][0] + b1 * p.bstr[k][1] + j * p.jstr[k];
-    for (int64_t rb = r_lo + y; rb < r_hi; rb += (int64_t)TY * U) {
-      T w[NIN][B];
-#pragma unroll
-      for (int k = 0; k < NIN; ++k) {
-#pragma unroll
-        for (int u = 0; u < U; ++u) {
-          const int64_t r = rb + (int64_t)u * TY;
-          T tmpv[V];
-          if (r < r_hi) {
-            int64_t off;
-            if (p.R0 == 1) off = r * p.rstr[k][1];
-            else { const int64_t r0 = r / p.R1; off = r0 * p.rstr[k][0] + (r - r0 * p.R1) * p.rstr[k][1]; }
-            if (p.jstr[k] != 0) load_vec<T, InT, V>(base[k] + off, tmpv);
-            else {
-              const T b = to_compute<T, InT>(__ldg(base[k] + off));
-#pragma unroll
-              for (int e = 0; e < V; ++e) tmpv[e] = b;
-            }
-          } else {
-#pragma unroll
-            for (int e = 0; e < V; ++e) tmpv[e] = (T)0;
-          }
-#pragma unroll
-          for (int e = 0; e < V; ++e) w[k][u * V + e] = tmpv[e];
-        }
-      }
-      T run[B];
-      if (MODE == 0) {
-#pragma unroll
-        for (int e = 0; e < B; ++e) run[e] = w[0][e];
-      } else {
-        if (MODE == 1) chain_eval_fast<T, NIN, B>(cr, w, run);
-          else chain_eval<T, NIN, B, false>(p.pro, w, run);
-      }
-#pragma unroll
-      for (int u = 0; u < U; ++u) {
-        const int64_t r = rb + (int64_t)u * TY;
-        if (r < r_hi) {
-#pragma unroll
-          for (int e = 0; e < V; ++e) acc[e].add(run[u * V + e], (int)r);
-        }
-      }
-    }
-  }
-  __shared__ T sv[TY][TILE];
-  __shared__ int si[ROP == ROP_ARGMAX ? TY : 1][TILE];
-#pragma unroll
-  for (int e = 0; e < V; ++e) {
-    sv[y][x * V + e] = acc[e].v;
-    if (ROP == ROP_ARGMAX) si[y][x * V + e] = acc[e].i;
-  }
-  __syncthreads();
-  for (int col = threadIdx.x; col < TILE; col += 256) {
-    const int64_t jj = tile * TILE + col;
-    if (jj >= p.J) break;
-    Acc<T, ROP> a;
-    a.init();
-#pragma unroll
-    for (int yy = 0; yy < TY; ++yy) a.merge(sv[yy][col], ROP == ROP_ARGMAX ? si[yy][col] : 0);
-    const int64_t o = b0 * p.bout[0] + b1 * p.bout[1] + jj * p.jout;
-    if (p.S == 1) finish_output<T>(p.epi, o, a.v, a.i);
-    else {
-      p.part_v[s * p.n_out + o] = a.v;
-      if (ROP == ROP_ARGMAX) p.part_i[s * p.n_out + o] = a.i;
-    }
-  }
-}
-
-// ---------------------------------------------------------------------------
-template <typename InT, int NIN>
-static int launch_col_typed(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain) {
-  using T = float;
-  const CanonReduce &c = j.c;
-  constexpr int VFULL = 16 / (int)sizeof(InT);
-  ColParams<T, NIN> p{};
-  // output strides of the kept dims (the output is contiguous in kept order)
-  int64_t kout[PGB_MAX_DIMS];
-  {
-    int64_t acc = 1;
-    for (int d = c.nk - 1; d >= 0; --d) { kout[d] = acc; acc *= c.ksize[d]; }
-  }
-  p.J = c.ksize[jd];
-  p.jout = kout[jd];
-  int bd[2] = {-1, -1};
-  {
-    int nb = 0;
-    for (int d = 0; d < c.nk; ++d) if (d != jd) bd[nb++] = d;
-    if (nb == 1) { bd[1] = bd[0]; bd[0] = -1; }  // right-align
-  }
-  int64_t bs[2] = {1, 1};
-  for (int q = 0; q < 2; ++q) {
-    if (bd[q] >= 0) { bs[q] = c.ksize[bd[q]]; p.bout[q] = kout[bd[q]]; }
-    else p.bout[q] = 0;
-  }
-  p.bsize1 = bs[1];
-  p.nbatch = bs[0] * bs[1];
-  p.R0 = (c.nr == 2) ? c.rsize[0] : 1;
-  p.R1 = (c.nr >= 1) ? c.rsize[c.nr - 1] : 1;
-  p.R = p.R0 * p.R1;
-  p.n_out = c.n_out;
-  bool vec = (p.J % VFULL) == 0;
-  for (int k = 0; k < NIN; ++k) {
-    p.in[k] = j.in[k].data;
-    p.jstr[k] = c.kin[k][jd];
-    for (int q = 0; q < 2; ++q) p.bstr[k][q] = bd[q] >= 0 ? c.kin[k][bd[q]] : 0;
-    p.rstr[k][0] = (c.nr == 2) ? c.rin[k][0] : 0;
-    p.rstr[k][1] = (c.nr >= 1) ? c.rin[k][c.nr - 1] : 0;
-    if (p.jstr[k] == 1) {
-      if ((reinterpret_cast<uintptr_t>(p.in[k]) & 15) != 0) vec = false;
-      for (int q = 0; q < 2; ++q) if (p.bstr[k][q] % VFULL) vec = false;
-      for (int q = 0; q < 2; ++q) if (p.rstr[k][q] % VFULL) vec = false;
-    }
-  }
-  const int V = vec ? VFULL : 1;
-  p.ntiles = (p.J + 32 * V - 1) / (32 * V);
-  const int64_t ctas = p.ntiles * p.nbatch;
-  const int64_t want = (int64_t)sm_count() * 16;
-  int64_t S = 1;
-  if (ctas < want) {
-    const int64_t s_want = (want + ctas - 1) / ctas;
-    const int64_t s_max = std::max<int64_t>(1, p.R / 64);
-    S = std::max<int64_t>(1, std::min(s_want, s_max));
-  }
-  p.rows_per_split = (p.R + S - 1) / S;
-  S = (p.R + p.rows_per_split - 1) / p.rows_per_split;
-  if (S < 1) S = 1;
-  p.S = S;
-  const int64_t grid = ctas * S;
-  if (grid > 2147483647LL) return 0;
-  const size_t ws = (S > 1) ? (size_t)(S * p.n_out) * (sizeof(T) + (j.rop == ROP_ARGMAX ? sizeof(int) : 0)) : 0;
-  j.ws_needed = ws;
-  char buf[256];
-  snprintf(buf, sizeof buf, "col in=%s nin=%d %s vec=%d split=%lld grid=%lld J=%lld jout=%lld R=%lld batch=%lld", dtype_name(j.in[0].dtype),
-           NIN, ident ? "ident" : (chain.lite ? "chain" : "chain-full"), V, (long long)S, (long long)grid, (long long)p.J, (long long)p.jout, (long long)p.R,
-           (long long)p.nbatch);
-  j.desc = buf;
-  if (j.dry_run) return 1;
-
-  void *ws_ptr = nullptr;
-  bool own_ws = false;
-  if (ws) {
-    if (j.workspace) {
-      if (j.workspace_bytes < ws) { set_error("fused_reduce: workspace too small"); return PGB_ERR_WORKSPACE; }
-      ws_ptr = j.workspace;
-    } else {
-      if (cudaMallocAsync(&ws_ptr, ws, j.stream) != cudaSuccess) { set_error("fused_reduce: workspace allocation failed"); return PGB_ERR_CUDA; }
-      own_ws = true;
-    }
-    p.part_v = (T *)ws_ptr;
-    p.part_i = (int *)((char *)ws_ptr + (size_t)(S * p.n_out) * sizeof(T));
-  }
-  p.pro = chain;
-  std::string err = make_epi<T>(j, p.epi);
-  if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
-
-  auto go = [&](auto rop_c, auto ident_c, auto v_c) {
-    constexpr int ROP = decltype(rop_c)::value;
-    constexpr int MD = decltype(ident_c)::value;
-    constexpr int VV = decltype(v_c)::value;
-    reduce_col_kernel<T, InT, NIN, ROP, MD, VV><<<(unsigned)grid, 256, 0, j.stream>>>(p);
-  };
-  auto by_v = [&](auto rop_c, auto ident_c) {
-    if (V == 1) go(rop_c, ident_c, std::integral_constant<int, 1>{});
-    else go(rop_c, ident_c, std::integral_constant<int, VFULL>{});
-  };
-  auto by_ident = [&](auto rop_c) {
-    if constexpr (NIN == 1) {
-      if (ident) { by_v(rop_c, std::integral_constant<int, 0>{}); return; }
-    }
-    if (chain.lite) by_v(rop_c, std::integral_constant<int, 1>{});
-    else by_v(rop_c, std::integral_constant<int, 2>{});
-  };
-  if (j.rop == ROP_SUM) by_ident(std::integral_constant<int, ROP_SUM>{});
-  else if (j.rop == ROP_MAX) by_ident(std::integral_constant<int, ROP_MAX>{});
-  else by_ident(std::integral_constant<int, ROP_ARGMAX>{});
-  count_launch();
-  int st = check_launch("reduce_col_kernel");
-  if (st == PGB_OK && S > 1) st = launch_reduce_finish(j, p.part_v, p.part_i, S);
-  if (own_ws) cudaFreeAsync(ws_ptr, j.stream);
-  return st == PGB_OK ? 1 : st;
-}
+extern template int launch_col_typed<float, 1>(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain);
+extern template int launch_col_typed<float, 2>(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain);
+extern template int launch_col_typed<__half, 1>(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain);
+extern template int launch_col_typed<__half, 2>(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain);
 
 int launch_reduce_col(ReduceJob &j) {
   const CanonReduce &c = j.c;

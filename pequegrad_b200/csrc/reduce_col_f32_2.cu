@@ -1,0 +1,6 @@
+// Instantiates the col reduce kernels for f32 inputs, 2 input tensor(s).
+#include "reduce_col.cuh"
+
+namespace pgb {
+template int launch_col_typed<float, 2>(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain);
+}  // namespace pgb

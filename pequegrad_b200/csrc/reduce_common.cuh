@@ -34,6 +34,7 @@ struct RowParams {
   int64_t r1str[NIN];    // outer reduced dim
   int64_t cstr[NIN];     // inner reduced dim: 1 or 0 (broadcast)
   int64_t ksize1, ksize2;
+  int nk;  // number of kept dims in use (0..3)
   int64_t n_out, C, R1;
   int64_t chunk;    // inner-dim elements per segment
   int64_t nchunks;  // segments per (row, r1)

@@ -1,0 +1,6 @@
+// Instantiates the row reduce kernels for f32 inputs, 1 input tensor(s).
+#include "reduce_row.cuh"
+
+namespace pgb {
+template int launch_row_typed<float, 1>(ReduceJob &j, bool ident, const ChainProg<float> &chain);
+}  // namespace pgb
