@@ -42,6 +42,7 @@ struct ChainProg {
   int n_steps;
   int identity;  // 1: the program is exactly LOAD 0
   int lite;      // 1: at most kFastSteps steps, all cheap binary ops (see chain_eval_fast)
+  int affine;    // 1: exactly (LOAD 0) * imm[0][1] + imm[1][1]
   uint8_t first_kind, first_idx;
   T first_imm;
   // step s: run = op(x, y[, z]) where exactly one of x/y/z is LEAF_RUN
@@ -400,6 +401,13 @@ struct EpiParams {
   int epi_dtype[kMaxIn];
   int64_t epi_stride[kMaxIn][kMaxDims];
   VmProg<T> prog;  // n == 0: store the value unchanged
+  // The two commonest epilogues skip the interpreter (which costs a few hundred
+  // instructions per output): 1 = one unary op on the result (exp, log, cast),
+  // 2 = one binary op with an immediate (scale, shift, clamp).
+  int fast_kind;
+  int fast_op;
+  int fast_rev;  // kind 2: the immediate is the first operand
+  T fast_imm;
 };
 
 template <typename T>
@@ -409,7 +417,11 @@ __device__ __forceinline__ void finish_output(const EpiParams<T> &ep, int64_t o,
     return;
   }
   if (ep.is_mean) acc = acc / ep.count;
-  if (ep.prog.n > 0) {
+  if (ep.fast_kind == 1) {
+    acc = apply_unary<T>(ep.fast_op, acc);
+  } else if (ep.fast_kind == 2) {
+    acc = ep.fast_rev ? apply_binary<T>(ep.fast_op, ep.fast_imm, acc) : apply_binary<T>(ep.fast_op, acc, ep.fast_imm);
+  } else if (ep.prog.n > 0) {
     T v[kMaxInstr];
     int64_t offs[kMaxIn];
     if (ep.n_epi_in > 0) {

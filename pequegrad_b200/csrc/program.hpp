@@ -135,6 +135,9 @@ inline bool to_chain(const pgb_instr *p, int n, ChainProg<T> &o) {
     if (!cheap) o.lite = 0;
   }
   if (ns > kFastSteps) o.lite = 0;
+  // x * a + b on input 0 (steps are still in reverse order here: steps[0] is the last op)
+  o.affine = (ns == 2 && o.first_kind == LEAF_LOAD && o.first_idx == 0 && steps[1].op == PGB_OP_MUL && steps[1].kind[1] == LEAF_IMM &&
+              steps[0].op == PGB_OP_ADD && steps[0].kind[1] == LEAF_IMM) ? 1 : 0;
   for (int s = 0; s < ns; ++s) {
     const Step &st = steps[ns - 1 - s];
     o.op[s] = st.op;

@@ -28,6 +28,8 @@ __global__ void __launch_bounds__(256, NIN == 1 ? PGB_COL_MINB : 2) reduce_col_k
   constexpr int U = B / V;
   ChainRegs<T> cr;
   if (MODE == 1) chain_decode<T>(p.pro, cr);
+  // MODE 3: the commonest prologue, x * a + b with two roundings, hard-wired
+  const T aff_a = p.pro.imm[0][1], aff_b = p.pro.imm[1][1];
   constexpr int TY = 8;
   constexpr int TILE = 32 * V;
   // 32-bit index arithmetic throughout (the host checks that the counts fit)
@@ -91,6 +93,9 @@ __global__ void __launch_bounds__(256, NIN == 1 ? PGB_COL_MINB : 2) reduce_col_k
       if (MODE == 0) {
 #pragma unroll
         for (int e = 0; e < B; ++e) run[e] = w[0][e];
+      } else if (MODE == 3) {
+#pragma unroll
+        for (int e = 0; e < B; ++e) run[e] = w[0][e] * aff_a + aff_b;
       } else if (MODE == 1) {
         chain_eval_fast<T, NIN, B>(cr, w, run);
       } else {
@@ -195,7 +200,7 @@ int launch_col_typed(ReduceJob &j, int jd, bool ident, const ChainProg<float> &c
   j.ws_needed = ws;
   char buf[256];
   snprintf(buf, sizeof buf, "col in=%s nin=%d %s vec=%d split=%lld grid=%lld J=%lld jout=%lld R=%lld batch=%lld", dtype_name(j.in[0].dtype),
-           NIN, ident ? "ident" : (chain.lite ? "chain" : "chain-full"), V, (long long)S, (long long)grid, (long long)p.J, (long long)p.jout, (long long)p.R,
+           NIN, ident ? "ident" : (chain.affine && NIN == 1 ? "chain-affine" : (chain.lite ? "chain" : "chain-full")), V, (long long)S, (long long)grid, (long long)p.J, (long long)p.jout, (long long)p.R,
            (long long)p.nbatch);
   j.desc = buf;
   if (j.dry_run) return 1;
@@ -230,6 +235,7 @@ int launch_col_typed(ReduceJob &j, int jd, bool ident, const ChainProg<float> &c
   auto by_ident = [&](auto rop_c) {
     if constexpr (NIN == 1) {
       if (ident) { by_v(rop_c, std::integral_constant<int, 0>{}); return; }
+      if (chain.affine) { by_v(rop_c, std::integral_constant<int, 3>{}); return; }
     }
     if (chain.lite) by_v(rop_c, std::integral_constant<int, 1>{});
     else by_v(rop_c, std::integral_constant<int, 2>{});

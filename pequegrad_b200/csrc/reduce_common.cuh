@@ -121,6 +121,21 @@ std::string make_epi(const ReduceJob &j, EpiParams<T> &e) {
     }
   }
   to_vm<T>(j.epi, j.n_epi, e.prog);
+  // epilogues that need no interpreter
+  const pgb_instr *p = j.epi;
+  if (j.n_epi == 2 && p[0].op == PGB_OP_ACC && op_is_unary(p[1].op) && p[1].a == 0) {
+    e.fast_kind = 1;
+    e.fast_op = p[1].op;
+  } else if (j.n_epi == 3 && op_is_binary(p[2].op)) {
+    const int ia = p[2].a, ib = p[2].b;
+    if (ia >= 0 && ia < 2 && ib >= 0 && ib < 2 && ia != ib && p[ia].op + p[ib].op == PGB_OP_ACC + PGB_OP_IMM &&
+        (p[ia].op == PGB_OP_ACC || p[ia].op == PGB_OP_IMM)) {
+      e.fast_kind = 2;
+      e.fast_op = p[2].op;
+      e.fast_rev = p[ia].op == PGB_OP_IMM;
+      e.fast_imm = (T)p[e.fast_rev ? ia : ib].imm;
+    }
+  }
   return "";
 }
 

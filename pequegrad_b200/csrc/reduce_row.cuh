@@ -9,6 +9,7 @@
 // Every thread keeps kBatch elements per input in flight as 128-bit loads,
 // runs the prologue over the batch, and accumulates; groups combine with
 // warp shuffles (+ shared memory across warps).
+#include <cstdlib>
 #include <type_traits>
 
 #include "reduce_common.cuh"
@@ -23,6 +24,8 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
   constexpr int U = B / V;
   ChainRegs<T> cr;
   if (MODE == 1) chain_decode<T>(p.pro, cr);
+  // MODE 3: the commonest prologue, x * a + b with two roundings, hard-wired
+  const T aff_a = p.pro.imm[0][1], aff_b = p.pro.imm[1][1];
   constexpr int GPB = 256 / G;
   // All index arithmetic is 32-bit (the host checks that the counts fit):
   // 64-bit divisions cost hundreds of instructions per thread, which a thread
@@ -94,6 +97,9 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
         if (MODE == 0) {
 #pragma unroll
           for (int e = 0; e < B; ++e) run[e] = w[0][e];
+        } else if (MODE == 3) {
+#pragma unroll
+          for (int e = 0; e < B; ++e) run[e] = w[0][e] * aff_a + aff_b;
         } else if (MODE == 1) {
           chain_eval_fast<T, NIN, B>(cr, w, run);
         } else {
@@ -114,15 +120,16 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
   for (int i = 1; i < 4; ++i) acc[0].merge(acc[i].v, acc[i].i);
   warp_combine<T, ROP>(acc[0]);
   if (G > 32) {
-    __shared__ T sv[G / 32 > 0 ? G / 32 : 1];
-    __shared__ int si[G / 32 > 0 ? G / 32 : 1];
+    constexpr int WPG = G / 32 > 0 ? G / 32 : 1;  // warps per group
+    __shared__ T sv[8];
+    __shared__ int si[8];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     if (lane == 0) { sv[warp] = acc[0].v; si[warp] = acc[0].i; }
     __syncthreads();
-    if (warp == 0) {
+    if (warp % WPG == 0) {  // the first warp of each group combines the group's warps
       Acc<T, ROP> a;
       a.init();
-      if (lane < G / 32) { a.v = sv[lane]; a.i = si[lane]; }
+      if (lane < WPG) { a.v = sv[warp + lane]; a.i = si[warp + lane]; }
       warp_combine<T, ROP>(a);
       acc[0] = a;
     }
@@ -169,7 +176,13 @@ int launch_row_typed(ReduceJob &j, bool ident, const ChainProg<float> &chain) {
 
   // work partition
   const int64_t per_row = p.R1 * p.C;
-  int G = (per_row <= 2048) ? 32 : 256;
+  // threads per row: a warp for short rows, half a CTA for medium ones (two rows per CTA
+  // halve the per-row combine cost), a whole CTA beyond
+  int G = (per_row <= 2048) ? 32 : (per_row <= 16384 ? 128 : 256);
+  if (const char *e = getenv("PGB_ROW_G")) {  // tuning aid
+    const int g = atoi(e);
+    if (g == 32 || g == 128 || g == 256) G = g;
+  }
   const int V = vec ? VFULL : 1;
   int64_t S = 1;
   p.chunk = p.C;
@@ -198,7 +211,7 @@ int launch_row_typed(ReduceJob &j, bool ident, const ChainProg<float> &chain) {
   j.ws_needed = ws;
   char buf[256];
   snprintf(buf, sizeof buf, "row in=%s nin=%d %s g=%d vec=%d split=%lld grid=%lld C=%lld R1=%lld", dtype_name(j.in[0].dtype), NIN,
-           ident ? "ident" : (chain.lite ? "chain" : "chain-full"), G, V, (long long)S, (long long)grid, (long long)p.C, (long long)p.R1);
+           ident ? "ident" : (chain.affine && NIN == 1 ? "chain-affine" : (chain.lite ? "chain" : "chain-full")), G, V, (long long)S, (long long)grid, (long long)p.C, (long long)p.R1);
   j.desc = buf;
   if (j.dry_run) return 1;
 
@@ -228,6 +241,7 @@ int launch_row_typed(ReduceJob &j, bool ident, const ChainProg<float> &chain) {
   };
   auto by_g = [&](auto rop_c, auto ident_c, auto v_c) {
     if (G == 32) go(rop_c, ident_c, v_c, std::integral_constant<int, 32>{});
+    else if (G == 128) go(rop_c, ident_c, v_c, std::integral_constant<int, 128>{});
     else go(rop_c, ident_c, v_c, std::integral_constant<int, 256>{});
   };
   auto by_v = [&](auto rop_c, auto ident_c) {
@@ -237,6 +251,7 @@ int launch_row_typed(ReduceJob &j, bool ident, const ChainProg<float> &chain) {
   auto by_ident = [&](auto rop_c) {
     if constexpr (NIN == 1) {
       if (ident) { by_v(rop_c, std::integral_constant<int, 0>{}); return; }
+      if (chain.affine) { by_v(rop_c, std::integral_constant<int, 3>{}); return; }
     }
     if (chain.lite) by_v(rop_c, std::integral_constant<int, 1>{});
     else by_v(rop_c, std::integral_constant<int, 2>{});
