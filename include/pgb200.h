@@ -182,6 +182,36 @@ PGB_API int pgb_fused_reduce_describe(const pgb_tensor *in, int n_in,
                               char *buf, size_t buf_len);
 
 /*
+ * pgb_fused_reduce for callers that cannot allocate device memory. This entry
+ * point has no counterpart in the reference (whose dispatch functions allocate
+ * freely, csrc/cuda/reduce.cu:26-30).
+ *
+ * Same arguments and results as pgb_fused_reduce, minus the workspace: the
+ * partial results of a split reduction go to a fixed array of
+ * PGB_NOALLOC_SCRATCH_BYTES that is part of the library image on every device
+ * that loads it. The call performs no cudaMalloc / cudaFree / cudaMallocAsync
+ * and calls no allocating library routine; it is meant for hosts that gave the
+ * whole device to their own arena, for serving loops that forbid allocator
+ * calls on the hot path, and for plugins that are only handed pointers.
+ *
+ *   - A reduction whose partials do not fit is refused with
+ *     PGB_ERR_WORKSPACE and a message naming both sizes; nothing is launched.
+ *   - The first call on a device that needs the scratch looks its address up
+ *     (cudaGetSymbolAddress, once per device, with that device current); make
+ *     that first call before starting any stream capture.
+ *   - Every call on a device shares the one array. It keeps the previous
+ *     call's partials, which is harmless (every partial is rewritten before it
+ *     is read), but two calls that may overlap on the GPU (different streams,
+ *     no dependency between them) race on it: order such calls.
+ */
+#define PGB_NOALLOC_SCRATCH_BYTES (4u << 20)
+PGB_API int pgb_fused_reduce_noalloc(const pgb_tensor *in, int n_in, const pgb_tensor *out,
+                     int reduce_op, const int32_t *axes, int n_axes,
+                     const pgb_instr *prologue, int n_pro,
+                     const pgb_tensor *epi_in, int n_epi_in,
+                     const pgb_instr *epilogue, int n_epi, void *stream);
+
+/*
  * Row softmax over the last axis, one kernel. Replaces the composite
  * pequegrad/ops.py:259-267 (max_reduce, sub, exp, sum, div) and the mask
  * `where(mask, s, -1e9)` of pequegrad/ops.py:807-814 when causal != 0

@@ -56,8 +56,9 @@ LIB_PATH = Path(__file__).resolve().parent / "lib" / "libpgb200.so"
 EXPORTS = [
     "pgb_status_string", "pgb_last_error", "pgb_version", "pgb_launch_count",
     "pgb_fused_elementwise", "pgb_fused_reduce", "pgb_fused_reduce_workspace", "pgb_fused_reduce_describe",
-    "pgb_softmax_rows", "pgb_layernorm_rows",
+    "pgb_softmax_rows", "pgb_layernorm_rows", "pgb_fused_reduce_noalloc",
 ]
+NOALLOC_SCRATCH_BYTES = 4 << 20  # PGB_NOALLOC_SCRATCH_BYTES
 
 _lib = None
 
@@ -84,6 +85,8 @@ def lib() -> C.CDLL:
                                    C.c_void_p, C.c_size_t, C.c_void_p]
     L.pgb_fused_reduce_workspace.argtypes = [TP, C.c_int, TP, C.c_int, C.POINTER(C.c_int32), C.c_int, C.POINTER(C.c_size_t)]
     L.pgb_fused_reduce_describe.argtypes = [TP, C.c_int, TP, C.c_int, C.POINTER(C.c_int32), C.c_int, IP, C.c_int, C.c_char_p, C.c_size_t]
+    L.pgb_fused_reduce_noalloc.argtypes = [TP, C.c_int, TP, C.c_int, C.POINTER(C.c_int32), C.c_int, IP, C.c_int, TP, C.c_int, IP, C.c_int,
+                                           C.c_void_p]
     L.pgb_softmax_rows.argtypes = [TP, TP, C.c_int, C.c_void_p]
     L.pgb_layernorm_rows.argtypes = [TP, TP, TP, C.c_float, TP, C.c_void_p]
     for name in EXPORTS:

@@ -78,6 +78,25 @@ def fused_reduce(inputs: Sequence[torch.Tensor], op: int, axes: Sequence[int], k
     return out
 
 
+def fused_reduce_noalloc(inputs: Sequence[torch.Tensor], op: int, axes: Sequence[int], out: torch.Tensor, prologue=(), epilogue=(),
+                         epi_inputs: Sequence[torch.Tensor] = ()) -> torch.Tensor:
+    """`fused_reduce` through the entry point that allocates nothing on the device: the caller
+    passes the output, split reductions use the library's built-in scratch array. For callers
+    that own all device memory themselves or may not call an allocator on their hot path."""
+    axes = list(axes)
+    ins = _arr([desc(t) for t in inputs])
+    eins = _arr([desc(t) for t in epi_inputs])
+    pro, npro = L.make_program(list(prologue))
+    epi, nepi = L.make_program(list(epilogue))
+    ax = (C.c_int32 * max(len(axes), 1))(*axes)
+    od = desc(out)
+    with torch.cuda.device(inputs[0].device):
+        st = L.lib().pgb_fused_reduce_noalloc(ins, len(inputs), C.byref(od), op, ax, len(axes), pro, npro, eins, len(epi_inputs), epi, nepi,
+                                              _stream())
+    L.check(st)
+    return out
+
+
 def reduce_workspace_bytes(x_desc_or_tensor, out_shape, op: int, axes: Sequence[int], out_dtype=torch.float32) -> int:
     d = x_desc_or_tensor if isinstance(x_desc_or_tensor, L.PgbTensor) else desc(x_desc_or_tensor)
     es = torch.empty((), dtype=out_dtype).element_size()
