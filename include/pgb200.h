@@ -231,6 +231,56 @@ PGB_API int pgb_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma,
                        const pgb_tensor *beta, float eps, const pgb_tensor *y,
                        void *stream);
 
+/*
+ * Dense matmul on the tensor cores (tcgen05 + TMEM, TMA-fed): out = act(a @ b + bias) + residual.
+ * Replaces MatMul::dispatch_cuda (csrc/cuda/matmul.cu:72-163: cuBLAS strided-batched
+ * GEMM; for half inputs the reference accumulates in fp16, here the accumulator
+ * is fp32) and FusedLinearBiasAct::dispatch_cuda (csrc/cuda/other.cu:19-166).
+ *   a         [.., M, K], f16 or bf16, K contiguous
+ *   b         [.., K, N] VIEW whose K dim is the contiguous one, i.e. the transposed
+ *             view of an [.., N, K] array (a Linear weight stored transposed once,
+ *             or k.transpose(-2,-1) in attention); a 2-D b is shared by all batches of a
+ *   bias      [N] or NULL;  act: 0 none, 1 ReLU (max(x,0), pequegrad/tensor.py:162-163),
+ *             2 GELU, tanh form (pequegrad/ops.py:109-118)
+ *   residual  same shape as out, or NULL
+ *   out       [.., M, N] f16 / bf16 / f32, N contiguous
+ * Row pitches must be multiples of 16 bytes. fp32 / fp64 / int32 operands return
+ * PGB_ERR_UNSUPPORTED ("matmul_cuda not implemented for ...").
+ */
+PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act,
+                       const pgb_tensor *residual, const pgb_tensor *out, void *stream);
+
+/*
+ * int8 quantized linear: acc = a_i8 @ w_i8^T in int32 (exact), then
+ *   out = act(float(acc) * (a_scale * w_scale[n]) + bias[n])   in fp32, in that association.
+ * The reference has no int8 type; its quantized example fake-quantizes weights in
+ * fp32 (examples/quantized_mlp.py:28-48). This is the real-int8 form of that layer.
+ *   a             [M, K] int8, K contiguous;  w  [N, K] int8 (per-output-channel quantized weight)
+ *   w_scale       device pointer to N floats
+ *   a_scale       per-tensor activation scale, used when a_absmax_dev is NULL; otherwise the
+ *                 scale is max(*a_absmax_dev, 1e-6) / 127 read on the device (no host round trip)
+ *   bias          [N] f32 or NULL;  relu != 0 applies max(x, 0)
+ *   out           [M, N] f32 / f16 / bf16, or NULL
+ *   acc_i32       [M, N] int32 raw accumulators, or NULL
+ *   out_absmax_dev  if not NULL, max |out| is folded into it with atomicMax (the caller zeroes
+ *                 it), ready to be the next layer's a_absmax_dev
+ */
+PGB_API int pgb_qlinear_i8(const pgb_tensor *a, const pgb_tensor *w, const float *w_scale, float a_scale,
+                           const float *a_absmax_dev, const pgb_tensor *bias, int relu, const pgb_tensor *out,
+                           const pgb_tensor *acc_i32, float *out_absmax_dev, void *stream);
+
+/* max |x| of a contiguous f32 tensor into *absmax_dev (zeroed by this call first). */
+PGB_API int pgb_absmax_f32(const pgb_tensor *x, float *absmax_dev, void *stream);
+
+/* q = clip(rint(x / s), -127, 127) with s = max(*absmax_dev, 1e-6) / 127, or s = scale when
+ * absmax_dev is NULL; round half to even, true fp32 division. x f32, q int8, contiguous. */
+PGB_API int pgb_quantize_i8(const pgb_tensor *x, const float *absmax_dev, float scale, const pgb_tensor *q,
+                            void *stream);
+
+/* Error word of the tensor-core kernels' bounded waits: 0 = none. Synchronises with the device.
+ * Nonzero = (role << 16) | block: 1 producer, 2 MMA issuer, 3 epilogue gave up waiting. */
+PGB_API int pgb_device_error(int *code, int reset);
+
 #ifdef __cplusplus
 }
 #endif

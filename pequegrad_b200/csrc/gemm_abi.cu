@@ -1,0 +1,223 @@
+// extern "C" entry points of the tensor-core GEMMs and of the dynamic int8
+// activation quantisation. Validation and view handling only; the kernels are
+// in gemm_sm100.cu.
+#include <string>
+
+#include "gemm.hpp"
+#include "reduce_common.cuh"
+
+namespace pgb {
+
+static bool device_present() {
+  int n = 0;
+  if (cudaGetDeviceCount(&n) != cudaSuccess || n <= 0) {
+    cudaGetLastError();
+    set_error("no CUDA device: this library has no CPU fallback");
+    return false;
+  }
+  return true;
+}
+
+// Views the dims [0, nlead) of t as one dim: count and element stride. False if they do not merge.
+static bool merge_leading(const pgb_tensor &t, int nlead, int64_t *count, int64_t *stride) {
+  const int es = dtype_size(t.dtype);
+  int64_t cnt = 1, str = 0;
+  bool have = false;
+  for (int d = nlead - 1; d >= 0; --d) {
+    if (t.shape[d] == 1) continue;
+    const int64_t s = t.stride_bytes[d] / es;
+    if (!have) { str = s; cnt = t.shape[d]; have = true; }
+    else {
+      if (s != str * cnt) return false;
+      cnt *= t.shape[d];
+    }
+  }
+  *count = cnt;
+  *stride = have ? str : 0;
+  return true;
+}
+
+// A row-major-like 2-D (+ batch) operand: rows x cols with cols contiguous.
+struct Mat {
+  const void *ptr;
+  int64_t rows, cols, ld, batch, batch_stride;
+};
+
+// Interprets t as [batch..., rows, cols] with the LAST dim contiguous.
+static std::string as_mat(const pgb_tensor &t, const char *what, Mat &m) {
+  const int es = dtype_size(t.dtype);
+  if (es == 0) return std::string("matmul: unknown dtype of ") + what;
+  if (t.ndim < 2) return std::string("matmul: ") + what + " must have at least 2 dims";
+  for (int d = 0; d < t.ndim; ++d)
+    if (t.stride_bytes[d] % es || t.stride_bytes[d] < 0) return std::string("matmul: bad stride in ") + what;
+  const int nd = t.ndim;
+  m.ptr = t.data;
+  m.rows = t.shape[nd - 2];
+  m.cols = t.shape[nd - 1];
+  if (m.cols > 1 && t.stride_bytes[nd - 1] != es) return std::string("matmul: ") + what + " must be contiguous along its contraction dim";
+  m.ld = t.stride_bytes[nd - 2] / es;
+  if (m.rows <= 1 && m.ld == 0) m.ld = m.cols;
+  if (!merge_leading(t, nd - 2, &m.batch, &m.batch_stride)) return std::string("matmul: batch dims of ") + what + " do not form one stride";
+  return "";
+}
+
+}  // namespace pgb
+
+using namespace pgb;
+
+extern "C" {
+
+PGB_API int pgb_device_error(int *code, int reset) {
+  if (!code) return PGB_ERR_INVALID_ARG;
+  return read_gemm_error(code, reset != 0);
+}
+
+PGB_API int pgb_absmax_f32(const pgb_tensor *x, float *absmax_dev, void *stream) {
+  if (!x || !absmax_dev) { set_error("absmax: null argument"); return PGB_ERR_INVALID_ARG; }
+  if (x->dtype != PGB_F32) { set_error(std::string("absmax not implemented for ") + dtype_name(x->dtype)); return PGB_ERR_UNSUPPORTED; }
+  if (!is_contiguous(*x)) { set_error("absmax: the tensor must be contiguous"); return PGB_ERR_UNSUPPORTED; }
+  if (!device_present()) return PGB_ERR_CUDA;
+  return run_absmax_f32((const float *)x->data, numel_of(*x), absmax_dev, (cudaStream_t)stream);
+}
+
+PGB_API int pgb_quantize_i8(const pgb_tensor *x, const float *absmax_dev, float scale, const pgb_tensor *q, void *stream) {
+  if (!x || !q) { set_error("quantize: null argument"); return PGB_ERR_INVALID_ARG; }
+  if (x->dtype != PGB_F32 || q->dtype != PGB_I8) { set_error("quantize: expects a float32 input and an int8 output"); return PGB_ERR_UNSUPPORTED; }
+  if (!is_contiguous(*x) || !is_contiguous(*q) || numel_of(*x) != numel_of(*q)) {
+    set_error("quantize: input and output must be contiguous and of one size");
+    return PGB_ERR_INVALID_ARG;
+  }
+  if (!absmax_dev && !(scale > 0.f)) { set_error("quantize: a positive scale or a device absmax is required"); return PGB_ERR_INVALID_ARG; }
+  if (!device_present()) return PGB_ERR_CUDA;
+  return run_quantize_i8((const float *)x->data, numel_of(*x), absmax_dev, scale, (int8_t *)q->data, (cudaStream_t)stream);
+}
+
+PGB_API int pgb_qlinear_i8(const pgb_tensor *a, const pgb_tensor *w, const float *w_scale, float a_scale, const float *a_absmax_dev,
+                           const pgb_tensor *bias, int relu, const pgb_tensor *out, const pgb_tensor *acc_i32, float *out_absmax_dev,
+                           void *stream) {
+  if (!a || !w) { set_error("qlinear: null operand"); return PGB_ERR_INVALID_ARG; }
+  if (a->dtype != PGB_I8 || w->dtype != PGB_I8) { set_error("qlinear: activations and weights must be int8"); return PGB_ERR_UNSUPPORTED; }
+  Mat A, W;
+  std::string err = as_mat(*a, "the activations", A);
+  if (err.empty()) err = as_mat(*w, "the weights", W);
+  if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
+  if (A.batch != 1 || W.batch != 1) { set_error("qlinear: activations [M,K] and weights [N,K] must be 2-D"); return PGB_ERR_INVALID_ARG; }
+  if (A.cols != W.cols) { set_error("qlinear: contraction dims differ"); return PGB_ERR_INVALID_ARG; }
+  const int64_t M = A.rows, N = W.rows, K = A.cols;
+  GemmEpilogue e{};
+  e.col_scale = w_scale;
+  e.a_scale = a_scale;
+  e.a_scale_dev = a_absmax_dev;
+  e.act = relu ? 1 : 0;
+  e.absmax = out_absmax_dev;
+  if (bias) {
+    if (numel_of(*bias) != N || !is_contiguous(*bias) || (bias->dtype != PGB_F32 && bias->dtype != PGB_F16)) {
+      set_error("qlinear: the bias must be a contiguous float32 / float16 vector of the output width");
+      return PGB_ERR_INVALID_ARG;
+    }
+    e.bias = bias->data;
+    e.bias_dtype = bias->dtype;
+  }
+  if (out) {
+    Mat O;
+    err = as_mat(*out, "the output", O);
+    if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
+    if (O.rows != M || O.cols != N || O.batch != 1) { set_error("qlinear: the output must be [M,N]"); return PGB_ERR_INVALID_ARG; }
+    if (out->dtype != PGB_F32 && out->dtype != PGB_F16 && out->dtype != PGB_BF16) {
+      set_error(std::string("qlinear output not implemented for ") + dtype_name(out->dtype));
+      return PGB_ERR_UNSUPPORTED;
+    }
+    e.out = out->data;
+    e.out_dtype = out->dtype;
+    e.ldc = O.ld;
+  }
+  if (acc_i32) {
+    Mat C;
+    err = as_mat(*acc_i32, "the accumulator output", C);
+    if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
+    if (acc_i32->dtype != PGB_I32 || C.rows != M || C.cols != N || C.batch != 1) { set_error("qlinear: the accumulator output must be int32 [M,N]"); return PGB_ERR_INVALID_ARG; }
+    e.acc_out = (int32_t *)acc_i32->data;
+    e.ld_acc = C.ld;
+  }
+  if (!out && !acc_i32) { set_error("qlinear: nothing to write"); return PGB_ERR_INVALID_ARG; }
+  if (!device_present()) return PGB_ERR_CUDA;
+  return run_gemm_tc(GEMM_I8, A.ptr, A.ld, 0, W.ptr, W.ld, 0, M, N, K, 1, e, (cudaStream_t)stream);
+}
+
+PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, const pgb_tensor *residual,
+                       const pgb_tensor *out, void *stream) {
+  if (!a || !b || !out) { set_error("matmul: null operand"); return PGB_ERR_INVALID_ARG; }
+  if (a->dtype != b->dtype) { set_error("matmul: operand dtypes differ"); return PGB_ERR_INVALID_ARG; }
+  if (a->dtype != PGB_F16 && a->dtype != PGB_BF16) {
+    // reference wording, csrc/cuda/matmul.cu:157-160
+    set_error(std::string("matmul_cuda not implemented for ") + dtype_name(a->dtype));
+    return PGB_ERR_UNSUPPORTED;
+  }
+  if (act < 0 || act > 2) { set_error("matmul: unknown activation"); return PGB_ERR_INVALID_ARG; }
+  if (b->ndim < 2) { set_error("matmul: b must have at least 2 dims"); return PGB_ERR_INVALID_ARG; }
+  // b is the [.., K, N] operand of `a @ b`; the kernel wants it K-major, i.e. as a view whose K dim is the contiguous one
+  pgb_tensor bt = *b;
+  const int nb = b->ndim;
+  bt.shape[nb - 2] = b->shape[nb - 1];
+  bt.shape[nb - 1] = b->shape[nb - 2];
+  bt.stride_bytes[nb - 2] = b->stride_bytes[nb - 1];
+  bt.stride_bytes[nb - 1] = b->stride_bytes[nb - 2];
+  Mat A, B, O;
+  std::string err = as_mat(*a, "a", A);
+  if (err.empty()) {
+    err = as_mat(bt, "b", B);
+    if (!err.empty()) err = "matmul: b must be K-major (pass the transposed view of an [N,K] array); N-major b is not built yet";
+  }
+  if (err.empty()) err = as_mat(*out, "the output", O);
+  if (!err.empty()) { set_error(err); return PGB_ERR_UNSUPPORTED; }
+  if (A.cols != B.cols) { set_error("matmul: contraction dims differ"); return PGB_ERR_INVALID_ARG; }
+  int64_t M = A.rows, batch = A.batch, a_bs = A.batch_stride, o_bs = O.batch_stride;
+  const int64_t N = B.rows, K = A.cols;
+  if (B.batch == 1 && b->ndim == 2 && A.batch > 1) {
+    // shared weight: fold a's batch into M when its rows form one pitch
+    if (A.batch_stride != A.rows * A.ld || O.batch != A.batch || O.batch_stride != O.rows * O.ld) {
+      set_error("matmul: a batched `a` with a 2-D `b` needs contiguous batches");
+      return PGB_ERR_UNSUPPORTED;
+    }
+    M = A.rows * A.batch;
+    batch = 1;
+    a_bs = 0;
+    o_bs = 0;
+  } else if (A.batch != B.batch || O.batch != A.batch) {
+    set_error("matmul: batch dims differ");
+    return PGB_ERR_INVALID_ARG;
+  }
+  if (O.rows * (batch == 1 ? O.batch : 1) != M || O.cols != N) { set_error("matmul: output shape does not match"); return PGB_ERR_INVALID_ARG; }
+  if (out->dtype != PGB_F32 && out->dtype != PGB_F16 && out->dtype != PGB_BF16) {
+    set_error(std::string("matmul output not implemented for ") + dtype_name(out->dtype));
+    return PGB_ERR_UNSUPPORTED;
+  }
+  GemmEpilogue e{};
+  e.act = act;
+  e.out = out->data;
+  e.out_dtype = out->dtype;
+  e.ldc = O.ld;
+  e.out_batch = o_bs;
+  if (bias) {
+    if (numel_of(*bias) != N || !is_contiguous(*bias) || dtype_size(bias->dtype) == 0) {
+      set_error("matmul: the bias must be a contiguous vector of the output width");
+      return PGB_ERR_INVALID_ARG;
+    }
+    e.bias = bias->data;
+    e.bias_dtype = bias->dtype;
+  }
+  if (residual) {
+    Mat R;
+    err = as_mat(*residual, "the residual", R);
+    if (!err.empty() || R.cols != N || R.rows * R.batch != O.rows * O.batch) { set_error("matmul: the residual must have the output's shape"); return PGB_ERR_INVALID_ARG; }
+    e.residual = residual->data;
+    e.res_dtype = residual->dtype;
+    e.res_ld = R.ld;
+    e.res_batch = batch == 1 ? 0 : R.batch_stride;
+  }
+  if (!device_present()) return PGB_ERR_CUDA;
+  return run_gemm_tc(a->dtype == PGB_F16 ? GEMM_F16 : GEMM_BF16, A.ptr, A.ld, a_bs, B.ptr, B.ld, B.batch_stride, M, N, K, batch, e,
+                     (cudaStream_t)stream);
+}
+
+}  // extern "C"

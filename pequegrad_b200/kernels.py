@@ -160,6 +160,72 @@ def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor | None, beta: torch.Tens
     return y
 
 
+def _ref(t):
+    if t is None:
+        return None
+    d = desc(t)
+    return C.byref(d), d  # keep the descriptor alive alongside the reference
+
+
+def matmul(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: int = 0, residual: torch.Tensor | None = None,
+           out: torch.Tensor | None = None, out_dtype=None) -> torch.Tensor:
+    """out = act(a @ b + bias) + residual on the tensor cores. `b` is the [.., K, N] operand as a
+    view whose K dim is contiguous (e.g. `w_t.T` for a weight stored as [N, K])."""
+    if out is None:
+        shape = tuple(a.shape[:-1]) + (b.shape[-1],)
+        out = torch.empty(shape, dtype=out_dtype or a.dtype, device=a.device)
+    ad, bd, od = desc(a), desc(b), desc(out)
+    bi, rs = _ref(bias), _ref(residual)
+    with torch.cuda.device(a.device):
+        st = L.lib().pgb_matmul(C.byref(ad), C.byref(bd), bi[0] if bi else None, act, rs[0] if rs else None, C.byref(od), _stream())
+    L.check(st)
+    return out
+
+
+def absmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(1, dtype=torch.float32, device=x.device)
+    xd = desc(x)
+    with torch.cuda.device(x.device):
+        st = L.lib().pgb_absmax_f32(C.byref(xd), out.data_ptr(), _stream())
+    L.check(st)
+    return out
+
+
+def quantize_i8(x: torch.Tensor, absmax_dev: torch.Tensor | None = None, scale: float = 0.0, out: torch.Tensor | None = None) -> torch.Tensor:
+    if out is None:
+        out = torch.empty(x.shape, dtype=torch.int8, device=x.device)
+    xd, qd = desc(x), desc(out)
+    with torch.cuda.device(x.device):
+        st = L.lib().pgb_quantize_i8(C.byref(xd), absmax_dev.data_ptr() if absmax_dev is not None else None, scale, C.byref(qd), _stream())
+    L.check(st)
+    return out
+
+
+def qlinear_i8(a: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, a_scale: float = 0.0, a_absmax: torch.Tensor | None = None,
+               bias: torch.Tensor | None = None, relu: bool = False, out: torch.Tensor | None = None, out_dtype=torch.float32,
+               want_acc: bool = False, out_absmax: torch.Tensor | None = None, want_out: bool = True):
+    """Returns (out, acc_i32 or None). a [M,K] int8, w [N,K] int8, w_scale [N] f32 on the device."""
+    M, N = a.shape[0], w.shape[0]
+    if out is None and want_out:
+        out = torch.empty((M, N), dtype=out_dtype, device=a.device)
+    acc = torch.empty((M, N), dtype=torch.int32, device=a.device) if want_acc else None
+    ad, wd = desc(a), desc(w)
+    bi, oo, ac = _ref(bias), _ref(out), _ref(acc)
+    with torch.cuda.device(a.device):
+        st = L.lib().pgb_qlinear_i8(C.byref(ad), C.byref(wd), w_scale.data_ptr(), a_scale, a_absmax.data_ptr() if a_absmax is not None else None,
+                                    bi[0] if bi else None, 1 if relu else 0, oo[0] if oo else None, ac[0] if ac else None,
+                                    out_absmax.data_ptr() if out_absmax is not None else None, _stream())
+    L.check(st)
+    return out, acc
+
+
+def device_error(reset: bool = True) -> int:
+    code = C.c_int(0)
+    L.check(L.lib().pgb_device_error(C.byref(code), 1 if reset else 0))
+    return code.value
+
+
 class PreparedReduce:
     """A fused reduce with its descriptors and programs built once, so that a
     call is one C-ABI invocation (what the reference's `Compiled` primitive
