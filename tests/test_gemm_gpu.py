@@ -1,0 +1,175 @@
+"""GPU parity of the tensor-core GEMMs through the C ABI.
+
+int8 quantized linear: int32 accumulators bit-exact against the oracle; the
+dequant + bias + ReLU epilogue and the dynamic activation quantiser bit-exact
+too (same fp32 operations in the same order). f16 / bf16 matmul: fp32
+accumulation, compared with an fp32 reference at 2e-2 (the bound north_star
+states for half precision)."""
+import numpy as np
+import pytest
+import torch
+
+import oracle
+from helpers import assert_close
+from pequegrad_b200 import kernels as K
+
+pytestmark = pytest.mark.gpu
+
+
+def cu(a):
+    return torch.from_numpy(np.ascontiguousarray(a)).cuda()
+
+
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 128), (200, 10, 1024), (513, 1024, 784), (1024, 1024, 1024), (1, 16, 16), (130, 257, 48)])
+def test_int8_accumulators_bit_exact(M, N, K_):
+    rng = np.random.default_rng(41)
+    a = rng.integers(-127, 128, (M, K_)).astype(np.int8)
+    w = rng.integers(-127, 128, (N, K_)).astype(np.int8)
+    ws = (rng.random(N) * 0.01 + 1e-3).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    want_acc = oracle.gemm_i8(a, w)
+    for relu in (False, True):
+        out, acc = K.qlinear_i8(cu(a), cu(w), cu(ws), a_scale=0.0123, bias=cu(b), relu=relu, want_acc=True)
+        assert K.device_error() == 0
+        assert np.array_equal(acc.cpu().numpy(), want_acc)
+        want = oracle.dequant_bias_act(want_acc, ws, np.float32(0.0123), b, relu)
+        assert np.array_equal(out.cpu().numpy(), want)  # same fp32 ops, same order
+    out16, _ = K.qlinear_i8(cu(a), cu(w), cu(ws), a_scale=0.0123, bias=cu(b), relu=True, out_dtype=torch.float16)
+    assert np.array_equal(out16.cpu().numpy(), want.astype(np.float16))
+    _, acc = K.qlinear_i8(cu(a), cu(w), cu(ws), a_scale=1.0, want_acc=True, want_out=False)
+    assert np.array_equal(acc.cpu().numpy(), want_acc)
+
+
+def test_dynamic_activation_quantiser_bit_exact():
+    rng = np.random.default_rng(42)
+    for shape in [(7, 13), (1000, 784), (33, 4099)]:
+        x = (rng.standard_normal(shape) * 3).astype(np.float32)
+        am = K.absmax(cu(x))
+        assert float(am.cpu()) == oracle.absmax(x)
+        q = K.quantize_i8(cu(x), absmax_dev=am)
+        s = oracle.quant_scale(oracle.absmax(x))
+        assert np.array_equal(q.cpu().numpy(), oracle.quantize_i8(x, s))
+        q2 = K.quantize_i8(cu(x), scale=float(s))
+        assert np.array_equal(q2.cpu().numpy(), oracle.quantize_i8(x, s))
+    z = np.zeros((5, 5), np.float32)  # the 1e-6 floor of examples/quantized_mlp.py:30
+    assert (K.quantize_i8(cu(z), absmax_dev=K.absmax(cu(z))).cpu().numpy() == 0).all()
+
+
+def _mlp_oracle(X, Ws, bs):
+    """784 -> 1024 -> 1024 -> 10 with ReLU, per-channel int8 weights, dynamic per-tensor int8 activations."""
+    h, per_layer = X, []
+    for i, (W, b) in enumerate(zip(Ws, bs)):
+        wq, wsc = oracle.quantize_weight_per_channel(W)
+        sx = oracle.quant_scale(oracle.absmax(h))
+        xq = oracle.quantize_i8(h, sx)
+        acc = oracle.gemm_i8(xq, wq)
+        h = oracle.dequant_bias_act(acc, wsc, sx, b, relu=i < len(Ws) - 1)
+        per_layer.append((xq, wq, wsc, sx, acc, h))
+    return per_layer
+
+
+def test_quantized_mlp_layers_and_pipeline():
+    rng = np.random.default_rng(3)
+    dims = [784, 1024, 1024, 10]
+    Ws = [(rng.standard_normal((dims[i], dims[i + 1])) * 0.05).astype(np.float32) for i in range(3)]
+    bs = [(rng.standard_normal(dims[i + 1]) * 0.05).astype(np.float32) for i in range(3)]
+    X = rng.random((2048, 784), dtype=np.float32)
+    layers = _mlp_oracle(X, Ws, bs)
+    # (1) per layer: the oracle's int8 inputs through the GPU GEMM -> bit-exact accumulators and outputs
+    for i, (xq, wq, wsc, sx, acc, h) in enumerate(layers):
+        out, gacc = K.qlinear_i8(cu(xq), cu(wq), cu(wsc), a_scale=float(sx), bias=cu(bs[i]), relu=i < 2, want_acc=True)
+        assert np.array_equal(gacc.cpu().numpy(), acc), f"layer {i} accumulators"
+        assert np.array_equal(out.cpu().numpy(), h), f"layer {i} outputs"
+    # (2) whole pipeline on the device, scales never leave the GPU
+    hd = cu(X)
+    am = K.absmax(hd)
+    for i in range(3):
+        wq, wsc = layers[i][1], layers[i][2]
+        xq = K.quantize_i8(hd, absmax_dev=am)
+        assert np.array_equal(xq.cpu().numpy(), layers[i][0]), f"layer {i} quantised activations"
+        nxt = torch.zeros(1, device="cuda")
+        hd, _ = K.qlinear_i8(xq, cu(wq), cu(wsc), a_absmax=am, bias=cu(bs[i]), relu=i < 2, out_absmax=nxt)
+        am = nxt
+    assert K.device_error() == 0
+    assert_close(hd.cpu().numpy(), layers[2][5], 1e-5)
+    # and the quantised network tracks the fp32 one
+    ref = X
+    for i in range(3):
+        ref = ref @ Ws[i] + bs[i]
+        if i < 2:
+            ref = np.maximum(ref, 0)
+    assert np.abs(hd.cpu().numpy() - ref).mean() < 0.05 * np.abs(ref).mean()
+
+
+def test_reference_fake_quant_numerics_through_the_fused_kernels():
+    # examples/quantized_mlp.py:28-34 expanded to primitives: abs = (x**2)**0.5, round = trunc(x + 0.5),
+    # clip = where chains; everything fp32, per tensor. Run as fused reduce + fused elementwise kernels.
+    from pequegrad_b200 import _lib as L
+    rng = np.random.default_rng(9)
+    w = (rng.standard_normal((784, 1024)) * 0.05).astype(np.float32)
+    wd = cu(w)
+    absprog = [("LOAD", 0), ("IMM", 0, 0, 0, 2.0), ("POW", 0, 1), ("IMM", 0, 0, 0, 0.5), ("POW", 2, 3)]
+    wmax = K.fused_reduce([wd], L.MAX, [0, 1], True, absprog, [("ACC",), ("IMM", 0, 0, 0, 1e-6), ("MAX", 0, 1)])
+    scale = wmax.expand(784, 1024)
+    q = [("LOAD", 0), ("LOAD", 1), ("DIV", 0, 1), ("IMM", 0, 0, 0, 127.0), ("MUL", 2, 3), ("IMM", 0, 0, 0, 0.5), ("ADD", 4, 5), ("CAST_I32", 6),
+         ("IMM", 0, 0, 0, -128.0), ("IMM", 0, 0, 0, 127.0), ("GT", 7, 9), ("WHERE", 10, 9, 7), ("LT", 7, 8), ("WHERE", 12, 8, 11),
+         ("DIV", 13, 3), ("MUL", 14, 1)]
+    (wq,) = K.fused_elementwise([wd, scale], q)
+    ws = np.float32(max(np.sqrt(np.float32(w) ** 2).max(), 1e-6))
+    r = (w / ws * np.float32(127) + np.float32(0.5)).astype(np.int32).astype(np.float32)
+    want = np.clip(r, -128, 127) / np.float32(127) * ws
+    assert_close(float(wmax.cpu()), float(ws), 1e-6)
+    got = wq.cpu().numpy()
+    assert_close(got, want, 1e-5, 1e-6)
+    # trunc(x + 0.5) rounds negatives toward zero-ish (-1.7 -> -1): up to one and a half steps off
+    assert np.abs(got - w).max() <= ws / 127 * 1.51
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("M,N,K_", [(128, 128, 64), (300, 200, 520), (1024, 768, 768), (77, 50264, 64)])
+def test_half_matmul_fp32_accumulate(M, N, K_, dt):
+    g = torch.Generator(device="cuda").manual_seed(5)
+    a = (torch.randn((M, K_), generator=g, device="cuda") * 0.5).to(dt)
+    wt = (torch.randn((N, K_), generator=g, device="cuda") * 0.5).to(dt)
+    out = K.matmul(a, wt.T, out_dtype=torch.float32)
+    assert K.device_error() == 0
+    ref = a.float() @ wt.float().T
+    assert_close(out.cpu().numpy(), ref.cpu().numpy(), 1e-4, 1e-4 * float(ref.abs().max()))  # fp32 accumulation: far inside 2e-2
+    out_h = K.matmul(a, wt.T)
+    assert out_h.dtype == dt
+    assert_close(out_h.float().cpu().numpy(), ref.cpu().numpy(), 2e-2, 2e-2 * float(ref.abs().max()))
+
+
+def test_linear_epilogues_and_batched_attention_shapes():
+    g = torch.Generator(device="cuda").manual_seed(6)
+    x = (torch.randn((4, 96, 768), generator=g, device="cuda") * 0.5).half()
+    wt = (torch.randn((3072, 768), generator=g, device="cuda") * 0.02).half()
+    b = (torch.randn(3072, generator=g, device="cuda") * 0.02).half()
+    y = K.matmul(x, wt.T, bias=b, act=2)  # Linear + GELU(tanh), batch folded into M
+    z = (x.float() @ wt.float().T + b.float())
+    ref = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    assert_close(y.float().cpu().numpy(), ref.cpu().numpy(), 2e-2, 2e-3)
+    wt2 = (torch.randn((768, 3072), generator=g, device="cuda") * 0.02).half()
+    res = (torch.randn((4, 96, 768), generator=g, device="cuda")).half()
+    y2 = K.matmul(y, wt2.T, residual=res)  # projection + residual add
+    ref2 = y.float() @ wt2.float().T + res.float()
+    assert_close(y2.float().cpu().numpy(), ref2.cpu().numpy(), 2e-2, 2e-3)
+    y3 = K.matmul(x, wt.T, act=1, out_dtype=torch.float32)
+    assert_close(y3.cpu().numpy(), torch.relu(x.float() @ wt.float().T).cpu().numpy(), 1e-4, 1e-4)
+    # scores = q @ k^T per (batch, head): both operands batched, k^T is a transposed view
+    q = (torch.randn((2, 12, 256, 64), generator=g, device="cuda")).half()
+    k = (torch.randn((2, 12, 256, 64), generator=g, device="cuda")).half()
+    s = K.matmul(q, k.transpose(-2, -1), out_dtype=torch.float32)
+    assert_close(s.cpu().numpy(), (q.float() @ k.float().transpose(-2, -1)).cpu().numpy(), 1e-4, 1e-3)
+    assert K.device_error() == 0
+
+
+def test_matmul_errors_follow_the_reference():
+    a = torch.zeros((8, 16), device="cuda")
+    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float32"):
+        K.matmul(a, a.T)
+    h = torch.zeros((16, 16), device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="K-major"):
+        K.matmul(h, h)  # [K, N] with N contiguous: not built yet
+    with pytest.raises(ValueError):
+        K.matmul(h, torch.zeros((24, 8), device="cuda", dtype=torch.float16).T)
