@@ -1,0 +1,147 @@
+// Epilogue role of the tcgen05 GEMM: one warp drains 32 TMEM lanes (32 rows of
+// the tile) of each finished accumulator, applies the fused epilogue and stores.
+// The epilogue's shape (activation, bias, residual) is a template parameter, chosen
+// once per kernel, so the per-element code has no branches and no dead code in it.
+#pragma once
+#include "gemm_kernel.cuh"
+
+namespace pgb {
+
+template <int KIND, int BN, int ACT, bool BIAS, bool RES>
+__device__ __noinline__ void gemm_epilogue_tiles(const GemmParams &p, uint32_t tmem_base, uint32_t *stage, uint64_t *acc_full,
+                                                 uint64_t *acc_empty, volatile int *abort_flag, int q, int lane, int num_tiles,
+                                                 int tiles_per_batch) {
+  const GemmEpilogue &e = p.epi;
+  float a_scale = e.a_scale;
+  if (KIND == GEMM_I8 && e.a_scale_dev) {
+    // activation scale from the running absmax: max(amax, 1e-6) / 127, same fp32 ops as the host formula
+    a_scale = fmaxf(__ldg(e.a_scale_dev), 1e-6f) / 127.0f;
+  }
+  float local_max = 0.f;
+  const int out_es = e.out_dtype == PGB_F32 ? 4 : 2;
+  // vector stores need 16-byte aligned rows
+  const bool out_vec = e.out && ((reinterpret_cast<uintptr_t>(e.out) & 15) == 0) && ((e.ldc * out_es) % 16 == 0) &&
+                       ((e.out_batch * out_es) % 16 == 0);
+  const bool acc_vec = e.acc_out && ((reinterpret_cast<uintptr_t>(e.acc_out) & 15) == 0) && ((e.ld_acc & 3) == 0);
+  const bool want_max = e.absmax != nullptr;
+  const bool has_scale = e.col_scale != nullptr;
+  const int out_dtype = e.out_dtype;
+  int it = 0;
+  for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
+    const int m0 = (rem / p.tiles_n) * kBM, n0 = (rem % p.tiles_n) * BN;
+    const int buf = it & 1;
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) {
+      if (lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_error, 0, (3 << 16) | (blockIdx.x & 0xffff)); }
+      break;
+    }
+    tc_fence_after();
+    const int row0 = m0 + q * 32;
+    const int row = row0 + lane;
+    for (int c0 = 0; c0 < BN; c0 += 32) {
+      if (n0 + c0 >= p.N) break;  // warp-uniform: nothing of this tile is left
+      uint32_t v[32];
+      tmem_ld32(tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN + c0), v);  // all lanes: sync.aligned
+      const bool full_chunk = n0 + c0 + 32 <= p.N;
+      if (e.acc_out) {
+        int32_t *dst = e.acc_out + (int64_t)row0 * e.ld_acc + n0 + c0;
+        if (full_chunk && acc_vec) stage_and_store<32>(stage, v, (uint8_t *)dst, e.ld_acc * 4, row0, p.M, lane);
+        else store_tail<4>(v, (uint8_t *)dst, e.ld_acc * 4, lane, row < p.M ? min(32, p.N - n0 - c0) : 0);
+      }
+      if (!e.out && !want_max) continue;
+      // Per-column operands: lane l fetches column c0 + l once (coalesced, both loads in flight
+      // together) and the values are handed round with shuffles. Loading them inside the element
+      // loop instead costs one L2 round trip per element (the L1 is all but gone with a
+      // 200 KB shared-memory carve-out).
+      const int col_l = n0 + c0 + lane;
+      const bool ok_l = col_l < p.N;
+      float sc_l = a_scale, bi_l = 0.f;
+      if (KIND == GEMM_I8 && has_scale) sc_l = __fmul_rn(a_scale, ok_l ? __ldg(e.col_scale + col_l) : 0.f);
+      if (BIAS) bi_l = (ok_l && e.bias) ? load_as<float>(e.bias, e.bias_dtype, col_l) : 0.f;
+      float res[RES ? 32 : 1];
+      if (RES) {
+        // the residual is this thread's own row segment: 32 consecutive elements
+        const int64_t roff = (int64_t)bz * e.res_batch + (int64_t)row * e.res_ld + n0 + c0;
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          res[RES ? i : 0] = (row < p.M && (full_chunk || n0 + c0 + i < p.N)) ? load_as<float>(e.residual, e.res_dtype, roff + i) : 0.f;
+      }
+      uint32_t f[32];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) {
+        float x;
+        if (KIND == GEMM_I8) x = __fmul_rn((float)(int)v[i], __shfl_sync(0xffffffffu, sc_l, i));
+        else x = __uint_as_float(v[i]);
+        if (BIAS) x = __fadd_rn(x, __shfl_sync(0xffffffffu, bi_l, i));
+        if (ACT == ACT_RELU) x = x > 0.f ? x : 0.f;
+        if (ACT == ACT_GELU_TANH) x = gelu_tanh(x);
+        if (RES) x = __fadd_rn(x, res[RES ? i : 0]);
+        f[i] = __float_as_uint(x);
+      }
+      if (want_max && row < p.M) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i)
+          if (full_chunk || n0 + c0 + i < p.N) local_max = fmaxf(local_max, fabsf(__uint_as_float(f[i])));
+      }
+      if (!e.out) continue;
+      const int64_t off0 = (int64_t)bz * e.out_batch + (int64_t)row0 * e.ldc + n0 + c0;
+      if (out_dtype == PGB_F32) {
+        float *dst = (float *)e.out + off0;
+        if (full_chunk && out_vec) stage_and_store<32>(stage, f, (uint8_t *)dst, e.ldc * 4, row0, p.M, lane);
+        else store_tail<4>(f, (uint8_t *)dst, e.ldc * 4, lane, row < p.M ? min(32, p.N - n0 - c0) : 0);
+      } else {
+        const bool is_h = out_dtype == PGB_F16;
+        uint32_t h[32];
+#pragma unroll
+        for (int i = 0; i < 16; ++i) {
+          const float lo = __uint_as_float(f[2 * i]), hi = __uint_as_float(f[2 * i + 1]);
+          const uint16_t l16 = is_h ? __half_as_ushort(__float2half_rn(lo)) : __bfloat16_as_ushort(__float2bfloat16_rn(lo));
+          const uint16_t h16 = is_h ? __half_as_ushort(__float2half_rn(hi)) : __bfloat16_as_ushort(__float2bfloat16_rn(hi));
+          h[i] = (uint32_t)l16 | ((uint32_t)h16 << 16);
+        }
+#pragma unroll
+        for (int i = 16; i < 32; ++i) h[i] = 0;
+        uint16_t *dst = (uint16_t *)e.out + off0;
+        if (full_chunk && out_vec) stage_and_store<16>(stage, h, (uint8_t *)dst, e.ldc * 2, row0, p.M, lane);
+        else store_tail<2>(h, (uint8_t *)dst, e.ldc * 2, lane, row < p.M ? min(32, p.N - n0 - c0) : 0);
+      }
+    }
+    // this warp is done reading the accumulator: hand the buffer back to the MMA warp
+    tc_fence_before();
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&acc_empty[buf]);
+  }
+  if (want_max) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, m));
+    // non-negative floats order like their bit patterns
+    if (lane == 0 && local_max > 0.f) atomicMax(reinterpret_cast<unsigned int *>(e.absmax), __float_as_uint(local_max));
+  }
+}
+
+// Chooses the specialisation once per kernel.
+template <int KIND, int BN>
+__device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, uint32_t tmem_base, uint32_t *stage, uint64_t *acc_full,
+                                                   uint64_t *acc_empty, volatile int *abort_flag, int q, int lane, int num_tiles,
+                                                   int tiles_per_batch) {
+#define PGB_EPI(ACT, BIAS, RES) \
+  gemm_epilogue_tiles<KIND, BN, ACT, BIAS, RES>(p, tmem_base, stage, acc_full, acc_empty, abort_flag, q, lane, num_tiles, tiles_per_batch)
+  const bool bias = p.epi.bias != nullptr, res = p.epi.residual != nullptr;
+  const int act = p.epi.act;
+  if (KIND == GEMM_I8) {
+    if (act == ACT_RELU) { if (bias) PGB_EPI(ACT_RELU, true, false); else PGB_EPI(ACT_RELU, false, false); }
+    else { if (bias) PGB_EPI(ACT_NONE, true, false); else PGB_EPI(ACT_NONE, false, false); }
+  } else {
+    if (act == ACT_GELU_TANH) { if (res) PGB_EPI(ACT_GELU_TANH, true, true); else PGB_EPI(ACT_GELU_TANH, true, false); }
+    else if (act == ACT_RELU) { if (res) PGB_EPI(ACT_RELU, true, true); else PGB_EPI(ACT_RELU, true, false); }
+    else if (res) { PGB_EPI(ACT_NONE, true, true); }
+    else if (bias) { PGB_EPI(ACT_NONE, true, false); }
+    else { PGB_EPI(ACT_NONE, false, false); }
+  }
+#undef PGB_EPI
+}
+
+}  // namespace pgb

@@ -1,0 +1,79 @@
+// Dynamic per-tensor int8 quantisation of activations (absmax, then quantise).
+// The reference has no int8 type; its example scales by max|.| floored at 1e-6
+// (examples/quantized_mlp.py:28-34), which these kernels keep.
+#include "gemm.hpp"
+#include "reduce_common.cuh"
+
+namespace pgb {
+
+// absmax: one pass, atomicMax on the bit pattern. quantize: q = clip(rint(x / s), -127, 127),
+// s = max(absmax, 1e-6) / 127, true fp32 division, round half to even.
+__global__ void __launch_bounds__(256) absmax_f32_kernel(const float *__restrict__ x, int64_t n, float *out) {
+  float m = 0.f;
+  const int64_t stride = (int64_t)gridDim.x * 256 * 4;
+  for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 4; i < n; i += stride) {
+    if (i + 3 < n) {
+      const float4 v = __ldcs(reinterpret_cast<const float4 *>(x + i));
+      m = fmaxf(m, fmaxf(fmaxf(fabsf(v.x), fabsf(v.y)), fmaxf(fabsf(v.z), fabsf(v.w))));
+    } else {
+      for (int64_t j = i; j < n; ++j) m = fmaxf(m, fabsf(x[j]));
+    }
+  }
+#pragma unroll
+  for (int k = 16; k > 0; k >>= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, k));
+  if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int *>(out), __float_as_uint(m));
+}
+
+__global__ void __launch_bounds__(256) quantize_i8_kernel(const float *__restrict__ x, int64_t n, const float *__restrict__ absmax,
+                                                          float scale_host, int8_t *__restrict__ q) {
+  const float s = absmax ? fmaxf(__ldg(absmax), 1e-6f) / 127.0f : scale_host;
+  const int64_t stride = (int64_t)gridDim.x * 256 * 16;
+  for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 16; i < n; i += stride) {
+    if (i + 15 < n) {
+      uint32_t w[4];
+#pragma unroll
+      for (int g = 0; g < 4; ++g) {
+        const float4 v = __ldcs(reinterpret_cast<const float4 *>(x + i + 4 * g));
+        const float f[4] = {v.x, v.y, v.z, v.w};
+        uint32_t pk = 0;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) {
+          float r = rintf(__fdiv_rn(f[e], s));
+          r = fminf(fmaxf(r, -127.f), 127.f);
+          pk |= ((uint32_t)(uint8_t)(int8_t)(int)r) << (8 * e);
+        }
+        w[g] = pk;
+      }
+      *reinterpret_cast<uint4 *>(q + i) = make_uint4(w[0], w[1], w[2], w[3]);
+    } else {
+      for (int64_t j = i; j < n; ++j) {
+        float r = rintf(__fdiv_rn(x[j], s));
+        r = fminf(fmaxf(r, -127.f), 127.f);
+        q[j] = (int8_t)(int)r;
+      }
+    }
+  }
+}
+
+int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream) {
+  if (cudaMemsetAsync(out, 0, sizeof(float), stream) != cudaSuccess) { set_error("absmax: memset failed"); return PGB_ERR_CUDA; }
+  if (n <= 0) return PGB_OK;
+  int64_t grid = (n + 1023) / 1024;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (grid > cap) grid = cap;
+  absmax_f32_kernel<<<(unsigned)grid, 256, 0, stream>>>(x, n, out);
+  count_launch();
+  return check_launch("absmax_f32_kernel");
+}
+
+int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float scale, int8_t *q, cudaStream_t stream) {
+  if (n <= 0) return PGB_OK;
+  int64_t grid = (n + 4095) / 4096;
+  const int64_t cap = (int64_t)sm_count() * 16;
+  if (grid > cap) grid = cap;
+  quantize_i8_kernel<<<(unsigned)grid, 256, 0, stream>>>(x, n, absmax_dev, scale, q);
+  count_launch();
+  return check_launch("quantize_i8_kernel");
+}
+
+}  // namespace pgb
