@@ -8,10 +8,12 @@ namespace pgb {
 constexpr int kBM = 128;
 constexpr int kSlabBytes = 128;  // bytes of K per stage = one 128B swizzle atom row
 constexpr int kTileABytes = kBM * kSlabBytes;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;  // two per TMEM lane group, each takes half of the tile's columns
+constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kStagePitch = 36;  // words per staged row: 32 + 4 keeps 128-bit accesses conflict-free
-constexpr int kEpiStageBytes = 4 * 32 * kStagePitch * 4;
-constexpr int kSmemBudget = 200 * 1024;  // for the operand ring
+constexpr int kEpiStageBytes = kEpiWarps * 32 * kStagePitch * 4;
+constexpr int kColStashBytes = kEpiWarps * 2 * 256 * 4;  // per epilogue warp: scale and bias of the tile's columns
+constexpr int kSmemBudget = 150 * 1024;  // for the operand ring
 
 template <int BN>
 struct TileCfg {
@@ -19,7 +21,7 @@ struct TileCfg {
   static constexpr int kStageBytes = kTileABytes + kTileBBytes;
   static constexpr int kStages = (kSmemBudget / kStageBytes) > 8 ? 8 : (kSmemBudget / kStageBytes);
   static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;  // two accumulators; a power of two >= 32
-  static constexpr int kSmem = kStages * kStageBytes + kEpiStageBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  static constexpr int kSmem = kStages * kStageBytes + kEpiStageBytes + kColStashBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
 static __device__ int g_gemm_error;  // 0 = ok; else (role << 16) | block index bits

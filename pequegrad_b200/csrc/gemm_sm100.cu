@@ -15,7 +15,7 @@
 // loops over 128 x BN tiles of C:
 //   warp 0     TMA producer: 128-byte-wide K slabs of A and B per stage, 128B swizzle
 //   warp 1     allocates TMEM, issues tcgen05.mma (one thread), commits to mbarriers
-//   warps 2-5  epilogue: tcgen05.ld the accumulator (one row per thread), apply the
+//   warps 2-9  epilogue: tcgen05.ld the accumulator (one row per thread), apply the
 //              fused epilogue, transpose through shared memory, coalesced 128-bit stores
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue
 // of tile i overlaps the MMAs of tile i+1.
@@ -44,7 +44,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   uint8_t *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   uint8_t *tiles = smem;
   uint32_t *epi_stage = reinterpret_cast<uint32_t *>(smem + STAGES * Cfg::kStageBytes);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::kStageBytes + kEpiStageBytes);
+  float *col_stash = reinterpret_cast<float *>(smem + STAGES * Cfg::kStageBytes + kEpiStageBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::kStageBytes + kEpiStageBytes + kColStashBytes);
   uint64_t *full = bars;                   // [STAGES]  TMA -> MMA
   uint64_t *empty = bars + STAGES;         // [STAGES]  MMA -> TMA
   uint64_t *acc_full = bars + 2 * STAGES;  // [2]       MMA -> epilogue
@@ -60,7 +61,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
 
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
-    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], 4); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kEpiWarps); }
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -132,7 +133,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
     }
   } else {
     const int q = warp & 3;  // a warp may read TMEM lanes 32*(warp%4) .. +31
-    gemm_epilogue_warp<KIND, BN>(p, tmem_base, epi_stage + q * 32 * kStagePitch, acc_full, acc_empty, abort_flag, q, lane, num_tiles,
+    const int ew = warp - 2;  // 0..7; warps ew and ew+4 share a lane group and split the columns
+    gemm_epilogue_warp<KIND, BN>(p, tmem_base, epi_stage + ew * 32 * kStagePitch, col_stash + ew * 512, ew >> 2, acc_full, acc_empty, abort_flag, q, lane, num_tiles,
                                  tiles_per_batch);
   }
   tc_fence_before();
