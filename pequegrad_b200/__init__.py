@@ -2,7 +2,8 @@
 
 Only what that path needs lives here: the CUDA sources and C ABI (`csrc/`,
 `include/pgb200.h`), the ctypes binding (`_lib`), torch-pointer wrappers
-(`kernels`), and a host-side mirror of the reference's operator interface.
+(`kernels`), and a host-side mirror of the reference's operator interface
+(`tensor`, `fuser`, `distrib`): lazy tensors, `jit`, `shard_tensor` / `pmap`.
 """
 from . import _lib  # noqa: F401
 
