@@ -232,14 +232,25 @@ PGB_API int pgb_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma,
                        void *stream);
 
 /*
- * Dense matmul on the tensor cores (tcgen05 + TMEM, TMA-fed): out = act(a @ b + bias) + residual.
+ * Token + position embedding: out[r, :] = wte[ids[r], :] + wpe[r % T, :]  (wpe may be NULL).
+ * Replaces the index-tensor Select gather and the add of pequegrad/modules.py:329-337 and
+ * examples/gpt2.py:365-372. ids int32 [rows], tables [V, C] / [>= T, C] f16 / bf16 / f32 contiguous.
+ */
+PGB_API int pgb_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, const pgb_tensor *wpe, int64_t T,
+                               const pgb_tensor *out, void *stream);
+
+/*
+ * Dense matmul on the tensor cores (tcgen05 + TMEM, TMA-fed): out = act(alpha * (a @ b) + bias) + residual.
  * Replaces MatMul::dispatch_cuda (csrc/cuda/matmul.cu:72-163: cuBLAS strided-batched
  * GEMM; for half inputs the reference accumulates in fp16, here the accumulator
  * is fp32) and FusedLinearBiasAct::dispatch_cuda (csrc/cuda/other.cu:19-166).
  *   a         [.., M, K], f16 or bf16, K contiguous
  *   b         [.., K, N] VIEW whose K dim is the contiguous one, i.e. the transposed
  *             view of an [.., N, K] array (a Linear weight stored transposed once,
- *             or k.transpose(-2,-1) in attention); a 2-D b is shared by all batches of a
+ *             or k.transpose(-2,-1) in attention); a 2-D b is shared by all batches of a;
+ *             otherwise the leading dims must reduce to at most two strided batch dims
+ *   alpha     scale of the product (1 for a plain matmul; 1/sqrt(d) for attention scores,
+ *             pequegrad/ops.py:792-818 divides after the matmul)
  *   bias      [N] or NULL;  act: 0 none, 1 ReLU (max(x,0), pequegrad/tensor.py:162-163),
  *             2 GELU, tanh form (pequegrad/ops.py:109-118)
  *   residual  same shape as out, or NULL
@@ -247,7 +258,7 @@ PGB_API int pgb_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma,
  * Row pitches must be multiples of 16 bytes. fp32 / fp64 / int32 operands return
  * PGB_ERR_UNSUPPORTED ("matmul_cuda not implemented for ...").
  */
-PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act,
+PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, float alpha,
                        const pgb_tensor *residual, const pgb_tensor *out, void *stream);
 
 /*

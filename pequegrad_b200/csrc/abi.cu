@@ -54,6 +54,9 @@ int run_softmax_rows(const pgb_tensor *x, const pgb_tensor *y, int causal, cudaS
 int run_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma, const pgb_tensor *beta, float eps, const pgb_tensor *y,
                        cudaStream_t stream);
 
+int run_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, const pgb_tensor *wpe, int64_t T, const pgb_tensor *out,
+                       cudaStream_t stream);
+
 static int build_reduce_job(ReduceJob &j, const pgb_tensor *in, int n_in, const pgb_tensor *out, int reduce_op, const int32_t *axes,
                             int n_axes, const pgb_instr *prologue, int n_pro, const pgb_tensor *epi_in, int n_epi_in,
                             const pgb_instr *epilogue, int n_epi) {
@@ -203,6 +206,12 @@ int pgb_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma, const pgb_t
   g_last_error.clear();
   if (!device_ok()) return PGB_ERR_CUDA;
   return run_layernorm_rows(x, gamma, beta, eps, y, (cudaStream_t)stream);
+}
+
+int pgb_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, const pgb_tensor *wpe, int64_t T, const pgb_tensor *out, void *stream) {
+  g_last_error.clear();
+  if (!device_ok()) return PGB_ERR_CUDA;
+  return run_embedding_rows(ids, wte, wpe, T, out, (cudaStream_t)stream);
 }
 
 }  // extern "C"

@@ -15,23 +15,25 @@ struct GemmEpilogue {
   const float *col_scale;    // [N] or null
   const float *a_scale_dev;  // device scalar holding max|activation|; if null a_scale is used
   float a_scale;
+  float alpha;  // f16 / bf16: v = acc * alpha (1 = off), e.g. the 1/sqrt(d) of attention scores
   const void *bias;  // [N], dtype bias_dtype, or null
   int bias_dtype;
   int act;
   const void *residual;  // laid out like the output, or null
   int res_dtype;
-  int64_t res_ld, res_batch;
+  int64_t res_ld, res_batch, res_batch0;  // row pitch, inner and outer batch strides (elements)
   void *out;      // or null
   int out_dtype;  // f32 / f16 / bf16
-  int64_t ldc, out_batch;
+  int64_t ldc, out_batch, out_batch0;
   int32_t *acc_out;  // raw int32 accumulators (i8 only), or null
   int64_t ld_acc;
   float *absmax;  // running max |v| over the whole output (atomicMax on the bit pattern), or null
 };
 
-// a: [batch, M, K], b: [batch, N, K], both K contiguous; strides in elements.
-int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_batch, const void *b, int64_t ldb, int64_t b_batch, int64_t M, int64_t N,
-                int64_t K, int64_t batch, const GemmEpilogue &epi, cudaStream_t stream);
+// a: [nb0, nb1, M, K], b: [nb0, nb1, N, K], both K contiguous; all strides in elements
+// (bs0 / bs1 = strides of the outer / inner batch dim).
+int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_bs1, const void *b, int64_t ldb, int64_t b_bs0, int64_t b_bs1,
+                int64_t M, int64_t N, int64_t K, int64_t nb0, int64_t nb1, const GemmEpilogue &epi, cudaStream_t stream);
 int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream);
 int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float scale, int8_t *q, cudaStream_t stream);
 int read_gemm_error(int *out, bool reset);

@@ -18,12 +18,12 @@ static bool device_present() {
   return true;
 }
 
-// Views the dims [0, nlead) of t as one dim: count and element stride. False if they do not merge.
-static bool merge_leading(const pgb_tensor &t, int nlead, int64_t *count, int64_t *stride) {
+// Views the dims [lo, hi) of t as one dim: count and element stride. False if they do not merge.
+static bool merge_dims(const pgb_tensor &t, int lo, int hi, int64_t *count, int64_t *stride) {
   const int es = dtype_size(t.dtype);
   int64_t cnt = 1, str = 0;
   bool have = false;
-  for (int d = nlead - 1; d >= 0; --d) {
+  for (int d = hi - 1; d >= lo; --d) {
     if (t.shape[d] == 1) continue;
     const int64_t s = t.stride_bytes[d] / es;
     if (!have) { str = s; cnt = t.shape[d]; have = true; }
@@ -36,6 +36,7 @@ static bool merge_leading(const pgb_tensor &t, int nlead, int64_t *count, int64_
   *stride = have ? str : 0;
   return true;
 }
+static bool merge_leading(const pgb_tensor &t, int nlead, int64_t *count, int64_t *stride) { return merge_dims(t, 0, nlead, count, stride); }
 
 // A row-major-like 2-D (+ batch) operand: rows x cols with cols contiguous.
 struct Mat {
@@ -44,7 +45,7 @@ struct Mat {
 };
 
 // Interprets t as [batch..., rows, cols] with the LAST dim contiguous.
-static std::string as_mat(const pgb_tensor &t, const char *what, Mat &m) {
+static std::string as_mat(const pgb_tensor &t, const char *what, Mat &m, bool need_one_batch = true) {
   const int es = dtype_size(t.dtype);
   if (es == 0) return std::string("matmul: unknown dtype of ") + what;
   if (t.ndim < 2) return std::string("matmul: ") + what + " must have at least 2 dims";
@@ -57,7 +58,10 @@ static std::string as_mat(const pgb_tensor &t, const char *what, Mat &m) {
   if (m.cols > 1 && t.stride_bytes[nd - 1] != es) return std::string("matmul: ") + what + " must be contiguous along its contraction dim";
   m.ld = t.stride_bytes[nd - 2] / es;
   if (m.rows <= 1 && m.ld == 0) m.ld = m.cols;
-  if (!merge_leading(t, nd - 2, &m.batch, &m.batch_stride)) return std::string("matmul: batch dims of ") + what + " do not form one stride";
+  m.batch = 1;
+  m.batch_stride = 0;
+  if (need_one_batch && !merge_leading(t, nd - 2, &m.batch, &m.batch_stride))
+    return std::string("matmul: batch dims of ") + what + " do not form one stride";
   return "";
 }
 
@@ -141,10 +145,11 @@ PGB_API int pgb_qlinear_i8(const pgb_tensor *a, const pgb_tensor *w, const float
   }
   if (!out && !acc_i32) { set_error("qlinear: nothing to write"); return PGB_ERR_INVALID_ARG; }
   if (!device_present()) return PGB_ERR_CUDA;
-  return run_gemm_tc(GEMM_I8, A.ptr, A.ld, 0, W.ptr, W.ld, 0, M, N, K, 1, e, (cudaStream_t)stream);
+  e.alpha = 1.f;
+  return run_gemm_tc(GEMM_I8, A.ptr, A.ld, 0, 0, W.ptr, W.ld, 0, 0, M, N, K, 1, 1, e, (cudaStream_t)stream);
 }
 
-PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, const pgb_tensor *residual,
+PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, float alpha, const pgb_tensor *residual,
                        const pgb_tensor *out, void *stream) {
   if (!a || !b || !out) { set_error("matmul: null operand"); return PGB_ERR_INVALID_ARG; }
   if (a->dtype != b->dtype) { set_error("matmul: operand dtypes differ"); return PGB_ERR_INVALID_ARG; }
@@ -163,41 +168,62 @@ PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tenso
   bt.stride_bytes[nb - 2] = b->stride_bytes[nb - 1];
   bt.stride_bytes[nb - 1] = b->stride_bytes[nb - 2];
   Mat A, B, O;
-  std::string err = as_mat(*a, "a", A);
+  std::string err = as_mat(*a, "a", A, false);
   if (err.empty()) {
-    err = as_mat(bt, "b", B);
+    err = as_mat(bt, "b", B, false);
     if (!err.empty()) err = "matmul: b must be K-major (pass the transposed view of an [N,K] array); N-major b is not built yet";
   }
-  if (err.empty()) err = as_mat(*out, "the output", O);
+  if (err.empty()) err = as_mat(*out, "the output", O, false);
+  Mat R{};
+  if (err.empty() && residual) err = as_mat(*residual, "the residual", R, false);
   if (!err.empty()) { set_error(err); return PGB_ERR_UNSUPPORTED; }
   if (A.cols != B.cols) { set_error("matmul: contraction dims differ"); return PGB_ERR_INVALID_ARG; }
-  int64_t M = A.rows, batch = A.batch, a_bs = A.batch_stride, o_bs = O.batch_stride;
   const int64_t N = B.rows, K = A.cols;
-  if (B.batch == 1 && b->ndim == 2 && A.batch > 1) {
-    // shared weight: fold a's batch into M when its rows form one pitch
-    if (A.batch_stride != A.rows * A.ld || O.batch != A.batch || O.batch_stride != O.rows * O.ld) {
-      set_error("matmul: a batched `a` with a 2-D `b` needs contiguous batches");
+  int64_t M = A.rows, nb0 = 1, nb1 = 1;
+  int64_t abs0 = 0, abs1 = 0, bbs0 = 0, bbs1 = 0, obs0 = 0, obs1 = 0, rbs0 = 0, rbs1 = 0;
+  const int nla = a->ndim - 2;
+  if (O.cols != N || O.rows != A.rows || out->ndim != a->ndim) { set_error("matmul: output shape does not match"); return PGB_ERR_INVALID_ARG; }
+  for (int d = 0; d < nla; ++d)
+    if (out->shape[d] != a->shape[d] || (residual && residual->shape[d] != a->shape[d])) { set_error("matmul: batch dims differ"); return PGB_ERR_INVALID_ARG; }
+  if (residual && (residual->ndim != out->ndim || R.rows != O.rows || R.cols != N)) { set_error("matmul: the residual must have the output's shape"); return PGB_ERR_INVALID_ARG; }
+  if (b->ndim == 2 && nla > 0) {
+    // shared weight: fold a's batch into M when its rows (and the output's) form one pitch
+    int64_t cnt = 1, st = 0;
+    auto folds = [&](const pgb_tensor &t, const Mat &m) { return merge_leading(t, nla, &cnt, &st) && (cnt == 1 || st == m.rows * m.ld); };
+    if (!folds(*a, A) || !folds(*out, O) || (residual && !folds(*residual, R))) {
+      set_error("matmul: a batched `a` with a 2-D `b` needs batches that are contiguous in memory");
       return PGB_ERR_UNSUPPORTED;
     }
-    M = A.rows * A.batch;
-    batch = 1;
-    a_bs = 0;
-    o_bs = 0;
-  } else if (A.batch != B.batch || O.batch != A.batch) {
-    set_error("matmul: batch dims differ");
-    return PGB_ERR_INVALID_ARG;
+    merge_leading(*a, nla, &cnt, &st);
+    M = A.rows * cnt;
+  } else if (nla > 0) {
+    if (b->ndim != a->ndim) { set_error("matmul: batch dims differ"); return PGB_ERR_INVALID_ARG; }
+    for (int d = 0; d < nla; ++d)
+      if (b->shape[d] != a->shape[d]) { set_error("matmul: batch dims differ"); return PGB_ERR_INVALID_ARG; }
+    // the leading dims become at most two batch dims with one stride each, the same split for every operand
+    bool found = false;
+    for (int sp = 0; sp <= nla && !found; ++sp) {
+      int64_t c0, c1, d0, d1;
+      bool ok = merge_dims(*a, 0, sp, &c0, &abs0) && merge_dims(*a, sp, nla, &c1, &abs1);
+      ok = ok && merge_dims(bt, 0, sp, &d0, &bbs0) && merge_dims(bt, sp, nla, &d1, &bbs1);
+      ok = ok && merge_dims(*out, 0, sp, &d0, &obs0) && merge_dims(*out, sp, nla, &d1, &obs1);
+      if (ok && residual) ok = merge_dims(*residual, 0, sp, &d0, &rbs0) && merge_dims(*residual, sp, nla, &d1, &rbs1);
+      if (ok) { nb0 = c0; nb1 = c1; found = true; }
+    }
+    if (!found) { set_error("matmul: the batch dims do not reduce to two strided dims"); return PGB_ERR_UNSUPPORTED; }
   }
-  if (O.rows * (batch == 1 ? O.batch : 1) != M || O.cols != N) { set_error("matmul: output shape does not match"); return PGB_ERR_INVALID_ARG; }
   if (out->dtype != PGB_F32 && out->dtype != PGB_F16 && out->dtype != PGB_BF16) {
     set_error(std::string("matmul output not implemented for ") + dtype_name(out->dtype));
     return PGB_ERR_UNSUPPORTED;
   }
   GemmEpilogue e{};
   e.act = act;
+  e.alpha = alpha;
   e.out = out->data;
   e.out_dtype = out->dtype;
   e.ldc = O.ld;
-  e.out_batch = o_bs;
+  e.out_batch = obs1;
+  e.out_batch0 = obs0;
   if (bias) {
     if (numel_of(*bias) != N || !is_contiguous(*bias) || dtype_size(bias->dtype) == 0) {
       set_error("matmul: the bias must be a contiguous vector of the output width");
@@ -207,16 +233,14 @@ PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tenso
     e.bias_dtype = bias->dtype;
   }
   if (residual) {
-    Mat R;
-    err = as_mat(*residual, "the residual", R);
-    if (!err.empty() || R.cols != N || R.rows * R.batch != O.rows * O.batch) { set_error("matmul: the residual must have the output's shape"); return PGB_ERR_INVALID_ARG; }
     e.residual = residual->data;
     e.res_dtype = residual->dtype;
     e.res_ld = R.ld;
-    e.res_batch = batch == 1 ? 0 : R.batch_stride;
+    e.res_batch = rbs1;
+    e.res_batch0 = rbs0;
   }
   if (!device_present()) return PGB_ERR_CUDA;
-  return run_gemm_tc(a->dtype == PGB_F16 ? GEMM_F16 : GEMM_BF16, A.ptr, A.ld, a_bs, B.ptr, B.ld, B.batch_stride, M, N, K, batch, e,
+  return run_gemm_tc(a->dtype == PGB_F16 ? GEMM_F16 : GEMM_BF16, A.ptr, A.ld, abs0, abs1, B.ptr, B.ld, bbs0, bbs1, M, N, K, nb0, nb1, e,
                      (cudaStream_t)stream);
 }
 

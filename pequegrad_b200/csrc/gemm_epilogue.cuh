@@ -33,10 +33,11 @@ struct EpiChunk {
     float res[RES ? 32 : 1];
     if (RES) {
       // the residual is this thread's own row segment: 32 consecutive elements
-      const int64_t roff = (int64_t)bz * e.res_batch + (int64_t)row * e.res_ld + n0 + c0;
+      const int64_t roff = (int64_t)(bz / p.nb1) * e.res_batch0 + (int64_t)(bz % p.nb1) * e.res_batch + (int64_t)row * e.res_ld + n0 + c0;
 #pragma unroll
       for (int i = 0; i < 32; ++i) res[RES ? i : 0] = i < n_left ? load_as<float>(e.residual, e.res_dtype, roff + i) : 0.f;
     }
+    const float alpha = e.alpha;
     uint32_t f[32];
     // column operands come from the warp's stash as 128-bit broadcast reads (every lane the same address)
     float sc[KIND == GEMM_I8 ? 32 : 1], bi[BIAS ? 32 : 1];
@@ -56,7 +57,7 @@ struct EpiChunk {
     for (int i = 0; i < 32; ++i) {
       float x;
       if (KIND == GEMM_I8) x = __fmul_rn((float)(int)v[i], sc[KIND == GEMM_I8 ? i : 0]);
-      else x = __uint_as_float(v[i]);
+      else x = __uint_as_float(v[i]) * alpha;
       if (BIAS) x = __fadd_rn(x, bi[BIAS ? i : 0]);
       if (ACT == ACT_RELU) x = x > 0.f ? x : 0.f;
       if (ACT == ACT_GELU_TANH) x = gelu_tanh(x);
@@ -69,7 +70,7 @@ struct EpiChunk {
         if (i < n_left) local_max = fmaxf(local_max, fabsf(__uint_as_float(f[i])));
     }
     if (!e.out) return;
-    const int64_t off0 = (int64_t)bz * e.out_batch + (int64_t)row0 * e.ldc + n0 + c0;
+    const int64_t off0 = (int64_t)(bz / p.nb1) * e.out_batch0 + (int64_t)(bz % p.nb1) * e.out_batch + (int64_t)row0 * e.ldc + n0 + c0;
     if (e.out_dtype == PGB_F32) {
       float *dst = (float *)e.out + off0;
       if (full_chunk && out_vec) stage_and_store<32>(stage, f, (uint8_t *)dst, e.ldc * 4, row0, p.M, lane);
@@ -107,7 +108,7 @@ __device__ __noinline__ void gemm_epilogue_tiles(const GemmParams &p, uint32_t t
   const int out_es = e.out_dtype == PGB_F32 ? 4 : 2;
   // vector stores need 16-byte aligned rows
   const bool out_vec = e.out && ((reinterpret_cast<uintptr_t>(e.out) & 15) == 0) && ((e.ldc * out_es) % 16 == 0) &&
-                       ((e.out_batch * out_es) % 16 == 0);
+                       ((e.out_batch * out_es) % 16 == 0) && ((e.out_batch0 * out_es) % 16 == 0);
   const bool acc_vec = e.acc_out && ((reinterpret_cast<uintptr_t>(e.acc_out) & 15) == 0) && ((e.ld_acc & 3) == 0);
   const bool want_max = e.absmax != nullptr;
   int it = 0;

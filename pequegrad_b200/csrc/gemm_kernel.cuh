@@ -29,7 +29,8 @@ static __device__ int g_gemm_error;  // 0 = ok; else (role << 16) | block index 
 struct GemmParams {
   int M, N, K;  // K in elements
   int num_kb;   // K slabs
-  int tiles_m, tiles_n, batch;
+  int tiles_m, tiles_n, batch;  // batch = nb0 * nb1
+  int nb1;                      // extent of the inner batch dim
   int dbg;  // tuning aid: bit 0 = epilogue skips math and stores, bit 1 = also skips the TMEM loads
   GemmEpilogue epi;
 };

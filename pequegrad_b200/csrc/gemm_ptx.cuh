@@ -39,11 +39,11 @@ __device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volati
   }
   return false;
 }
-__device__ __forceinline__ void tma_load_3d(void *smem_dst, const CUtensorMap *tmap, int x, int y, int z, uint64_t *bar) {
+__device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *tmap, int x, int y, int z, int w, uint64_t *bar) {
   asm volatile(
-      "cp.async.bulk.tensor.3d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4}], [%5];" ::"r"(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];" ::"r"(
           smem_u32(smem_dst)),
-      "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(smem_u32(bar))
+      "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
       : "memory");
 }
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t ncols) {

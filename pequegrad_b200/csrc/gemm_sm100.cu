@@ -90,8 +90,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
           }
           mbar_expect_tx(&full[s], Cfg::kStageBytes);
           uint8_t *sa = tiles + s * Cfg::kStageBytes;
-          tma_load_3d(sa, &tmap_a, kb * SLAB_ELEMS, m0, bz, &full[s]);
-          tma_load_3d(sa + kTileABytes, &tmap_b, kb * SLAB_ELEMS, n0, bz, &full[s]);
+          tma_load_4d(sa, &tmap_a, kb * SLAB_ELEMS, m0, bz % p.nb1, bz / p.nb1, &full[s]);
+          tma_load_4d(sa + kTileABytes, &tmap_b, kb * SLAB_ELEMS, n0, bz % p.nb1, bz / p.nb1, &full[s]);
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }
       }
@@ -159,23 +159,26 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
-// [batch, rows, K] K-major operand -> 3-D tensor map with a {128 bytes of K, box_rows, 1} box, 128B swizzle
-static int make_operand_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, int64_t K, int64_t ld_elems, int64_t batch,
-                            int64_t batch_stride_elems, int box_rows, const char *what) {
+// [nb0, nb1, rows, K] K-major operand -> 4-D tensor map with a {128 bytes of K, box_rows, 1, 1} box, 128B swizzle
+static int make_operand_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, int64_t K, int64_t ld_elems, int64_t nb0, int64_t nb1,
+                            int64_t bs0, int64_t bs1, int box_rows, const char *what) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) { set_error("matmul: cuTensorMapEncodeTiled is not available from this driver"); return PGB_ERR_CUDA; }
   const int es = kind == GEMM_I8 ? 1 : 2;
-  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld_elems * es) % 16 || (batch > 1 && (batch_stride_elems * es) % 16)) {
+  // a batch dim of extent 1 has no stride of its own: give it a valid one
+  if (nb1 <= 1) bs1 = rows * ld_elems;
+  if (nb0 <= 1) bs0 = std::max<int64_t>(nb1, 1) * bs1;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld_elems * es) % 16 || (bs1 * es) % 16 || (bs0 * es) % 16) {
     set_error(std::string("matmul: operand ") + what + " must be 16-byte aligned with row and batch pitches that are multiples of 16 bytes");
     return PGB_ERR_UNSUPPORTED;
   }
   const CUtensorMapDataType dt = kind == GEMM_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                                  : (kind == GEMM_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
-  const cuuint64_t dims[3] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)batch};
-  const cuuint64_t strides[2] = {(cuuint64_t)(ld_elems * es), (cuuint64_t)((batch > 1 ? batch_stride_elems : rows * ld_elems) * es)};
-  const cuuint32_t box[3] = {(cuuint32_t)(kSlabBytes / es), (cuuint32_t)box_rows, 1};
-  const cuuint32_t estr[3] = {1, 1, 1};
-  const CUresult r = fn(map, dt, 3, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+  const cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(nb1, 1), (cuuint64_t)std::max<int64_t>(nb0, 1)};
+  const cuuint64_t strides[3] = {(cuuint64_t)(ld_elems * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
+  const cuuint32_t box[4] = {(cuuint32_t)(kSlabBytes / es), (cuuint32_t)box_rows, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
                         CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
   if (r != CUDA_SUCCESS) {
     set_error(std::string("matmul: cuTensorMapEncodeTiled failed for operand ") + what + " (code " + std::to_string((int)r) + ")");
@@ -207,9 +210,10 @@ static int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, 
   return launch_gemm<KIND, 32>(ma, mb, p, grid, stream);
 }
 
-// a: [batch, M, K], b: [batch, N, K], both K contiguous; strides in elements.
-int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_batch, const void *b, int64_t ldb, int64_t b_batch, int64_t M, int64_t N,
-                int64_t K, int64_t batch, const GemmEpilogue &epi, cudaStream_t stream) {
+// a: [nb0, nb1, M, K], b: [nb0, nb1, N, K], both K contiguous; strides in elements.
+int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_bs1, const void *b, int64_t ldb, int64_t b_bs0, int64_t b_bs1,
+                int64_t M, int64_t N, int64_t K, int64_t nb0, int64_t nb1, const GemmEpilogue &epi, cudaStream_t stream) {
+  const int64_t batch = nb0 * nb1;
   if (M <= 0 || N <= 0 || batch <= 0) return PGB_OK;
   if (K <= 0) { set_error("matmul: empty contraction dim"); return PGB_ERR_INVALID_ARG; }
   int bn = N > 128 ? 256 : (N > 32 ? 128 : 32);
@@ -222,11 +226,10 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_batch, const voi
     set_error("matmul: problem too large for one launch");
     return PGB_ERR_UNSUPPORTED;
   }
-  if (b_batch == 0 && batch > 1) { set_error("matmul: batched A with an unbatched B: flatten the batch into M"); return PGB_ERR_UNSUPPORTED; }
   CUtensorMap ma, mb;
-  int st = make_operand_map(&ma, a, kind, M, K, lda, batch, a_batch, kBM, "A");
+  int st = make_operand_map(&ma, a, kind, M, K, lda, nb0, nb1, a_bs0, a_bs1, kBM, "A");
   if (st != PGB_OK) return st;
-  st = make_operand_map(&mb, b, kind, N, K, ldb, batch, b_batch, bn, "B");
+  st = make_operand_map(&mb, b, kind, N, K, ldb, nb0, nb1, b_bs0, b_bs1, bn, "B");
   if (st != PGB_OK) return st;
   GemmParams p{};
   p.M = (int)M;
@@ -237,6 +240,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_batch, const voi
   p.tiles_m = (int)tiles_m;
   p.tiles_n = (int)tiles_n;
   p.batch = (int)batch;
+  p.nb1 = (int)std::max<int64_t>(nb1, 1);
   p.epi = epi;
   if (const char *e = getenv("PGB_GEMM_DBG")) p.dbg = atoi(e);
   const int64_t num_tiles = tiles_m * tiles_n * batch;

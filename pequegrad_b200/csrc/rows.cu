@@ -305,4 +305,69 @@ int run_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma, const pgb_t
   return rows_launch<__nv_bfloat16, false>(p, stream);
 }
 
+// ---------------------------------------------------------------------------
+// Token + position embedding: out[r, :] = wte[ids[r], :] + wpe[r % T, :].
+// Replaces the Select-with-index-tensor gather plus the add of
+// pequegrad/modules.py:329-337 and examples/gpt2.py:365-372. One warp per row,
+// 128-bit loads; an id outside [0, V) yields a zero row instead of a wild read.
+template <typename IoT>
+__global__ void __launch_bounds__(256) embedding_rows_kernel(const int *__restrict__ ids, const IoT *__restrict__ wte,
+                                                             const IoT *__restrict__ wpe, IoT *__restrict__ out, int64_t rows, int64_t C,
+                                                             int64_t V, int64_t T) {
+  constexpr int VEC = 16 / (int)sizeof(IoT);
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= rows) return;
+  const int id = __ldg(ids + row);
+  const bool ok = id >= 0 && id < V;
+  const IoT *te = wte + (int64_t)(ok ? id : 0) * C;
+  const IoT *pe = wpe ? wpe + (row % T) * C : nullptr;
+  IoT *o = out + row * C;
+  for (int64_t c = (int64_t)lane * VEC; c < C; c += 32 * VEC) {
+    float a[VEC], b[VEC];
+    load_vec_cached<float, IoT, VEC>(te + c, a);
+    if (pe) load_vec_cached<float, IoT, VEC>(pe + c, b);
+#pragma unroll
+    for (int e = 0; e < VEC; ++e) a[e] = ok ? (pe ? a[e] + b[e] : a[e]) : 0.f;
+    store_vec<IoT, float, VEC>(o + c, a);
+  }
+}
+
+int run_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, const pgb_tensor *wpe, int64_t T, const pgb_tensor *out,
+                       cudaStream_t stream) {
+  if (!ids || !wte || !out) { set_error("embedding: null tensor"); return PGB_ERR_INVALID_ARG; }
+  if (ids->dtype != PGB_I32 || !is_contiguous(*ids)) { set_error("embedding: ids must be contiguous int32"); return PGB_ERR_INVALID_ARG; }
+  if (wte->ndim != 2 || !is_contiguous(*wte) || !is_contiguous(*out) || out->dtype != wte->dtype) {
+    set_error("embedding: the table must be a contiguous [V, C] matrix and the output of its dtype");
+    return PGB_ERR_INVALID_ARG;
+  }
+  if (wte->dtype != PGB_F16 && wte->dtype != PGB_F32 && wte->dtype != PGB_BF16) {
+    set_error(std::string("embedding not implemented for ") + dtype_name(wte->dtype));
+    return PGB_ERR_UNSUPPORTED;
+  }
+  const int64_t rows = numel_of(*ids), V = wte->shape[0], C = wte->shape[1];
+  if (numel_of(*out) != rows * C) { set_error("embedding: output shape does not match"); return PGB_ERR_INVALID_ARG; }
+  if (wpe && (wpe->ndim != 2 || wpe->shape[1] != C || wpe->shape[0] < T || wpe->dtype != wte->dtype || !is_contiguous(*wpe) || T <= 0)) {
+    set_error("embedding: the position table must be [>= T, C] of the same dtype");
+    return PGB_ERR_INVALID_ARG;
+  }
+  const int es = dtype_size(wte->dtype);
+  if ((C * es) % 16 || (reinterpret_cast<uintptr_t>(wte->data) & 15) || (reinterpret_cast<uintptr_t>(out->data) & 15) ||
+      (wpe && (reinterpret_cast<uintptr_t>(wpe->data) & 15))) {
+    set_error("embedding: rows must be 16-byte aligned");
+    return PGB_ERR_UNSUPPORTED;
+  }
+  if (rows == 0) return PGB_OK;
+  const unsigned grid = (unsigned)((rows + 7) / 8);
+  const int *idp = (const int *)ids->data;
+  if (wte->dtype == PGB_F32)
+    embedding_rows_kernel<float><<<grid, 256, 0, stream>>>(idp, (const float *)wte->data, wpe ? (const float *)wpe->data : nullptr, (float *)out->data, rows, C, V, T > 0 ? T : 1);
+  else if (wte->dtype == PGB_F16)
+    embedding_rows_kernel<__half><<<grid, 256, 0, stream>>>(idp, (const __half *)wte->data, wpe ? (const __half *)wpe->data : nullptr, (__half *)out->data, rows, C, V, T > 0 ? T : 1);
+  else
+    embedding_rows_kernel<__nv_bfloat16><<<grid, 256, 0, stream>>>(idp, (const __nv_bfloat16 *)wte->data, wpe ? (const __nv_bfloat16 *)wpe->data : nullptr, (__nv_bfloat16 *)out->data, rows, C, V, T > 0 ? T : 1);
+  count_launch();
+  return check_launch("embedding_rows_kernel");
+}
+
 }  // namespace pgb

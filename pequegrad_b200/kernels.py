@@ -160,6 +160,17 @@ def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor | None, beta: torch.Tens
     return y
 
 
+def embedding_rows(ids: torch.Tensor, wte: torch.Tensor, wpe: torch.Tensor | None, T: int) -> torch.Tensor:
+    """out[r] = wte[ids[r]] + wpe[r % T]; ids int32 of any shape, result ids.shape + (C,)."""
+    out = torch.empty(tuple(ids.shape) + (wte.shape[1],), dtype=wte.dtype, device=wte.device)
+    idd, td, od = desc(ids), desc(wte), desc(out)
+    pd = desc(wpe) if wpe is not None else None
+    with torch.cuda.device(wte.device):
+        st = L.lib().pgb_embedding_rows(C.byref(idd), C.byref(td), C.byref(pd) if pd else None, T, C.byref(od), _stream())
+    L.check(st)
+    return out
+
+
 def _ref(t):
     if t is None:
         return None
@@ -168,7 +179,7 @@ def _ref(t):
 
 
 def matmul(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, act: int = 0, residual: torch.Tensor | None = None,
-           out: torch.Tensor | None = None, out_dtype=None) -> torch.Tensor:
+           out: torch.Tensor | None = None, out_dtype=None, alpha: float = 1.0) -> torch.Tensor:
     """out = act(a @ b + bias) + residual on the tensor cores. `b` is the [.., K, N] operand as a
     view whose K dim is contiguous (e.g. `w_t.T` for a weight stored as [N, K])."""
     if out is None:
@@ -177,7 +188,7 @@ def matmul(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, a
     ad, bd, od = desc(a), desc(b), desc(out)
     bi, rs = _ref(bias), _ref(residual)
     with torch.cuda.device(a.device):
-        st = L.lib().pgb_matmul(C.byref(ad), C.byref(bd), bi[0] if bi else None, act, rs[0] if rs else None, C.byref(od), _stream())
+        st = L.lib().pgb_matmul(C.byref(ad), C.byref(bd), bi[0] if bi else None, act, alpha, rs[0] if rs else None, C.byref(od), _stream())
     L.check(st)
     return out
 

@@ -1,0 +1,68 @@
+"""int8 quantized MLP inference (784 -> 1024 -> 1024 -> 10 with ReLU).
+
+The workload of the reference's examples/quantized_mlp.py, with real int8 in
+place of its fp32 fake quantisation (examples/quantized_mlp.py:28-48):
+  weights      offline, per output channel: s_w[n] = max(max_k |W[k,n]|, 1e-6) / 127,
+               Wq[n,k] = clip(rint(W[k,n] / s_w[n]), -127, 127), stored [N, K] (K-major)
+  activations  on the device, per tensor and per layer: s_x = max(max|x|, 1e-6) / 127,
+               xq = clip(rint(x / s_x), -127, 127); the absmax never leaves the GPU
+  layer        acc = xq . Wq^T in int32 (tcgen05 kind::i8), then
+               h = relu(acc * (s_x * s_w[n]) + b[n]) in fp32; the last layer has no ReLU
+Per layer that is: quantise kernel, GEMM kernel with fused dequant + bias + ReLU +
+absmax of its own output (which is the next layer's activation absmax).
+"""
+from __future__ import annotations
+
+from typing import Sequence
+
+import numpy as np
+import torch
+
+from . import kernels as K
+
+
+def quantize_weight(w: np.ndarray):
+    """w: [K, N] fp32 as a Linear stores it (pequegrad/modules.py:221-225) -> (Wq [N, K] int8, s_w [N] fp32)."""
+    wt = np.ascontiguousarray(w.T, np.float32)
+    amax = np.maximum(np.abs(wt).max(axis=1), np.float32(1e-6)).astype(np.float32)
+    scale = (amax / np.float32(127)).astype(np.float32)
+    q = np.clip(np.rint(wt / scale[:, None]), -127, 127).astype(np.int8)
+    return q, scale
+
+
+class QuantizedMLP:
+    def __init__(self, weights: Sequence[np.ndarray], biases: Sequence[np.ndarray], device="cuda"):
+        self.layers = []
+        for w, b in zip(weights, biases):
+            q, s = quantize_weight(w)
+            self.layers.append((torch.from_numpy(q).to(device), torch.from_numpy(s).to(device),
+                                torch.from_numpy(np.ascontiguousarray(b, np.float32)).to(device)))
+        self._bufs = {}
+
+    def _buffers(self, rows: int, device):
+        key = (rows, str(device))
+        if key not in self._bufs:
+            dims = [self.layers[0][0].shape[1]] + [l[0].shape[0] for l in self.layers]
+            self._bufs[key] = dict(
+                q=[torch.empty((rows, d), dtype=torch.int8, device=device) for d in dims[:-1]],
+                h=[torch.empty((rows, d), dtype=torch.float32, device=device) for d in dims[1:]],
+                amax=torch.zeros(len(self.layers) + 1, dtype=torch.float32, device=device),
+            )
+        return self._bufs[key]
+
+    def forward(self, x: torch.Tensor, keep: bool = False):
+        """x: [rows, 784] fp32 on the device. Returns logits [rows, 10] fp32 (and, with keep, the per-layer tensors)."""
+        b = self._buffers(x.shape[0], x.device)
+        amax = b["amax"]
+        amax[1:].zero_()  # slot i holds max|input of layer i|; the GEMM epilogues fold into slots 1..
+        K.absmax(x, out=amax[0:1])
+        h = x
+        kept = []
+        n = len(self.layers)
+        for i, (wq, ws, bias) in enumerate(self.layers):
+            xq = K.quantize_i8(h, absmax_dev=amax[i:i + 1], out=b["q"][i])
+            h, _ = K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=i < n - 1, out=b["h"][i],
+                                out_absmax=amax[i + 1:i + 2] if i < n - 1 else None)
+            if keep:
+                kept.append((xq, h))
+        return (h, kept) if keep else h

@@ -1,0 +1,124 @@
+"""The host-side mirror (lazy Tensor, jit) against torch CPU, in the form of the reference's
+own tests: `_compare_fn_with_torch` with seed 1337 and uniform[0.5,0.9) inputs
+(tests/test_ops.py:20-80), jit-vs-eager (tests/test_compile.py:26-57), composites
+(tests/test_high_level_ops.py:100-121, 354-367, 529-544)."""
+import numpy as np
+import pytest
+import torch
+
+from helpers import assert_close, ref_test_inputs
+from pequegrad_b200 import _lib as L
+from pequegrad_b200 import fuser
+from pequegrad_b200 import tensor as pg
+
+pytestmark = pytest.mark.gpu
+
+
+def _compare_fn_with_torch(shapes, pg_fn, torch_fn=None, tol=1e-5, dtype=np.float32, jit=False):
+    torch_fn = torch_fn or pg_fn
+    arrs = ref_test_inputs(shapes, dtype)
+    want = torch_fn(*[torch.from_numpy(a) for a in arrs])
+    fn = fuser.jit(pg_fn) if jit else pg_fn
+    got = fn(*[pg.Tensor(a) for a in arrs])
+    assert list(got.shape) == list(want.shape)
+    assert_close(got.numpy(), want.numpy().astype(got.numpy().dtype), tol, tol)
+
+
+def launches(fn):
+    before = L.lib().pgb_launch_count()
+    fn()
+    return L.lib().pgb_launch_count() - before
+
+
+@pytest.mark.parametrize("jit", [False, True])
+@pytest.mark.parametrize("shape", [(2, 3), (3, 4), (4, 5)])
+def test_binary_unary_and_reducers_like_the_reference_tests(shape, jit):
+    ops = [(lambda x, y: x + y, None), (lambda x, y: x * y, None), (lambda x, y: x - y, None), (lambda x, y: x / y, None),
+           (lambda x, y: x ** y, None), (lambda x, y: pg.max(x, y) if isinstance(x, pg.Tensor) else torch.max(x, y), None)]
+    for f, _ in ops:
+        _compare_fn_with_torch([shape, shape], f, jit=jit)
+    # comparisons return 0/1 in the operand dtype (csrc/cuda/binary.cu:24-41)
+    _compare_fn_with_torch([shape, shape], lambda x, y: x > y, lambda x, y: (x > y).float(), jit=jit)
+    _compare_fn_with_torch([shape, shape, shape], lambda a, b, c: (a * b + c) * b, jit=jit)  # tests/test_ops.py:96-104
+    _compare_fn_with_torch([shape], lambda x: x.exp() if isinstance(x, pg.Tensor) else torch.exp(x), jit=jit)
+    _compare_fn_with_torch([shape], lambda x: x.log() if isinstance(x, pg.Tensor) else torch.log(x), jit=jit)
+    for axes in [(0, 1), (1, 0), (0,), (1,), -1, (-1, -2), None]:
+        for kd in (True, False):
+            tdim = list(range(len(shape))) if axes is None else axes
+            _compare_fn_with_torch([shape], lambda x: x.sum(axes, kd), lambda x: torch.sum(x, dim=tdim, keepdim=kd), jit=jit)
+            _compare_fn_with_torch([shape], lambda x: x.mean(axes, kd), lambda x: torch.mean(x, dim=tdim, keepdim=kd), jit=jit)
+            _compare_fn_with_torch([shape], lambda x: x.max_reduce(axes, kd), lambda x: torch.amax(x, dim=tdim, keepdim=kd), jit=jit)
+
+
+def test_permute_broadcast_where_astype():
+    _compare_fn_with_torch([(2, 3, 4)], lambda x: pg.permute(x, (2, 0, 1)) * 2.0 if isinstance(x, pg.Tensor) else x.permute(2, 0, 1) * 2.0)
+    _compare_fn_with_torch([(4, 3, 2), (2,)], lambda x, y: x * y + 5.0, jit=True)  # tests/test_compile.py broadcast case
+    _compare_fn_with_torch([(3, 4), (3, 4), (3, 4)], lambda c, a, b: pg.where(c > 0.7, a, b) if isinstance(c, pg.Tensor) else torch.where(c > 0.7, a, b))
+    x = ref_test_inputs([(5, 6)], np.float32)[0] * 10
+    assert np.array_equal(pg.Tensor(x).astype(pg.int32).numpy(), x.astype(np.int32))
+    assert pg.Tensor(x).reshape(6, 5).permute(1, 0).reshape(30).numpy().tolist() == x.reshape(6, 5).T.reshape(30).tolist()
+    with pytest.raises(ValueError):
+        pg.Tensor(x) + pg.Tensor(x.astype(np.float64))
+
+
+def test_readme_fusion_is_one_kernel_and_matches_eager():
+    # README.md:59-63; eager = fill, fill, add, add, sum, mul kernels; jit = one fused reduce kernel
+    rng = np.random.default_rng(1)
+    x = pg.Tensor(rng.random((1000, 20, 100), dtype=np.float32))
+    y = pg.Tensor(rng.random((1000, 100, 20), dtype=np.float32))
+
+    def f(x, y):
+        return ((pg.permute(x, (0, 2, 1)) + 2) + y).sum(2) * 3
+    out = {}
+    n_eager = launches(lambda: out.setdefault("e", f(x, y).numpy()))
+    n_jit = launches(lambda: out.setdefault("j", fuser.jit(f)(x, y).numpy()))
+    assert n_jit == 1 and n_eager >= 4
+    want = ((x.numpy().transpose(0, 2, 1).astype(np.float64) + 2 + y.numpy()).sum(2) * 3)
+    assert_close(out["j"], want, 1e-5)
+    assert_close(out["e"], out["j"], 1e-6)
+
+
+def test_long_reduce_with_prologue_and_epilogue_fuses():
+    # the reference refuses to fuse reduces of >= 1024 elements (csrc/compiler/scheduler.cpp:55-61)
+    rng = np.random.default_rng(2)
+    a = rng.standard_normal((256, 4096)).astype(np.float32)
+    x = pg.Tensor(a)
+    for ax in (0, 1):
+        f = lambda t: ((t * 1.5 + 0.25).mean(ax)).exp()  # noqa: E731
+        got = {}
+        assert launches(lambda: got.setdefault("v", fuser.jit(f)(x).numpy())) <= 2  # the kernel (+ finish kernel if split)
+        assert_close(got["v"], np.exp((a.astype(np.float64) * 1.5 + 0.25).mean(ax)), 1e-5)
+    assert np.array_equal(pg.argmax(x, 1).numpy(), a.argmax(1))
+
+
+def test_composites_eager_and_jit():
+    # layer_norm shapes and tolerance of tests/test_high_level_ops.py:100-121
+    for shape, ns in [((2, 3, 4), (4,)), ((2, 3, 4), (3, 4)), ((5, 10), (10,)), ((64, 768), (768,))]:
+        (x,) = ref_test_inputs([shape], np.float32)
+        want = torch.nn.functional.layer_norm(torch.from_numpy(x), ns, eps=1e-5).numpy()
+        assert_close(pg.layer_norm(pg.Tensor(x), ns).numpy(), want, 1e-4)
+        assert_close(fuser.jit(lambda t: pg.layer_norm(t, ns))(pg.Tensor(x)).numpy(), want, 1e-4)
+    (x,) = ref_test_inputs([(8, 1024)], np.float32)
+    want = torch.softmax(torch.from_numpy(x), -1).numpy()
+    assert_close(pg.softmax(pg.Tensor(x)).numpy(), want, 1e-5)
+    n = launches(lambda: assert_close(fuser.jit(pg.softmax)(pg.Tensor(x)).numpy(), want, 1e-5))
+    assert n == 1
+    (x,) = ref_test_inputs([(2, 3)], np.float32)
+    want = torch.nn.functional.gelu(torch.from_numpy(x), approximate="tanh").numpy()
+    assert_close(pg.gelu(pg.Tensor(x)).numpy(), want, 1e-5)
+    assert_close(fuser.jit(pg.gelu)(pg.Tensor(x)).numpy(), want, 1e-5)
+
+
+def test_matmul_half_and_reference_error_for_float32():
+    rng = np.random.default_rng(3)
+    a = rng.standard_normal((5, 64, 128)).astype(np.float16)
+    w = rng.standard_normal((128, 96)).astype(np.float16)
+    got = (pg.Tensor(a) @ pg.Tensor(w)).numpy().astype(np.float32)
+    want = a.astype(np.float32) @ w.astype(np.float32)
+    assert_close(got, want, 2e-2, 2e-2 * float(np.abs(want).max()))
+    b = rng.standard_normal((5, 128, 32)).astype(np.float16)
+    got = (pg.Tensor(a) @ pg.Tensor(b)).numpy().astype(np.float32)
+    want = a.astype(np.float32) @ b.astype(np.float32)
+    assert_close(got, want, 2e-2, 2e-2 * float(np.abs(want).max()))
+    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float32"):
+        (pg.Tensor(a.astype(np.float32)) @ pg.Tensor(w.astype(np.float32))).eval()
