@@ -86,26 +86,33 @@ class GPT2:
         return logits
 
 
-def reference_forward(cfg: GPT2Config, weights: dict, idx: np.ndarray) -> np.ndarray:
-    """fp32 torch-CPU restatement of examples/gpt2.py (mask -1e9 -> -inf), for parity tests.
-    Weights are first rounded to fp16 as the device model stores them."""
+def round_weights_fp16(weights: dict) -> dict:
+    """The weights as fp32 torch-CPU tensors after a round trip through fp16 (what the device model stores)."""
     r = lambda a: torch.from_numpy(a.astype(np.float16).astype(np.float32))  # noqa: E731
+    return {k: ({k2: r(v2) for k2, v2 in v.items()} if isinstance(v, dict) else r(v)) for k, v in weights.items()}
+
+
+def reference_forward(cfg: GPT2Config, weights: dict, idx: np.ndarray, rounded: dict | None = None) -> np.ndarray:
+    """fp32 torch-CPU restatement of examples/gpt2.py for parity tests (masked scores are -inf here where the
+    example adds -1e9: after the softmax both give exactly 0 in fp32). Weights are first rounded to fp16 as
+    the device model stores them (`rounded` = a cached `round_weights_fp16(weights)`)."""
+    w = rounded if rounded is not None else round_weights_fp16(weights)
     B, T = idx.shape
     C, H = cfg.n_embd, cfg.n_head
     ids = torch.from_numpy(idx.astype(np.int64))
-    x = r(weights["wte"])[ids] + r(weights["wpe"])[:T]
+    x = w["wte"][ids] + w["wpe"][:T]
     mask = torch.tril(torch.ones(T, T, dtype=torch.bool))
-    ln = lambda t, g, b: torch.nn.functional.layer_norm(t, (C,), r(g), r(b), 1e-5)  # noqa: E731
+    ln = lambda t, g, b: torch.nn.functional.layer_norm(t, (C,), g, b, 1e-5)  # noqa: E731
     for i in range(cfg.n_layer):
-        h = weights[f"h{i}"]
-        a = ln(x, h["ln1_g"], h["ln1_b"]) @ r(h["attn_w"]) + r(h["attn_b"])
+        h = w[f"h{i}"]
+        a = ln(x, h["ln1_g"], h["ln1_b"]) @ h["attn_w"] + h["attn_b"]
         q, k, v = (t.view(B, T, H, C // H).transpose(1, 2) for t in a.split(C, dim=2))
         s = (q @ k.transpose(-2, -1)) / (C // H) ** 0.5
         s = torch.softmax(s.masked_fill(~mask, float("-inf")), -1)
         y = (s @ v).transpose(1, 2).reshape(B, T, C)
-        x = x + y @ r(h["proj_w"]) + r(h["proj_b"])
-        m = ln(x, h["ln2_g"], h["ln2_b"]) @ r(h["fc_w"]) + r(h["fc_b"])
+        x = x + y @ h["proj_w"] + h["proj_b"]
+        m = ln(x, h["ln2_g"], h["ln2_b"]) @ h["fc_w"] + h["fc_b"]
         m = 0.5 * m * (1.0 + torch.tanh(0.7978845608028654 * (m + 0.044715 * m ** 3)))
-        x = x + m @ r(h["fc2_w"]) + r(h["fc2_b"])
-    x = ln(x, weights["lnf_g"], weights["lnf_b"])
-    return (x @ r(weights["lm_head"])).numpy()
+        x = x + m @ h["fc2_w"] + h["fc2_b"]
+    x = ln(x, w["lnf_g"], w["lnf_b"])
+    return (x @ w["lm_head"]).numpy()
