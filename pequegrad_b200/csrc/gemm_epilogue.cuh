@@ -7,6 +7,7 @@
 // the TMEM load of chunk c+1 is in flight while chunk c is processed; and the
 // accumulator itself is double-buffered against the MMA warp.
 #pragma once
+#include "gemm_epilogue_tma.cuh"
 #include "gemm_kernel.cuh"
 
 namespace pgb {
@@ -131,7 +132,7 @@ __device__ __noinline__ void gemm_epilogue_tiles(const GemmParams &p, uint32_t t
     if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) {
-      if (lane == 0) { *abort_flag = 1; atomicCAS(&g_gemm_error, 0, (3 << 16) | (blockIdx.x & 0xffff)); }
+      if (lane == 0) report_error(p, abort_flag, 3);
       break;
     }
     tc_fence_after();
@@ -164,13 +165,24 @@ __device__ __noinline__ void gemm_epilogue_tiles(const GemmParams &p, uint32_t t
   }
 }
 
-// Chooses the specialisation once per kernel.
+// Chooses the specialisation once per kernel: the TMA-store epilogue when the host found the output
+// (and residual) aligned for it, else the plain-store one above.
 template <int KIND, int BN>
-__device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, uint32_t tmem_base, uint32_t *stage, float *stash, int half, uint64_t *acc_full,
-                                                   uint64_t *acc_empty, volatile int *abort_flag, int q, int lane, int num_tiles,
-                                                   int tiles_per_batch) {
-#define PGB_EPI(ACT, BIAS, RES) \
-  gemm_epilogue_tiles<KIND, BN, ACT, BIAS, RES>(p, tmem_base, stage, stash, half, acc_full, acc_empty, abort_flag, q, lane, num_tiles, tiles_per_batch)
+__device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, const CUtensorMap *omap, uint32_t tmem_base, uint8_t *stage, float *stash,
+                                                   int half, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag, int q, int lane,
+                                                   int num_tiles, int tiles_per_batch) {
+#define PGB_EPI_ARGS tmem_base, stage, stash, half, acc_full, acc_empty, abort_flag, q, lane, num_tiles, tiles_per_batch
+#define PGB_EPI(ACT, BIAS, RES)                                                                         \
+  do {                                                                                                  \
+    if constexpr (BN >= 128) {                                                                          \
+      if (p.out_tma == 4) { gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, 4>(p, omap, PGB_EPI_ARGS); break; } \
+      if constexpr (KIND != GEMM_I8) {                                                                  \
+        if (p.out_tma == 2) { gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, 2>(p, omap, PGB_EPI_ARGS); break; } \
+      }                                                                                                 \
+    }                                                                                                   \
+    gemm_epilogue_tiles<KIND, BN, ACT, BIAS, RES>(p, tmem_base, reinterpret_cast<uint32_t *>(stage), stash, half, acc_full, acc_empty, abort_flag, q, \
+                                                  lane, num_tiles, tiles_per_batch);                   \
+  } while (0)
   const bool bias = p.epi.bias != nullptr, res = p.epi.residual != nullptr;
   const int act = p.epi.act;
   if (KIND == GEMM_I8) {
@@ -184,6 +196,7 @@ __device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, uint32_t
     else { PGB_EPI(ACT_NONE, false, false); }
   }
 #undef PGB_EPI
+#undef PGB_EPI_ARGS
 }
 
 }  // namespace pgb

@@ -1,0 +1,230 @@
+// Epilogue of the tcgen05 GEMM for outputs that TMA can store (16-byte aligned base and pitches):
+// each epilogue warp drains 32 TMEM lanes (32 rows) of the finished accumulator 32 columns at a
+// time, applies the fused epilogue in registers, writes its rows into a 32-row x 128-byte box in
+// shared memory (128B swizzle, so the 16-byte writes of a warp hit 32 distinct banks) and one lane
+// issues a TMA tile store of the box. The tensor map clips ragged bottom / right edges.
+// A box is 32 fp32 columns or 64 16-bit columns, so 16-bit outputs store after every second chunk.
+// Two boxes per warp: a store drains while the next box is being filled.
+// The residual (laid out like the output) is read straight into registers, 16 bytes per load,
+// one chunk ahead of its use.
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include "gemm_kernel.cuh"
+
+namespace pgb {
+
+template <int OES>
+struct ResChunk {
+  uint4 r[OES == 4 ? 8 : 4];  // 32 residual elements of this thread's row
+};
+
+// Edge chunk: element-wise guarded loads (columns >= n_valid read as zero).
+template <int OES>
+__device__ __noinline__ void res_load_edge(ResChunk<OES> &rc, const uint8_t *ptr, int n_valid) {
+  uint32_t w[OES == 4 ? 32 : 16];
+#pragma unroll
+  for (int i = 0; i < 32; ++i) {
+    if (OES == 4) {
+      w[OES == 4 ? i : 0] = i < n_valid ? reinterpret_cast<const uint32_t *>(ptr)[i] : 0u;
+    } else {
+      const uint32_t h = i < n_valid ? (uint32_t) reinterpret_cast<const uint16_t *>(ptr)[i] : 0u;
+      if (i & 1) w[OES == 4 ? 0 : i >> 1] |= h << 16;
+      else w[OES == 4 ? 0 : i >> 1] = h;
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < (OES == 4 ? 8 : 4); ++j) rc.r[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
+}
+
+template <int OES>
+__device__ __forceinline__ void res_load(ResChunk<OES> &rc, const uint8_t *ptr, bool row_ok, int n_valid) {
+  if (n_valid >= 32) {
+#pragma unroll
+    for (int j = 0; j < (OES == 4 ? 8 : 4); ++j) rc.r[j] = row_ok ? reinterpret_cast<const uint4 *>(ptr)[j] : make_uint4(0, 0, 0, 0);
+  } else {
+    res_load_edge<OES>(rc, ptr, row_ok ? n_valid : 0);
+  }
+}
+
+template <int OES>
+__device__ __forceinline__ float res_get(const ResChunk<OES> &rc, int i, bool is_h) {
+  if (OES == 4) {
+    const uint4 &q = rc.r[i >> 2];
+    const uint32_t w = (i & 3) == 0 ? q.x : (i & 3) == 1 ? q.y : (i & 3) == 2 ? q.z : q.w;
+    return __uint_as_float(w);
+  } else {
+    const uint4 &q = rc.r[i >> 3];
+    const int k = (i >> 1) & 3;
+    const uint32_t w = k == 0 ? q.x : k == 1 ? q.y : k == 2 ? q.z : q.w;
+    const uint16_t h = (uint16_t)((i & 1) ? (w >> 16) : (w & 0xffffu));
+    return is_h ? __half2float(__ushort_as_half(h)) : __bfloat162float(__ushort_as_bfloat16(h));
+  }
+}
+
+__device__ __forceinline__ uint32_t pack2(float lo, float hi, bool is_h) {
+  if (is_h) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+  const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&b);
+}
+
+template <int KIND, int BN, int ACT, bool BIAS, bool RES, int OES>
+__device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtensorMap *omap, uint32_t tmem_base, uint8_t *stage, float *stash,
+                                               int half, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag, int q, int lane,
+                                               int num_tiles, int tiles_per_batch) {
+  const GemmEpilogue &e = p.epi;
+  float a_scale = e.a_scale;
+  if (KIND == GEMM_I8 && e.a_scale_dev) {
+    // activation scale from the running absmax: max(amax, 1e-6) / 127, same fp32 ops as the host formula
+    a_scale = fmaxf(__ldg(e.a_scale_dev), 1e-6f) / 127.0f;
+  }
+  float local_max = 0.f;
+  const bool want_max = e.absmax != nullptr;
+  const bool is_h = e.out_dtype == PGB_F16;
+  const float alpha = e.alpha;
+  constexpr int HALF = BN / 2;  // columns per epilogue warp of a lane group
+  const int cbeg = half * HALF, cend = cbeg + HALF;
+  uint32_t g = 0;  // boxes stored by this warp so far; box buffer = g & 1
+  int it = 0;
+  for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
+    const int m0 = (rem / p.tiles_n) * kBM, n0 = (rem % p.tiles_n) * BN;
+    const int zb = bz % p.nb1, wb = bz / p.nb1;
+    const int buf = it & 1;
+    // column operands of this tile, fetched while the MMAs are still running
+    __syncwarp();
+    for (int c = cbeg + lane; c < cend; c += 32) {
+      const int col = n0 + c;
+      const bool okc = col < p.N;
+      if (KIND == GEMM_I8) stash[c] = e.col_scale ? __fmul_rn(a_scale, okc ? __ldg(e.col_scale + col) : 0.f) : a_scale;
+      if (BIAS) stash[256 + c] = (okc && e.bias) ? load_as<float>(e.bias, e.bias_dtype, col) : 0.f;
+    }
+    __syncwarp();
+    const int row0 = m0 + q * 32, row = row0 + lane;
+    const bool row_ok = row < p.M;
+    const int lim = min(cend, p.N - n0);  // end of this warp's columns that exist (warp-uniform)
+    const uint8_t *res_row = nullptr;
+    ResChunk<OES> ra, rb;
+    if (RES) {
+      res_row = reinterpret_cast<const uint8_t *>(e.residual) +
+                ((int64_t)wb * e.res_batch0 + (int64_t)zb * e.res_batch + (int64_t)row * e.res_ld + n0) * OES;
+      if (cbeg < lim) res_load<OES>(ra, res_row + cbeg * OES, row_ok, lim - cbeg);  // does not depend on the accumulator
+    }
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) {
+      if (lane == 0) report_error(p, abort_flag, 3);
+      break;
+    }
+    tc_fence_after();
+    const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+
+    auto release_acc = [&]() {
+      // every TMEM load of this tile has landed in registers: hand the buffer back to the MMA warp
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+    };
+    auto run = [&](const uint32_t(&v)[32], const ResChunk<OES> &rc, int c0) {
+      float x[32];
+      const float *sc = stash + c0, *bi = stash + 256 + c0;
+#pragma unroll
+      for (int i = 0; i < 32; i += 4) {
+        float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f), b4 = s4;
+        if (KIND == GEMM_I8) s4 = *reinterpret_cast<const float4 *>(sc + i);  // 128-bit broadcast reads
+        if (BIAS) b4 = *reinterpret_cast<const float4 *>(bi + i);
+        const float s[4] = {s4.x, s4.y, s4.z, s4.w}, b[4] = {b4.x, b4.y, b4.z, b4.w};
+#pragma unroll
+        for (int k = 0; k < 4; ++k) {
+          float t;
+          if (KIND == GEMM_I8) t = __fmul_rn((float)(int)v[i + k], s[k]);
+          else t = __uint_as_float(v[i + k]) * alpha;
+          if (BIAS) t = __fadd_rn(t, b[k]);
+          if (ACT == ACT_RELU) t = t > 0.f ? t : 0.f;
+          if (ACT == ACT_GELU_TANH) t = gelu_tanh(t);
+          if (RES) t = __fadd_rn(t, res_get<OES>(rc, i + k, is_h));
+          x[i + k] = t;
+        }
+      }
+      if (want_max && row_ok) {
+#pragma unroll
+        for (int i = 0; i < 32; ++i) local_max = fmaxf(local_max, fabsf(x[i]));
+      }
+      if (row0 >= p.M) return;  // the whole warp is below the bottom edge
+      const int sub = OES == 2 ? (((c0 - cbeg) >> 5) & 1) : 0;
+      uint8_t *box = stage + (g & 1u) * kStoreBoxBytes;
+      if (sub == 0) {
+        // the store that last read this box was issued two boxes ago
+        if (lane == 0) tma_store_wait_read<1>();
+        __syncwarp();
+      }
+      uint8_t *rowp = box + lane * 128;
+      const int sw = lane & 7;
+      if (OES == 4) {
+#pragma unroll
+        for (int j = 0; j < 8; ++j)
+          *reinterpret_cast<uint4 *>(rowp + ((j ^ sw) << 4)) = make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
+                                                                         __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3]));
+      } else {
+#pragma unroll
+        for (int j = 0; j < 4; ++j)
+          *reinterpret_cast<uint4 *>(rowp + (((sub * 4 + j) ^ sw) << 4)) =
+              make_uint4(pack2(x[8 * j], x[8 * j + 1], is_h), pack2(x[8 * j + 2], x[8 * j + 3], is_h), pack2(x[8 * j + 4], x[8 * j + 5], is_h),
+                         pack2(x[8 * j + 6], x[8 * j + 7], is_h));
+      }
+      if (OES == 4 || sub == 1 || c0 + 32 >= lim) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_4d(omap, box, n0 + c0 - sub * 32, row0, zb, wb);
+          tma_store_commit();
+        }
+        ++g;
+      }
+    };
+
+    uint32_t va[32], vb[32];
+    if (cbeg < lim) {
+      tmem_ld32_issue(taddr + cbeg, va);
+      for (int c0 = cbeg; c0 < lim; c0 += 64) {
+        tmem_ld_wait();
+        const bool more1 = c0 + 32 < lim;
+        if (more1) {
+          tmem_ld32_issue(taddr + c0 + 32, vb);
+          if (RES) res_load<OES>(rb, res_row + (c0 + 32) * OES, row_ok, lim - c0 - 32);
+        } else {
+          release_acc();
+        }
+        run(va, ra, c0);
+        if (more1) {
+          tmem_ld_wait();
+          const bool more2 = c0 + 64 < lim;
+          if (more2) {
+            tmem_ld32_issue(taddr + c0 + 64, va);
+            if (RES) res_load<OES>(ra, res_row + (c0 + 64) * OES, row_ok, lim - c0 - 64);
+          } else {
+            release_acc();
+          }
+          run(vb, rb, c0 + 32);
+        }
+      }
+    } else {
+      release_acc();  // none of this warp's columns exist in this tile
+    }
+  }
+  // shared memory must outlive the reads of the last stores
+  if (lane == 0) tma_store_wait_all();
+  if (want_max) {
+#pragma unroll
+    for (int m = 16; m > 0; m >>= 1) local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, m));
+    // non-negative floats order like their bit patterns
+    if (lane == 0 && local_max > 0.f) atomicMax(reinterpret_cast<unsigned int *>(e.absmax), __float_as_uint(local_max));
+  }
+}
+
+}  // namespace pgb

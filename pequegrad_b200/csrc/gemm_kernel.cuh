@@ -11,7 +11,10 @@ constexpr int kTileABytes = kBM * kSlabBytes;
 constexpr int kEpiWarps = 8;  // two per TMEM lane group, each takes half of the tile's columns
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kStagePitch = 36;  // words per staged row: 32 + 4 keeps 128-bit accesses conflict-free
-constexpr int kEpiStageBytes = kEpiWarps * 32 * kStagePitch * 4;
+constexpr int kStoreBoxBytes = 32 * 128;  // the TMA-store box of one epilogue warp: 32 rows x 128 bytes (128B swizzle)
+constexpr int kEpiWarpStageBytes = 2 * kStoreBoxBytes;  // two boxes per warp, so a store drains while the next box is filled
+constexpr int kEpiStageBytes = kEpiWarps * kEpiWarpStageBytes;
+static_assert(kEpiWarpStageBytes >= 32 * kStagePitch * 4, "the plain-store path stages one 32 x 36-word block in the same area");
 constexpr int kColStashBytes = kEpiWarps * 2 * 256 * 4;  // per epilogue warp: scale and bias of the tile's columns
 constexpr int kSmemBudget = 150 * 1024;  // for the operand ring
 
@@ -24,16 +27,21 @@ struct TileCfg {
   static constexpr int kSmem = kStages * kStageBytes + kEpiStageBytes + kColStashBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
 };
 
-static __device__ int g_gemm_error;  // 0 = ok; else (role << 16) | block index bits
-
 struct GemmParams {
   int M, N, K;  // K in elements
   int num_kb;   // K slabs
   int tiles_m, tiles_n, batch;  // batch = nb0 * nb1
   int nb1;                      // extent of the inner batch dim
-  int dbg;  // tuning aid: bit 0 = epilogue skips math and stores, bit 1 = also skips the TMEM loads
+  int out_tma;  // 0: plain stores; 2 / 4: the output goes through TMA tile stores, value = its element size
+  int res_vec;  // the residual rows can be read with 16-byte loads
+  int *err;     // device error word: 0 = ok; else (role << 16) | block index bits
   GemmEpilogue epi;
 };
+
+__device__ __forceinline__ void report_error(const GemmParams &p, volatile int *abort_flag, int role) {
+  *abort_flag = 1;
+  atomicCAS(p.err, 0, (role << 16) | (int)(blockIdx.x & 0xffff));
+}
 
 // Instruction descriptor: c format [4,6) (1 = f32, 2 = s32), a format [7,10), b format [10,13)
 // (f16 kinds: 0 f16, 1 bf16; i8: 1 = signed), a/b major [15],[16] (0 = K-major),

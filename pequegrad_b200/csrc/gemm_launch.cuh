@@ -1,0 +1,146 @@
+// The persistent tcgen05 GEMM kernel and its launcher, instantiated once per instruction kind
+// (gemm_kind_*.cu) so that the kinds compile in parallel. Overview in gemm_sm100.cu.
+#pragma once
+#include <mutex>
+#include <string>
+
+#include "gemm_epilogue.cuh"
+
+namespace pgb {
+
+template <int KIND, int BN>
+__global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
+                                                                    const __grid_constant__ CUtensorMap tmap_b,
+                                                                    const __grid_constant__ CUtensorMap tmap_out,
+                                                                    const __grid_constant__ GemmParams p) {
+  using Cfg = TileCfg<BN>;
+  constexpr int STAGES = Cfg::kStages;
+  extern __shared__ uint8_t smem_raw[];
+  // a kernel of an earlier launch gave up on a wait: do nothing until the host has read and cleared the error
+  if (*(volatile int *)p.err != 0) return;
+  // 1024-byte alignment for the 128B-swizzled tiles
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  uint8_t *tiles = smem;
+  uint8_t *epi_stage = smem + STAGES * Cfg::kStageBytes;  // 1024-aligned: every stage is a multiple of 1024 bytes
+  float *col_stash = reinterpret_cast<float *>(smem + STAGES * Cfg::kStageBytes + kEpiStageBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::kStageBytes + kEpiStageBytes + kColStashBytes);
+  uint64_t *full = bars;                   // [STAGES]  TMA -> MMA
+  uint64_t *empty = bars + STAGES;         // [STAGES]  MMA -> TMA
+  uint64_t *acc_full = bars + 2 * STAGES;  // [2]       MMA -> epilogue
+  uint64_t *acc_empty = acc_full + 2;      // [2]       epilogue -> MMA
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  constexpr int ES = (KIND == GEMM_I8) ? 1 : 2;
+  constexpr int SLAB_ELEMS = kSlabBytes / ES;
+  const int tiles_per_batch = p.tiles_m * p.tiles_n;
+  const int num_tiles = tiles_per_batch * p.batch;
+
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
+    for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kEpiWarps); }
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, Cfg::kTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_a) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_b) : "memory");
+      uint32_t phase = 0;
+      int s = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x) {
+        const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
+        const int m0 = (rem / p.tiles_n) * kBM, n0 = (rem % p.tiles_n) * BN;
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) {
+            report_error(p, abort_flag, 1);
+            ok = false;
+            break;
+          }
+          mbar_expect_tx(&full[s], Cfg::kStageBytes);
+          uint8_t *sa = tiles + s * Cfg::kStageBytes;
+          tma_load_4d(sa, &tmap_a, kb * SLAB_ELEMS, m0, bz % p.nb1, bz / p.nb1, &full[s]);
+          tma_load_4d(sa + kTileABytes, &tmap_b, kb * SLAB_ELEMS, n0, bz % p.nb1, bz / p.nb1, &full[s]);
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc = make_idesc<KIND, BN>();
+      uint32_t phase = 0;
+      int s = 0, it = 0;
+      bool ok = true;
+      for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
+        const int buf = it & 1;
+        // the epilogue must have drained this accumulator (its use two tiles ago)
+        if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) {
+          report_error(p, abort_flag, 4);
+          break;
+        }
+        tc_fence_after();
+        const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
+        for (int kb = 0; kb < p.num_kb; ++kb) {
+          if (!mbar_wait(&full[s], phase, abort_flag)) {
+            report_error(p, abort_flag, 2);
+            ok = false;
+            break;
+          }
+          tc_fence_after();
+          const uint32_t sa = smem_u32(tiles + s * Cfg::kStageBytes);
+          const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kTileABytes);
+#pragma unroll
+          for (int kk = 0; kk < kSlabBytes / 32; ++kk)  // one MMA consumes 32 bytes of K: +2 in 16-byte units
+            tc_mma<KIND>(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
+          tc_commit(&empty[s]);  // frees the stage when these MMAs have read it
+          if (++s == STAGES) { s = 0; phase ^= 1; }
+        }
+        if (ok) tc_commit(&acc_full[buf]);
+      }
+    }
+  } else {
+    const int q = warp & 3;   // a warp may read TMEM lanes 32*(warp%4) .. +31
+    const int ew = warp - 2;  // 0..7; warps ew and ew+4 share a lane group and split the columns
+    if (lane == 0 && p.out_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
+    gemm_epilogue_warp<KIND, BN>(p, &tmap_out, tmem_base, epi_stage + ew * kEpiWarpStageBytes, col_stash + ew * 512, ew >> 2, acc_full, acc_empty,
+                                 abort_flag, q, lane, num_tiles, tiles_per_batch);
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
+}
+
+template <int KIND, int BN>
+static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const GemmParams &p, int grid, cudaStream_t stream) {
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] {
+    attr_err = cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::kSmem);
+  });
+  if (attr_err != cudaSuccess) {
+    set_error(std::string("matmul: cannot raise the shared-memory limit: ") + cudaGetErrorString(attr_err));
+    return PGB_ERR_CUDA;
+  }
+  gemm_tc_kernel<KIND, BN><<<grid, kGemmThreads, TileCfg<BN>::kSmem, stream>>>(ma, mb, mo, p);
+  count_launch();
+  return check_launch("gemm_tc_kernel");
+}
+
+template <int KIND>
+int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const GemmParams &p, int grid,
+                   cudaStream_t stream) {
+  if (bn == 256) return launch_gemm<KIND, 256>(ma, mb, mo, p, grid, stream);
+  if (bn == 128) return launch_gemm<KIND, 128>(ma, mb, mo, p, grid, stream);
+  return launch_gemm<KIND, 32>(ma, mb, mo, p, grid, stream);
+}
+
+}  // namespace pgb

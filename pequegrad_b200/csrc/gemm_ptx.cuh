@@ -110,12 +110,27 @@ __device__ __forceinline__ void mbar_arrive(uint64_t *bar) {
   asm volatile("mbarrier.arrive.shared::cta.b64 _, [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+// TMA tile store shared -> global (bulk async group of the issuing thread). The tensor map clips the box
+// at the tensor's extents, so ragged right / bottom edges need no special case.
+__device__ __forceinline__ void tma_store_4d(const CUtensorMap *tmap, const void *smem_src, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.tensor.4d.global.shared::cta.bulk_group [%0, {%2, %3, %4, %5}], [%1];" ::"l"(tmap), "r"(smem_u32(smem_src)),
+               "r"(x), "r"(y), "r"(z), "r"(w)
+               : "memory");
+}
+__device__ __forceinline__ void tma_store_commit() { asm volatile("cp.async.bulk.commit_group;" ::: "memory"); }
+// waits until at most N of this thread's bulk groups still have to READ their shared-memory source
+template <int N>
+__device__ __forceinline__ void tma_store_wait_read() { asm volatile("cp.async.bulk.wait_group.read %0;" ::"n"(N) : "memory"); }
+__device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bulk.wait_group 0;" ::: "memory"); }
+// makes this thread's generic-proxy writes to shared memory visible to the async proxy (TMA)
+__device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
+
 __device__ __forceinline__ float gelu_tanh(float x) {
-  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))), tanh(z) = 2 / (1 + exp(-2z)) - 1
-  // (pequegrad/ops.py:109-118, 159-164)
+  // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) with tanh(z) = 2 / (1 + exp(-2z)) - 1, i.e.
+  // x / (1 + exp(-2z))  (pequegrad/ops.py:109-118, 159-164). exp and the reciprocal are the hardware
+  // approximations (about 2 ulp each), far inside the 16-bit tolerance of the outputs this feeds.
   const float z = 0.7978845608028654f * (x + 0.044715f * x * x * x);
-  const float t = 2.0f / (1.0f + expf(-2.0f * z)) - 1.0f;
-  return 0.5f * x * (1.0f + t);
+  return __fdividef(x, 1.0f + __expf(-2.0f * z));
 }
 
 }  // namespace pgb
