@@ -221,12 +221,102 @@ static int ew_generic(const CanonEw &c, const pgb_tensor *in, int n_in, const pg
   return check_launch("ew_generic_kernel");
 }
 
+// ---------------------------------------------------------------------------
+// Copy of a permuted view whose contiguous dim is not the output's inner dim (`as_contiguous`
+// of a transpose, csrc/cuda/copy.cu of the reference does it element by element). 64 x 64
+// tiles go through shared memory so that both the reads (along the input's contiguous dim i)
+// and the writes (along the output's inner dim j) are coalesced; the other dims are a batch.
+struct EwTrParams {
+  const void *in;
+  void *out;
+  int nd_b;
+  int64_t bsize[3], bin[3], bout[3];
+  int64_t ni, nj, in_sj, out_si, tiles_i, tiles_j;
+};
+
+template <typename E>
+__global__ void __launch_bounds__(256) ew_transpose_kernel(const __grid_constant__ EwTrParams p) {
+  __shared__ E tile[64][64 + (sizeof(E) == 2 ? 2 : 1)];  // odd pitch in 32-bit words: conflict-free column reads
+  int64_t b = blockIdx.x;
+  const int64_t tj = b % p.tiles_j;
+  b /= p.tiles_j;
+  const int64_t ti = b % p.tiles_i;
+  b /= p.tiles_i;
+  int64_t ioff = 0, ooff = 0;
+  for (int d = p.nd_b - 1; d >= 0; --d) {
+    const int64_t c = b % p.bsize[d];
+    b /= p.bsize[d];
+    ioff += c * p.bin[d];
+    ooff += c * p.bout[d];
+  }
+  const E *src = (const E *)p.in + ioff;
+  E *dst = (E *)p.out + ooff;
+  const int tx = threadIdx.x & 63, ty = threadIdx.x >> 6;
+  const int64_t i0 = ti * 64, j0 = tj * 64;
+#pragma unroll 4
+  for (int r = ty; r < 64; r += 4) {
+    const int64_t i = i0 + tx, j = j0 + r;
+    if (i < p.ni && j < p.nj) tile[r][tx] = src[j * p.in_sj + i];
+  }
+  __syncthreads();
+#pragma unroll 4
+  for (int r = ty; r < 64; r += 4) {
+    const int64_t i = i0 + r, j = j0 + tx;
+    if (i < p.ni && j < p.nj) dst[i * p.out_si + j] = tile[tx][r];
+  }
+}
+
+// Returns 1 if the transposing copy was launched, 0 if the call is not of that shape.
+static int ew_try_transpose(const CanonEw &c, const pgb_tensor *in, int n_in, const pgb_tensor *out, int n_out, const pgb_instr *prog, int n,
+                            const int16_t *out_vals, cudaStream_t stream) {
+  if (n_in != 1 || n_out != 1 || n != 1 || prog[0].op != PGB_OP_LOAD || prog[0].a != 0 || out_vals[0] != 0) return 0;
+  if (in[0].dtype != out[0].dtype || c.nd < 2 || c.nd > 5) return 0;
+  const int es = dtype_size(in[0].dtype);
+  if (es != 2 && es != 4) return 0;
+  const int j = c.nd - 1;
+  if (c.in[0][j] == 1 || c.in[0][j] == 0) return 0;
+  int t = -1;
+  for (int d = 0; d < j; ++d)
+    if (c.in[0][d] == 1) t = d;
+  if (t < 0) return 0;
+  EwTrParams p{};
+  p.in = in[0].data;
+  p.out = out[0].data;
+  int64_t ostride[PGB_MAX_DIMS];
+  int64_t acc = 1;
+  for (int d = c.nd - 1; d >= 0; --d) { ostride[d] = acc; acc *= c.size[d]; }
+  int64_t batch = 1;
+  for (int d = 0; d < j; ++d) {
+    if (d == t) continue;
+    p.bsize[p.nd_b] = c.size[d];
+    p.bin[p.nd_b] = c.in[0][d];
+    p.bout[p.nd_b] = ostride[d];
+    ++p.nd_b;
+    batch *= c.size[d];
+  }
+  p.ni = c.size[t];
+  p.nj = c.size[j];
+  p.in_sj = c.in[0][j];
+  p.out_si = ostride[t];
+  p.tiles_i = (p.ni + 63) / 64;
+  p.tiles_j = (p.nj + 63) / 64;
+  const int64_t grid = p.tiles_i * p.tiles_j * batch;
+  if (grid <= 0 || grid > 2147483647LL) return 0;
+  if (es == 2) ew_transpose_kernel<uint16_t><<<(unsigned)grid, 256, 0, stream>>>(p);
+  else ew_transpose_kernel<uint32_t><<<(unsigned)grid, 256, 0, stream>>>(p);
+  count_launch();
+  const int st = check_launch("ew_transpose_kernel");
+  return st == PGB_OK ? 1 : st;
+}
+
 int run_fused_elementwise(const pgb_tensor *in, int n_in, const pgb_tensor *out, int n_out, const pgb_instr *prog, int n,
                           const int16_t *out_vals, cudaStream_t stream) {
   CanonEw c;
   std::string err = canonicalise_elementwise(in, n_in, &out[0], c);
   if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
   if (c.numel == 0) return PGB_OK;
+  const int tr = ew_try_transpose(c, in, n_in, out, n_out, prog, n, out_vals, stream);
+  if (tr != 0) return tr == 1 ? PGB_OK : tr;
   const int cdtype = compute_dtype(in, n_in, out[0].dtype);
   const int r = ew_try_fast(c, in, n_in, out, n_out, prog, n, out_vals, cdtype, stream);
   if (r != 0) return r == 1 ? PGB_OK : r;

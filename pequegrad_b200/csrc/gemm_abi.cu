@@ -80,6 +80,7 @@ PGB_API int pgb_absmax_f32(const pgb_tensor *x, float *absmax_dev, void *stream)
   if (!x || !absmax_dev) { set_error("absmax: null argument"); return PGB_ERR_INVALID_ARG; }
   if (x->dtype != PGB_F32) { set_error(std::string("absmax not implemented for ") + dtype_name(x->dtype)); return PGB_ERR_UNSUPPORTED; }
   if (!is_contiguous(*x)) { set_error("absmax: the tensor must be contiguous"); return PGB_ERR_UNSUPPORTED; }
+  if (reinterpret_cast<uintptr_t>(x->data) & 15) { set_error("absmax: the tensor must be 16-byte aligned"); return PGB_ERR_UNSUPPORTED; }
   if (!device_present()) return PGB_ERR_CUDA;
   return run_absmax_f32((const float *)x->data, numel_of(*x), absmax_dev, (cudaStream_t)stream);
 }
@@ -90,6 +91,10 @@ PGB_API int pgb_quantize_i8(const pgb_tensor *x, const float *absmax_dev, float 
   if (!is_contiguous(*x) || !is_contiguous(*q) || numel_of(*x) != numel_of(*q)) {
     set_error("quantize: input and output must be contiguous and of one size");
     return PGB_ERR_INVALID_ARG;
+  }
+  if ((reinterpret_cast<uintptr_t>(x->data) & 15) || (reinterpret_cast<uintptr_t>(q->data) & 3)) {
+    set_error("quantize: the input must be 16-byte and the output 4-byte aligned");
+    return PGB_ERR_UNSUPPORTED;
   }
   if (!absmax_dev && !(scale > 0.f)) { set_error("quantize: a positive scale or a device absmax is required"); return PGB_ERR_INVALID_ARG; }
   if (!device_present()) return PGB_ERR_CUDA;

@@ -24,34 +24,42 @@ __global__ void __launch_bounds__(256) absmax_f32_kernel(const float *__restrict
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int *>(out), __float_as_uint(m));
 }
 
+__device__ __forceinline__ uint32_t quantize4(const float4 v, float s) {
+  const float f[4] = {v.x, v.y, v.z, v.w};
+  uint32_t pk = 0;
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    float r = rintf(__fdiv_rn(f[e], s));
+    r = fminf(fmaxf(r, -127.f), 127.f);
+    pk |= ((uint32_t)(uint8_t)(int8_t)(int)r) << (8 * e);
+  }
+  return pk;
+}
+
+// One float4 in, one packed word out per thread and step: a warp reads 512 and writes 128 contiguous
+// bytes. Four independent steps are in flight per thread.
 __global__ void __launch_bounds__(256) quantize_i8_kernel(const float *__restrict__ x, int64_t n, const float *__restrict__ absmax,
                                                           float scale_host, int8_t *__restrict__ q) {
   const float s = absmax ? fmaxf(__ldg(absmax), 1e-6f) / 127.0f : scale_host;
-  const int64_t stride = (int64_t)gridDim.x * 256 * 16;
-  for (int64_t i = ((int64_t)blockIdx.x * 256 + threadIdx.x) * 16; i < n; i += stride) {
-    if (i + 15 < n) {
-      uint32_t w[4];
+  const int64_t nvec = n >> 2;
+  const int64_t stride = (int64_t)gridDim.x * 256;
+  const float4 *x4 = reinterpret_cast<const float4 *>(x);
+  uint32_t *q4 = reinterpret_cast<uint32_t *>(q);
+  int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
+  for (; i + 3 * stride < nvec; i += 4 * stride) {
+    float4 v[4];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
-        const float4 v = __ldcs(reinterpret_cast<const float4 *>(x + i + 4 * g));
-        const float f[4] = {v.x, v.y, v.z, v.w};
-        uint32_t pk = 0;
+    for (int u = 0; u < 4; ++u) v[u] = __ldcs(x4 + i + u * stride);
 #pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          float r = rintf(__fdiv_rn(f[e], s));
-          r = fminf(fmaxf(r, -127.f), 127.f);
-          pk |= ((uint32_t)(uint8_t)(int8_t)(int)r) << (8 * e);
-        }
-        w[g] = pk;
-      }
-      *reinterpret_cast<uint4 *>(q + i) = make_uint4(w[0], w[1], w[2], w[3]);
-    } else {
-      for (int64_t j = i; j < n; ++j) {
-        float r = rintf(__fdiv_rn(x[j], s));
-        r = fminf(fmaxf(r, -127.f), 127.f);
-        q[j] = (int8_t)(int)r;
-      }
-    }
+    for (int u = 0; u < 4; ++u) q4[i + u * stride] = quantize4(v[u], s);
+  }
+  for (; i < nvec; i += stride) q4[i] = quantize4(__ldcs(x4 + i), s);
+  // the last n % 4 elements
+  if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
+    const int64_t j = (nvec << 2) + threadIdx.x;
+    float r = rintf(__fdiv_rn(x[j], s));
+    r = fminf(fmaxf(r, -127.f), 127.f);
+    q[j] = (int8_t)(int)r;
   }
 }
 
@@ -68,9 +76,10 @@ int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream) {
 
 int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float scale, int8_t *q, cudaStream_t stream) {
   if (n <= 0) return PGB_OK;
-  int64_t grid = (n + 4095) / 4096;
-  const int64_t cap = (int64_t)sm_count() * 16;
+  int64_t grid = (n + 4095) / 4096;  // 4 vectors of 4 elements per thread
+  const int64_t cap = (int64_t)sm_count() * 32;
   if (grid > cap) grid = cap;
+  if (grid < 1) grid = 1;
   quantize_i8_kernel<<<(unsigned)grid, 256, 0, stream>>>(x, n, absmax_dev, scale, q);
   count_launch();
   return check_launch("quantize_i8_kernel");

@@ -32,7 +32,18 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// One warp per row, the row held in NV vectors of V elements per lane.
+// e^d for d <= 0 as 2^(d * log2 e) on the special-function unit: one multiply and one ex2.approx
+// (2 ulp). The rounding of the product adds |d| * 1e-7 relative error, below 2e-6 for |d| < 20;
+// e^(-inf) = 0, so masked elements need no special case.
+__device__ __forceinline__ float exp_nonpos(float d) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d * 1.4426950408889634f));
+  return r;
+}
+
+// One warp per row, the row held in NV vectors of V elements per lane. With a causal mask the
+// vectors that lie wholly above the diagonal are neither loaded nor exponentiated (the test is
+// warp-uniform); they are stored as zeros.
 template <typename IoT, int V, int NV>
 __global__ void __launch_bounds__(256) softmax_warp_kernel(const __grid_constant__ RowsParams p) {
   const int lane = threadIdx.x & 31;
@@ -40,14 +51,18 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const __grid_constant
   if (row >= p.rows) return;
   const IoT *xr = (const IoT *)p.x + row * p.C;
   IoT *yr = (IoT *)p.y + row * p.C;
+  const int C = (int)p.C;  // at most 16 * 32 * V here
   // number of columns that take part (the rest are masked out)
-  int64_t L = p.C;
-  if (p.causal_rows > 0) L = min(p.C, (row % p.causal_rows) + 1);
+  int L = C;
+  if (p.causal_rows > 0) {
+    const int64_t r = p.rows <= 0xffffffffLL ? (int64_t)((uint32_t)row % (uint32_t)p.causal_rows) : row % p.causal_rows;
+    L = (int)min((int64_t)C, r + 1);
+  }
   float v[NV][V];
   float m = -INFINITY;
 #pragma unroll
   for (int u = 0; u < NV; ++u) {
-    const int64_t c = ((int64_t)u * 32 + lane) * V;
+    const int c = (u * 32 + lane) * V;
     if (c < L) {
       load_vec<float, IoT, V>(xr + c, v[u]);
 #pragma unroll
@@ -63,21 +78,28 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const __grid_constant
   m = warp_max(m);
   float s = 0.f;
 #pragma unroll
-  for (int u = 0; u < NV; ++u)
+  for (int u = 0; u < NV; ++u) {
+    if (u * 32 * V < L) {  // warp-uniform
 #pragma unroll
-    for (int e = 0; e < V; ++e) {
-      const float ex = (v[u][e] == -INFINITY) ? 0.f : expf(v[u][e] - m);
-      v[u][e] = ex;
-      s += ex;
+      for (int e = 0; e < V; ++e) {
+        const float ex = exp_nonpos(v[u][e] - m);
+        v[u][e] = ex;
+        s += ex;
+      }
+    } else {
+#pragma unroll
+      for (int e = 0; e < V; ++e) v[u][e] = 0.f;
     }
+  }
   s = warp_sum(s);
+  const float inv = 1.0f / s;  // v * (1/s) is within 1 ulp of the composite's v / s
 #pragma unroll
   for (int u = 0; u < NV; ++u) {
-    const int64_t c = ((int64_t)u * 32 + lane) * V;
-    if (c < p.C) {
+    const int c = (u * 32 + lane) * V;
+    if (c < C) {
       float o[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) o[e] = v[u][e] / s;
+      for (int e = 0; e < V; ++e) o[e] = v[u][e] * inv;
       store_vec<IoT, float, V>(yr + c, o);
     }
   }
@@ -106,7 +128,7 @@ __global__ void __launch_bounds__(256) softmax_cta_kernel(const __grid_constant_
   float s = 0.f;
   for (int64_t c = threadIdx.x; c < L; c += 256) {
     const float xv = to_compute<float, IoT>(xr[c]);
-    s += (xv == -INFINITY) ? 0.f : expf(xv - m);
+    s += exp_nonpos(xv - m);
   }
   s = warp_sum(s);
   __syncthreads();
@@ -114,13 +136,10 @@ __global__ void __launch_bounds__(256) softmax_cta_kernel(const __grid_constant_
   __syncthreads();
   if (threadIdx.x == 0) { float t = 0.f; for (int i = 0; i < 8; ++i) t += red[i]; bc = t; }
   __syncthreads();
-  s = bc;
+  s = 1.0f / bc;
   for (int64_t c = threadIdx.x; c < p.C; c += 256) {
     float o = 0.f;
-    if (c < L) {
-      const float xv = to_compute<float, IoT>(xr[c]);
-      o = ((xv == -INFINITY) ? 0.f : expf(xv - m)) / s;
-    }
+    if (c < L) o = exp_nonpos(to_compute<float, IoT>(xr[c]) - m) * s;
     yr[c] = from_compute<IoT, float>(o);
   }
 }
@@ -161,14 +180,14 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const __grid_consta
     }
   }
   const float var = warp_sum(q) / n;
-  const float sd = sqrtf(var + p.eps);
+  const float rsd = 1.0f / sqrtf(var + p.eps);  // d * (1/sd) is within 1 ulp of the composite's d / sd
 #pragma unroll
   for (int u = 0; u < NV; ++u) {
     const int64_t c = ((int64_t)u * 32 + lane) * V;
     if (c < p.C) {
       float o[V];
 #pragma unroll
-      for (int e = 0; e < V; ++e) o[e] = v[u][e] / sd;
+      for (int e = 0; e < V; ++e) o[e] = v[u][e] * rsd;
       if (p.gamma) {
         float g[V];
         load_vec_cached<float, IoT, V>((const IoT *)p.gamma + c, g);

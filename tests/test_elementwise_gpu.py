@@ -117,3 +117,21 @@ def test_large_contiguous_and_errors():
         K.fused_elementwise([x], [("LOAD", 1)])
     with pytest.raises(ValueError):
         K.fused_elementwise([x], [("LOAD", 0)], shape=(5,))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16, torch.int32])
+@pytest.mark.parametrize("shape,perm", [((70, 130), (1, 0)), ((3, 65, 7, 64), (0, 2, 3, 1)), ((2, 5, 100, 64), (0, 1, 3, 2)),
+                                        ((2, 3, 4, 33, 65), (2, 0, 1, 4, 3)), ((1, 129, 1, 63), (3, 2, 1, 0))])
+def test_copy_of_a_permuted_view_is_bit_exact(shape, perm, dtype):
+    # `as_contiguous` of a transpose: the tiled shared-memory path (input contiguous along another dim than the output)
+    g = torch.Generator().manual_seed(11)
+    x = (torch.randn(shape, generator=g) * 100).to(dtype).cuda()
+    v = x.permute(perm)
+    (got,) = K.fused_elementwise([v], [("LOAD", 0)])
+    assert got.is_contiguous() and got.shape == v.shape
+    assert torch.equal(got, v.contiguous())
+    # a sliced, permuted view (the V of an attention head inside a packed qkv buffer)
+    if len(shape) == 4:
+        w = x[..., : shape[-1] // 2 + 1].permute(perm)
+        (got,) = K.fused_elementwise([w], [("LOAD", 0)])
+        assert torch.equal(got, w.contiguous())
