@@ -262,6 +262,21 @@ PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tenso
                        const pgb_tensor *residual, const pgb_tensor *out, void *stream);
 
 /*
+ * Fused scaled-dot-product attention: out = softmax(scale * q @ k^T [+ causal mask]) @ v in ONE
+ * kernel; the [T, Tk] scores stay in tensor memory. Replaces the composite of the reference's
+ * GPT-2 block (examples/gpt2.py:168-186: matmul, mask add, softmax of pequegrad/ops.py:259-267,
+ * matmul), i.e. MatMul::dispatch_cuda twice (csrc/cuda/matmul.cu:72-163) around the softmax chain.
+ *   q    [B, H, T, 64]   f16 or bf16, any view with a contiguous last dim (e.g. a slice of a packed
+ *   k,v  [B, H, Tk, 64]  qkv buffer seen as [B, T, H, 64] and permuted); fewer leading dims are allowed
+ *   out  [B, H, T, 64]   same dtype, a view with a contiguous last dim
+ *   causal != 0: key j takes part in query row i only if j <= i (the -inf mask above the diagonal)
+ * Base addresses and the row / head / batch pitches must be multiples of 16 bytes; other head
+ * dims and dtypes return PGB_ERR_UNSUPPORTED. fp32 accumulation and fp32 softmax statistics.
+ */
+PGB_API int pgb_attention(const pgb_tensor *q, const pgb_tensor *k, const pgb_tensor *v, float scale, int causal, const pgb_tensor *out,
+                          void *stream);
+
+/*
  * int8 quantized linear: acc = a_i8 @ w_i8^T in int32 (exact), then
  *   out = act(float(acc) * (a_scale * w_scale[n]) + bias[n])   in fp32, in that association.
  * The reference has no int8 type; its quantized example fake-quantizes weights in

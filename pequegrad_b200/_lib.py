@@ -57,7 +57,7 @@ EXPORTS = [
     "pgb_status_string", "pgb_last_error", "pgb_version", "pgb_launch_count",
     "pgb_fused_elementwise", "pgb_fused_reduce", "pgb_fused_reduce_workspace", "pgb_fused_reduce_describe",
     "pgb_softmax_rows", "pgb_layernorm_rows", "pgb_fused_reduce_noalloc",
-    "pgb_embedding_rows", "pgb_matmul", "pgb_qlinear_i8", "pgb_absmax_f32", "pgb_quantize_i8", "pgb_device_error",
+    "pgb_embedding_rows", "pgb_matmul", "pgb_attention", "pgb_qlinear_i8", "pgb_absmax_f32", "pgb_quantize_i8", "pgb_device_error",
 ]
 NOALLOC_SCRATCH_BYTES = 4 << 20  # PGB_NOALLOC_SCRATCH_BYTES
 
@@ -90,6 +90,7 @@ def lib() -> C.CDLL:
                                            C.c_void_p]
     L.pgb_embedding_rows.argtypes = [TP, TP, TP, C.c_int64, TP, C.c_void_p]
     L.pgb_matmul.argtypes = [TP, TP, TP, C.c_int, C.c_float, TP, TP, C.c_void_p]
+    L.pgb_attention.argtypes = [TP, TP, TP, C.c_float, C.c_int, TP, C.c_void_p]
     L.pgb_qlinear_i8.argtypes = [TP, TP, C.c_void_p, C.c_float, C.c_void_p, TP, C.c_int, TP, TP, C.c_void_p, C.c_void_p]
     L.pgb_absmax_f32.argtypes = [TP, C.c_void_p, C.c_void_p]
     L.pgb_quantize_i8.argtypes = [TP, C.c_void_p, C.c_float, TP, C.c_void_p]

@@ -1,0 +1,369 @@
+// Fused scaled-dot-product attention (forward) for head dim 64 on the 5th-generation tensor cores.
+//
+// Replaces the composite of the reference's GPT-2 block (examples/gpt2.py:168-186): scores = q @ k^T / sqrt(d),
+// additive causal mask, softmax (pequegrad/ops.py:259-267), att @ v, which runs as four kernel chains and
+// materialises the [B, H, T, T] scores twice. Here the scores never leave the SM:
+//   one CTA per (batch, head, block of 128 query rows); keys and values stream in blocks of 64
+//   warp 0      TMA producer: Q once, then K and V blocks into two rings (128B swizzle, no multicast)
+//   warp 1      allocates TMEM and issues tcgen05.mma (one thread):
+//                 S = Q K^T    128 x 64 x 64, fp32 in TMEM, double-buffered
+//                 O += P V     128 x 64 x 64, fp32 in TMEM; V is read as an MN-major operand, so it needs no transpose
+//   warps 2-5   softmax: thread = query row. tcgen05.ld the row of S, mask, online max / sum with exp2 on the
+//               SFU, rescale the row of O in TMEM when its max grew, write P (16-bit) to shared memory in the
+//               K-major 128B-swizzled operand layout for the PV MMA; at the end O / sum -> global
+// Two CTAs fit per SM (about 100 KB of shared memory and 256 TMEM columns each), so one CTA's MMAs run under
+// the other's exponentials. Every wait is bounded; a timeout sets the device error word and the CTA drains.
+#include <cuda_bf16.h>
+#include <cuda_fp16.h>
+
+#include <algorithm>
+#include <cmath>
+#include <cstdlib>
+#include <mutex>
+#include <string>
+
+#include "gemm_ptx.cuh"
+#include "reduce_common.cuh"
+
+namespace pgb {
+
+constexpr int kQB = 128;  // query rows per CTA
+constexpr int kKB = 64;   // keys per block
+constexpr int kHD = 64;   // head dim
+constexpr int kKStages = 4, kVStages = 4;
+constexpr int kAttnThreads = 192;
+constexpr int kQBytes = kQB * kHD * 2, kKVBytes = kKB * kHD * 2, kPBytes = kQB * kKB * 2;
+constexpr int kAttnSmem = kQBytes + (kKStages + kVStages) * kKVBytes + kPBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kAttnTmemCols = 256;  // S0 [0,64), S1 [64,128), O [128,192)
+
+struct AttnParams {
+  int T, Tk, H, B, n_qblk;
+  int causal;
+  int is_half;  // 1 = f16, 0 = bf16
+  float c;      // scale * log2(e)
+  void *out;
+  int64_t o_row, o_head, o_batch;  // output strides in elements
+  int *err;
+  uint32_t v_lbo;
+};
+
+// f16 / bf16 instruction descriptor, M = 128, N = 64, fp32 accumulate; bit 16 = B operand is MN-major
+__device__ __forceinline__ uint32_t attn_idesc(bool is_half, bool b_mn_major) {
+  uint32_t d = 0;
+  const uint32_t fmt = is_half ? 0u : 1u;
+  d |= 1u << 4;
+  d |= fmt << 7;
+  d |= fmt << 10;
+  if (b_mn_major) d |= 1u << 16;
+  d |= (uint32_t)(64 >> 3) << 17;
+  d |= (uint32_t)(128 >> 4) << 24;
+  return d;
+}
+
+__device__ __forceinline__ float ex2f(float x) {
+  float r;
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
+  return r;
+}
+
+__device__ __forceinline__ uint32_t pack_pair(float lo, float hi, bool is_h) {
+  if (is_h) {
+    const __half2 h = __floats2half2_rn(lo, hi);
+    return *reinterpret_cast<const uint32_t *>(&h);
+  }
+  const __nv_bfloat162 b = __floats2bfloat162_rn(lo, hi);
+  return *reinterpret_cast<const uint32_t *>(&b);
+}
+
+__device__ __forceinline__ void attn_fail(const AttnParams &p, volatile int *abort_flag, int role) {
+  *abort_flag = 1;
+  atomicCAS(p.err, 0, ((8 + role) << 16) | (int)(blockIdx.x & 0xffff));
+}
+
+__global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
+                                                                        const __grid_constant__ CUtensorMap map_k,
+                                                                        const __grid_constant__ CUtensorMap map_v,
+                                                                        const __grid_constant__ AttnParams p) {
+  extern __shared__ uint8_t smem_raw[];
+  if (*(volatile int *)p.err != 0) return;
+  const uint32_t raw = smem_u32(smem_raw);
+  uint8_t *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  uint8_t *q_s = smem;
+  uint8_t *k_s = q_s + kQBytes;
+  uint8_t *v_s = k_s + kKStages * kKVBytes;
+  uint8_t *p_s = v_s + kVStages * kKVBytes;
+  uint64_t *bars = reinterpret_cast<uint64_t *>(p_s + kPBytes);
+  uint64_t *q_full = bars;                   // [1]
+  uint64_t *k_full = bars + 1;               // [kKStages]
+  uint64_t *k_empty = k_full + kKStages;     // [kKStages]
+  uint64_t *v_full = k_empty + kKStages;     // [kVStages]
+  uint64_t *v_empty = v_full + kVStages;     // [kVStages]
+  uint64_t *s_full = v_empty + kVStages;     // [2]  MMA -> softmax
+  uint64_t *s_free = s_full + 2;             // [2]  softmax -> MMA (4 warps)
+  uint64_t *p_full = s_free + 2;             // [1]  softmax -> MMA (4 warps): P written, O rescaled
+  uint64_t *pv_done = p_full + 1;            // [1]  MMA -> softmax: P and V consumed, O updated
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pv_done + 1);
+  volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  // heavy query blocks (those with the most keys under a causal mask) are scheduled first
+  const int qb = p.n_qblk - 1 - (int)(blockIdx.x % p.n_qblk);
+  const int bh = (int)(blockIdx.x / p.n_qblk);
+  const int h = bh % p.H, b = bh / p.H;
+  const int q0 = qb * kQB;
+  int n_kb = (p.Tk + kKB - 1) / kKB;
+  if (p.causal) n_kb = min(n_kb, (min(q0 + kQB, p.T) - 1) / kKB + 1);
+
+  if (threadIdx.x == 0) {
+    mbar_init(q_full, 1);
+    for (int s = 0; s < kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
+    for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
+    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4); }
+    mbar_init(p_full, 4);
+    mbar_init(pv_done, 1);
+    *abort_flag = 0;
+    asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
+  }
+  if (warp == 1) tmem_alloc(tmem_slot, kAttnTmemCols);
+  tc_fence_before();
+  __syncthreads();
+  tc_fence_after();
+  const uint32_t tmem_base = *tmem_slot;
+
+  if (warp == 0) {
+    if (lane == 0) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
+      mbar_expect_tx(q_full, kQBytes);
+      tma_load_4d(q_s, &map_q, 0, q0, h, b, q_full);
+      for (int j = 0; j < n_kb; ++j) {
+        const int ks = j % kKStages, vs = j % kVStages;
+        if (!mbar_wait(&k_empty[ks], ((j / kKStages) & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 1); break; }
+        mbar_expect_tx(&k_full[ks], kKVBytes);
+        tma_load_4d(k_s + ks * kKVBytes, &map_k, 0, j * kKB, h, b, &k_full[ks]);
+        if (!mbar_wait(&v_empty[vs], ((j / kVStages) & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 2); break; }
+        mbar_expect_tx(&v_full[vs], kKVBytes);
+        tma_load_4d(v_s + vs * kKVBytes, &map_v, 0, j * kKB, h, b, &v_full[vs]);
+      }
+    }
+  } else if (warp == 1) {
+    if (lane == 0) {
+      const uint32_t idesc_s = attn_idesc(p.is_half != 0, false), idesc_pv = attn_idesc(p.is_half != 0, true);
+      const uint64_t dq = make_kmajor_sw128_desc(smem_u32(q_s)), dp = make_kmajor_sw128_desc(smem_u32(p_s));
+      bool ok = mbar_wait(q_full, 0, abort_flag);
+      if (!ok) attn_fail(p, abort_flag, 3);
+      // S(j) = Q K(j)^T into S buffer j & 1
+      auto issue_s = [&](int j) -> bool {
+        const int ks = j % kKStages, sb = j & 1;
+        if (!mbar_wait(&k_full[ks], (j / kKStages) & 1, abort_flag)) { attn_fail(p, abort_flag, 4); return false; }
+        if (!mbar_wait(&s_free[sb], ((j >> 1) & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 5); return false; }
+        tc_fence_after();
+        const uint64_t dk = make_kmajor_sw128_desc(smem_u32(k_s + ks * kKVBytes));
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk) tc_mma<GEMM_F16>(tmem_base + (uint32_t)(sb * 64), dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
+        tc_commit(&k_empty[ks]);
+        tc_commit(&s_full[sb]);
+        return true;
+      };
+      if (ok && n_kb > 0) ok = issue_s(0);
+      for (int j = 0; j < n_kb && ok; ++j) {
+        if (j + 1 < n_kb) {
+          ok = issue_s(j + 1);
+          if (!ok) break;
+        }
+        const int vs = j % kVStages;
+        if (!mbar_wait(p_full, j & 1, abort_flag)) { attn_fail(p, abort_flag, 6); break; }
+        if (!mbar_wait(&v_full[vs], (j / kVStages) & 1, abort_flag)) { attn_fail(p, abort_flag, 7); break; }
+        tc_fence_after();
+        const uint32_t v_addr = smem_u32(v_s + vs * kKVBytes);
+#pragma unroll
+        for (int kk = 0; kk < 4; ++kk)  // 16 keys per MMA: 32 bytes along P's rows, 16 rows of V
+          tc_mma<GEMM_F16>(tmem_base + 128u, dp + 2 * kk, make_mnmajor_sw128_desc(v_addr + kk * 2048, p.v_lbo), idesc_pv, (j | kk) != 0);
+        tc_commit(&v_empty[vs]);
+        tc_commit(pv_done);
+      }
+    }
+  } else {
+    const int quad = warp & 3;  // TMEM lanes 32*quad .. +31
+    const int row = quad * 32 + lane, qrow = q0 + row;
+    const bool is_h = p.is_half != 0;
+    const float c = p.c;
+    const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    float m = -INFINITY, l = 0.f;
+    bool ok = true;
+    for (int j = 0; j < n_kb; ++j) {
+      const int sb = j & 1;
+      if (lane == 0) ok = mbar_wait(&s_full[sb], (j >> 1) & 1, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok) { if (lane == 0) attn_fail(p, abort_flag, 8); break; }
+      tc_fence_after();
+      uint32_t sa[32], sbv[32];
+      tmem_ld32_issue(lane_addr + (uint32_t)(sb * 64), sa);
+      tmem_ld32_issue(lane_addr + (uint32_t)(sb * 64 + 32), sbv);
+      tmem_ld_wait();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&s_free[sb]);
+      float s[64];
+#pragma unroll
+      for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(sa[i]); s[32 + i] = __uint_as_float(sbv[i]); }
+      const int key0 = j * kKB;
+      if ((p.causal && key0 + kKB - 1 > q0) || key0 + kKB > p.Tk) {  // block-uniform: only edge blocks pay for the mask
+#pragma unroll
+        for (int i = 0; i < 64; ++i) {
+          const int key = key0 + i;
+          if ((p.causal && key > qrow) || key >= p.Tk) s[i] = -INFINITY;
+        }
+      }
+      float mx = s[0];
+#pragma unroll
+      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+      const float m_new = fmaxf(m, mx);
+      const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no key yet: every p is 0
+      const float alpha = ex2f((m - m_use) * c);
+      const float mc = m_use * c;
+      float sum = 0.f;
+      uint32_t pk[32];
+#pragma unroll
+      for (int i = 0; i < 64; i += 2) {
+        const float p0 = ex2f(fmaf(s[i], c, -mc)), p1 = ex2f(fmaf(s[i + 1], c, -mc));
+        sum += p0 + p1;
+        pk[i >> 1] = pack_pair(p0, p1, is_h);
+      }
+      l = l * alpha + sum;
+      m = m_new;
+      if (j > 0) {
+        // PV(j-1) must have consumed P and updated O before either is touched
+        if (lane == 0) ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok) { if (lane == 0) attn_fail(p, abort_flag, 9); break; }
+        tc_fence_after();
+        if (__any_sync(0xffffffffu, alpha != 1.0f)) {
+          // some row of this warp got a larger max: O_row *= 2^((m_old - m_new) c)
+#pragma unroll
+          for (int half = 0; half < 2; ++half) {
+            uint32_t o[32];
+            tmem_ld32_issue(lane_addr + 128u + (uint32_t)(half * 32), o);
+            tmem_ld_wait();
+#pragma unroll
+            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+            tmem_st32(lane_addr + 128u + (uint32_t)(half * 32), o);
+          }
+          tmem_st_wait();
+        }
+      }
+      // P row -> shared memory, K-major with the 128B swizzle: 16-byte chunk i of row r sits at chunk i ^ (r & 7)
+      uint8_t *prow = p_s + row * 128;
+#pragma unroll
+      for (int i = 0; i < 8; ++i)
+        *reinterpret_cast<uint4 *>(prow + ((i ^ (row & 7)) << 4)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+      fence_proxy_async();
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(p_full);
+    }
+    if (ok && n_kb > 0) {
+      if (lane == 0) ok = mbar_wait(pv_done, (n_kb - 1) & 1, abort_flag);
+      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+      if (!ok && lane == 0) attn_fail(p, abort_flag, 10);
+    }
+    if (ok) {
+      tc_fence_after();
+      const float inv = n_kb > 0 ? 1.0f / l : 0.f;
+      uint8_t *orow = reinterpret_cast<uint8_t *>(p.out) + ((int64_t)b * p.o_batch + (int64_t)h * p.o_head + (int64_t)qrow * p.o_row) * 2;
+#pragma unroll
+      for (int half = 0; half < 2; ++half) {
+        uint32_t o[32];
+        if (n_kb > 0) {
+          tmem_ld32_issue(lane_addr + 128u + (uint32_t)(half * 32), o);
+          tmem_ld_wait();
+        } else {
+#pragma unroll
+          for (int i = 0; i < 32; ++i) o[i] = 0u;
+        }
+        if (qrow < p.T) {
+#pragma unroll
+          for (int i = 0; i < 4; ++i) {
+            uint32_t w[4];
+#pragma unroll
+            for (int k = 0; k < 4; ++k)
+              w[k] = pack_pair(__uint_as_float(o[8 * i + 2 * k]) * inv, __uint_as_float(o[8 * i + 2 * k + 1]) * inv, is_h);
+            *reinterpret_cast<uint4 *>(orow + half * 64 + i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
+          }
+        }
+      }
+    }
+  }
+  tc_fence_before();
+  __syncthreads();
+  if (warp == 1) tmem_dealloc(tmem_base, kAttnTmemCols);
+}
+
+// ---- host side ---------------------------------------------------------------
+// q, k, v, out: [B, H, T, 64] views with a contiguous head dim; *_str = strides in elements of the
+// batch, head and row dims. Rows and all strides must be multiples of 8 elements (16 bytes).
+int run_attention(const void *q, const void *k, const void *v, void *out, int is_half, int64_t B, int64_t H, int64_t T, int64_t Tk,
+                  const int64_t q_str[3], const int64_t k_str[3], const int64_t v_str[3], const int64_t o_str[3], float scale, int causal,
+                  cudaStream_t stream) {
+  if (B <= 0 || H <= 0 || T <= 0) return PGB_OK;
+  if (!(scale > 0.f) || !std::isfinite(scale)) { set_error("attention: the scale must be positive and finite"); return PGB_ERR_INVALID_ARG; }
+  const int64_t n_qblk = (T + kQB - 1) / kQB;
+  if (T > 2147483647LL / 2 || Tk > 2147483647LL / 2 || B * H * n_qblk > 2147483647LL) {
+    set_error("attention: problem too large for one launch");
+    return PGB_ERR_UNSUPPORTED;
+  }
+  const void *ptrs[4] = {q, k, v, out};
+  const int64_t *strs[4] = {q_str, k_str, v_str, o_str};
+  for (int i = 0; i < 4; ++i) {
+    if ((reinterpret_cast<uintptr_t>(ptrs[i]) & 15) || strs[i][0] % 8 || strs[i][1] % 8 || strs[i][2] % 8 || strs[i][2] < kHD) {
+      set_error("attention: q, k, v and out must be 16-byte aligned with row, head and batch pitches that are multiples of 16 bytes");
+      return PGB_ERR_UNSUPPORTED;
+    }
+  }
+  const CUtensorMapDataType dt = is_half ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
+  CUtensorMap mq, mk, mv;
+  auto encode = [&](CUtensorMap *m, const void *ptr, const int64_t str[3], int64_t rows, uint32_t box_rows) {
+    // a dim of extent 1 still needs a valid stride
+    const uint64_t dims[4] = {(uint64_t)kHD, (uint64_t)rows, (uint64_t)H, (uint64_t)B};
+    const uint64_t row_b = (uint64_t)str[2] * 2;
+    const uint64_t head_b = H > 1 ? (uint64_t)str[1] * 2 : row_b * (uint64_t)rows;
+    const uint64_t batch_b = B > 1 ? (uint64_t)str[0] * 2 : head_b * (uint64_t)H;
+    const uint64_t strides[3] = {row_b, head_b, batch_b};
+    const uint32_t box[4] = {(uint32_t)kHD, box_rows, 1, 1};
+    return encode_map_4d(m, dt, ptr, dims, strides, box);
+  };
+  if (!encode(&mq, q, q_str, T, kQB) || !encode(&mk, k, k_str, Tk, kKB) || !encode(&mv, v, v_str, Tk, kKB)) {
+    set_error("attention: cuTensorMapEncodeTiled failed");
+    return PGB_ERR_CUDA;
+  }
+  static std::once_flag once;
+  static cudaError_t attr_err = cudaSuccess;
+  std::call_once(once, [] { attr_err = cudaFuncSetAttribute(attention_fwd_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, kAttnSmem); });
+  if (attr_err != cudaSuccess) {
+    set_error(std::string("attention: cannot raise the shared-memory limit: ") + cudaGetErrorString(attr_err));
+    return PGB_ERR_CUDA;
+  }
+  AttnParams p{};
+  p.T = (int)T;
+  p.Tk = (int)Tk;
+  p.H = (int)H;
+  p.B = (int)B;
+  p.n_qblk = (int)n_qblk;
+  p.causal = causal ? 1 : 0;
+  p.is_half = is_half ? 1 : 0;
+  p.c = scale * 1.4426950408889634f;
+  p.out = out;
+  p.o_batch = o_str[0];
+  p.o_head = o_str[1];
+  p.o_row = o_str[2];
+  p.err = gemm_error_word();
+  if (!p.err) { set_error("attention: cannot resolve the device error word"); return PGB_ERR_CUDA; }
+  p.v_lbo = 1024;
+  if (const char *e = getenv("PGB_ATTN_VLBO")) p.v_lbo = (uint32_t)atoi(e);  // bring-up aid
+  attention_fwd_kernel<<<(unsigned)(B * H * n_qblk), kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, p);
+  count_launch();
+  return check_launch("attention_fwd_kernel");
+}
+
+}  // namespace pgb

@@ -1,6 +1,7 @@
 // Shared between the tensor-core GEMM kernels (gemm_sm100.cu) and their entry
 // points (gemm_abi.cu).
 #pragma once
+#include <cuda.h>
 #include <cuda_runtime.h>
 #include <stdint.h>
 
@@ -37,5 +38,13 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
 int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream);
 int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float scale, int8_t *q, cudaStream_t stream);
 int read_gemm_error(int *out, bool reset);
+// The device error word of the current device (set by a kernel whose bounded wait ran out), or null.
+int *gemm_error_word();
+// 4-D tensor map with a 128B-swizzled box (dims innermost first, strides in bytes for dims 1..3). False on failure.
+bool encode_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, const uint64_t dims[4], const uint64_t strides[3],
+                   const uint32_t box[4]);
+int run_attention(const void *q, const void *k, const void *v, void *out, int is_half, int64_t B, int64_t H, int64_t T, int64_t Tk,
+                  const int64_t q_str[3], const int64_t k_str[3], const int64_t v_str[3], const int64_t o_str[3], float scale, int causal,
+                  cudaStream_t stream);
 
 }  // namespace pgb

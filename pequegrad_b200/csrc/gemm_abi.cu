@@ -101,6 +101,50 @@ PGB_API int pgb_quantize_i8(const pgb_tensor *x, const float *absmax_dev, float 
   return run_quantize_i8((const float *)x->data, numel_of(*x), absmax_dev, scale, (int8_t *)q->data, (cudaStream_t)stream);
 }
 
+// [.., T, 64] view -> batch / head / row strides in elements; leading dims are padded to [B, H, T, 64]
+static std::string as_heads(const pgb_tensor &t, const char *what, int64_t dims[3], int64_t str[3]) {
+  if (t.ndim < 2 || t.ndim > 4) return std::string("attention: ") + what + " must have 2 to 4 dims";
+  const int es = dtype_size(t.dtype);
+  if (t.shape[t.ndim - 1] != 64) return std::string("attention: only a head dim of 64 is implemented (") + what + ")";
+  if (t.stride_bytes[t.ndim - 1] != es) return std::string("attention: the head dim of ") + what + " must be contiguous";
+  for (int i = 0; i < 3; ++i) { dims[i] = 1; str[i] = 0; }
+  for (int d = 0; d < t.ndim - 1; ++d) {
+    const int slot = 3 - (t.ndim - 1) + d;
+    dims[slot] = t.shape[d];
+    if (t.stride_bytes[d] % es || t.stride_bytes[d] < 0) return std::string("attention: bad stride in ") + what;
+    str[slot] = t.stride_bytes[d] / es;
+  }
+  // dims of extent 1 take the stride a contiguous layout would give them
+  if (dims[2] == 1) str[2] = 64;
+  if (dims[1] == 1) str[1] = str[2] * dims[2];
+  if (dims[0] == 1) str[0] = str[1] * dims[1];
+  return "";
+}
+
+PGB_API int pgb_attention(const pgb_tensor *q, const pgb_tensor *k, const pgb_tensor *v, float scale, int causal, const pgb_tensor *out,
+                          void *stream) {
+  if (!q || !k || !v || !out) { set_error("attention: null tensor"); return PGB_ERR_INVALID_ARG; }
+  if (q->dtype != PGB_F16 && q->dtype != PGB_BF16) {
+    set_error(std::string("attention not implemented for ") + dtype_name(q->dtype));
+    return PGB_ERR_UNSUPPORTED;
+  }
+  if (k->dtype != q->dtype || v->dtype != q->dtype || out->dtype != q->dtype) { set_error("attention: q, k, v and out must share one dtype"); return PGB_ERR_INVALID_ARG; }
+  int64_t qd[3], kd[3], vd[3], od[3], qs[3], ks[3], vs[3], os[3];
+  std::string err = as_heads(*q, "q", qd, qs);
+  if (err.empty()) err = as_heads(*k, "k", kd, ks);
+  if (err.empty()) err = as_heads(*v, "v", vd, vs);
+  if (err.empty()) err = as_heads(*out, "out", od, os);
+  if (!err.empty()) { set_error(err); return err.find("only a head dim") != std::string::npos ? PGB_ERR_UNSUPPORTED : PGB_ERR_INVALID_ARG; }
+  if (kd[0] != qd[0] || kd[1] != qd[1] || vd[0] != qd[0] || vd[1] != qd[1] || vd[2] != kd[2] || od[0] != qd[0] || od[1] != qd[1] || od[2] != qd[2]) {
+    set_error("attention: q, k, v and out disagree on batch, heads or sequence length");
+    return PGB_ERR_INVALID_ARG;
+  }
+  if (qd[2] > 0 && kd[2] == 0) { set_error("attention: no keys"); return PGB_ERR_INVALID_ARG; }
+  if (!device_present()) return PGB_ERR_CUDA;
+  return run_attention(q->data, k->data, v->data, out->data, q->dtype == PGB_F16, qd[0], qd[1], qd[2], kd[2], qs, ks, vs, os, scale, causal,
+                       (cudaStream_t)stream);
+}
+
 PGB_API int pgb_qlinear_i8(const pgb_tensor *a, const pgb_tensor *w, const float *w_scale, float a_scale, const float *a_absmax_dev,
                            const pgb_tensor *bias, int relu, const pgb_tensor *out, const pgb_tensor *acc_i32, float *out_absmax_dev,
                            void *stream) {

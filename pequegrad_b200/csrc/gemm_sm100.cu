@@ -76,6 +76,18 @@ static int make_operand_map(CUtensorMap *map, const void *ptr, int kind, int64_t
   return PGB_OK;
 }
 
+bool encode_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, const uint64_t dims[4], const uint64_t strides[3],
+                   const uint32_t box[4]) {
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return false;
+  const cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
+  const cuuint64_t s[3] = {strides[0], strides[1], strides[2]};
+  const cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  return fn(map, dt, 4, const_cast<void *>(ptr), d, s, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
+            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
 // The output as a 4-D tensor map for TMA tile stores: {N, M, nb1, nb0} with a {128 bytes, 32 rows, 1, 1} box, 128B swizzle.
 // Returns false (and leaves the plain-store epilogue in charge) when the layout does not meet TMA's alignment rules.
 static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, int64_t N, int64_t nb0, int64_t nb1) {
@@ -99,7 +111,7 @@ static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, 
 // The device error word that a kernel sets when one of its bounded waits runs out (one per device).
 static __device__ int g_gemm_error;
 
-static int *error_word() {
+int *gemm_error_word() {
   static std::mutex mu;
   static int *ptrs[64] = {};
   int dev = 0;
@@ -152,7 +164,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   p.batch = (int)batch;
   p.nb1 = (int)std::max<int64_t>(nb1, 1);
   p.epi = epi;
-  p.err = error_word();
+  p.err = gemm_error_word();
   if (!p.err) { set_error("matmul: cannot resolve the device error word"); return PGB_ERR_CUDA; }
   // TMA-store epilogue: the output (and the residual, read with 16-byte loads in the output's dtype) must be aligned for it;
   // raw int32 accumulators and 32-column tiles stay on the plain-store epilogue

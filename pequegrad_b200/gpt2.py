@@ -5,11 +5,12 @@ The model is the one of the reference's examples/gpt2.py:149-204, 365-380
 MLP 768->3072->768 with tanh GELU, final LayerNorm, untied lm_head without
 bias), batched over sequences: fp16 weights and activations, fp32 accumulation
 in every GEMM and in LayerNorm / softmax. Per layer the launches are:
-  layernorm | qkv GEMM(+bias) | scores GEMM(alpha=1/8) | causal softmax |
-  V transpose | PV GEMM | proj GEMM(+bias,+residual) | layernorm |
-  fc GEMM(+bias,+GELU) | proj GEMM(+bias,+residual)
+  layernorm | qkv GEMM(+bias) | fused causal attention (scores, softmax and PV in
+  one kernel, heads read from and written to the packed [B, T, C] buffers) |
+  proj GEMM(+bias,+residual) | layernorm | fc GEMM(+bias,+GELU) | proj GEMM(+bias,+residual)
 Weights of a Linear are kept transposed ([out, in], K-major for the GEMM).
-Not fused yet: attention still materialises the [B, 12, T, T] scores.
+`fused_attention=False` runs attention as the reference composes it (scores GEMM,
+causal softmax kernel, V transpose, PV GEMM) for comparison.
 """
 from __future__ import annotations
 
@@ -39,8 +40,9 @@ def init_weights(cfg: GPT2Config, seed: int = 5) -> dict:
 
 
 class GPT2:
-    def __init__(self, cfg: GPT2Config, weights: dict, device="cuda", dtype=torch.float16):
+    def __init__(self, cfg: GPT2Config, weights: dict, device="cuda", dtype=torch.float16, fused_attention: bool = True):
         self.cfg, self.dtype = cfg, dtype
+        self.fused_attention = fused_attention and cfg.n_embd // cfg.n_head == 64
         dev = lambda a: torch.from_numpy(np.ascontiguousarray(a)).to(device=device, dtype=dtype)  # noqa: E731
         lin = lambda w_: dev(np.ascontiguousarray(w_.T))  # noqa: E731  [in, out] -> [out, in]
         self.wte, self.wpe = dev(weights["wte"]), dev(weights["wpe"])
@@ -61,19 +63,25 @@ class GPT2:
         B, T = idx.shape
         C, H = cfg.n_embd, cfg.n_head
         D = C // H
-        if T % 8 or T > cfg.block_size:
+        if T > cfg.block_size:
+            raise ValueError("GPT2.forward: the sequence is longer than block_size")
+        if not self.fused_attention and T % 8:
             # the [T, T] score rows feed the tensor-map loads of the PV GEMM, whose row pitch must be a multiple of 16 bytes
-            raise ValueError("GPT2.forward: the sequence length must be a multiple of 8 and at most block_size")
+            raise ValueError("GPT2.forward: the unfused attention path needs a sequence length that is a multiple of 8")
         x = K.embedding_rows(idx, self.wte, self.wpe, T)  # [B, T, C]
         for blk in self.blocks:
             h = K.layernorm_rows(x, blk["ln1_g"], blk["ln1_b"], 1e-5)
             qkv = K.matmul(h, blk["attn_wt"].T, bias=blk["attn_b"])  # [B, T, 3C]
             q, k, v = (qkv[:, :, i * C:(i + 1) * C].view(B, T, H, D).permute(0, 2, 1, 3) for i in range(3))  # [B, H, T, D] views
-            att = K.matmul(q, k.transpose(-2, -1), alpha=1.0 / 8.0 if D == 64 else float(D) ** -0.5)  # [B, H, T, T]
-            att = K.softmax_rows(att, causal=True)
-            (vt,) = K.fused_elementwise([v.transpose(-2, -1)], [("LOAD", 0)])  # [B, H, D, T] contiguous: V with T as the contraction dim
             y = torch.empty((B, T, C), dtype=self.dtype, device=x.device)
-            K.matmul(att, vt.transpose(-2, -1), out=y.view(B, T, H, D).permute(0, 2, 1, 3))  # heads written straight into [B, T, C]
+            y_heads = y.view(B, T, H, D).permute(0, 2, 1, 3)  # heads written straight into [B, T, C]
+            if self.fused_attention:
+                K.attention(q, k, v, scale=float(D) ** -0.5, causal=True, out=y_heads)
+            else:
+                att = K.matmul(q, k.transpose(-2, -1), alpha=1.0 / 8.0 if D == 64 else float(D) ** -0.5)  # [B, H, T, T]
+                att = K.softmax_rows(att, causal=True)
+                (vt,) = K.fused_elementwise([v.transpose(-2, -1)], [("LOAD", 0)])  # [B, H, D, T] contiguous: V with T as the contraction dim
+                K.matmul(att, vt.transpose(-2, -1), out=y_heads)
             x = K.matmul(y, blk["proj_wt"].T, bias=blk["proj_b"], residual=x)
             h = K.layernorm_rows(x, blk["ln2_g"], blk["ln2_b"], 1e-5)
             h = K.matmul(h, blk["fc_wt"].T, bias=blk["fc_b"], act=2)

@@ -193,6 +193,21 @@ def matmul(a: torch.Tensor, b: torch.Tensor, bias: torch.Tensor | None = None, a
     return out
 
 
+def attention(q: torch.Tensor, k: torch.Tensor, v: torch.Tensor, scale: float | None = None, causal: bool = False,
+              out: torch.Tensor | None = None) -> torch.Tensor:
+    """softmax(scale * q @ k^T [+ causal mask]) @ v in one kernel. q [.., T, 64], k / v [.., Tk, 64] (views with a
+    contiguous last dim); `out` may be a view too (e.g. heads written straight into a [B, T, H*64] buffer)."""
+    if scale is None:
+        scale = float(q.shape[-1]) ** -0.5
+    if out is None:
+        out = torch.empty(q.shape, dtype=q.dtype, device=q.device)
+    qd, kd, vd, od = desc(q), desc(k), desc(v), desc(out)
+    with torch.cuda.device(q.device):
+        st = L.lib().pgb_attention(C.byref(qd), C.byref(kd), C.byref(vd), scale, 1 if causal else 0, C.byref(od), _stream())
+    L.check(st)
+    return out
+
+
 def absmax(x: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
     if out is None:
         out = torch.empty(1, dtype=torch.float32, device=x.device)

@@ -194,10 +194,13 @@ class Gpt2:
         y = torch.empty((self.B, self.T, C), dtype=torch.float16, device=dev)
         parts["layernorm"] = _event_us(lambda: K.layernorm_rows(x3, blk["ln1_g"], blk["ln1_b"], 1e-5), reps)
         parts["qkv_gemm"] = _event_us(lambda: K.matmul(x3, blk["attn_wt"].T, bias=blk["attn_b"], out=qkv), reps)
-        parts["scores_gemm"] = _event_us(lambda: K.matmul(q, k.transpose(-2, -1), alpha=0.125, out=att), reps)
-        parts["causal_softmax"] = _event_us(lambda: K.softmax_rows(att, causal=True), reps)
-        parts["v_transpose"] = _event_us(lambda: K.fused_elementwise([v.transpose(-2, -1)], [("LOAD", 0)]), reps)
-        parts["pv_gemm"] = _event_us(lambda: K.matmul(att, vt.transpose(-2, -1), out=y.view(self.B, self.T, H, D).permute(0, 2, 1, 3)), reps)
+        y_heads = y.view(self.B, self.T, H, D).permute(0, 2, 1, 3)
+        parts["fused_attention"] = _event_us(lambda: K.attention(q, k, v, scale=0.125, causal=True, out=y_heads), reps)
+        # the same attention as four kernels (what GPT2(fused_attention=False) runs), for comparison
+        parts["unfused_scores_gemm"] = _event_us(lambda: K.matmul(q, k.transpose(-2, -1), alpha=0.125, out=att), reps)
+        parts["unfused_causal_softmax"] = _event_us(lambda: K.softmax_rows(att, causal=True), reps)
+        parts["unfused_v_transpose"] = _event_us(lambda: K.fused_elementwise([v.transpose(-2, -1)], [("LOAD", 0)]), reps)
+        parts["unfused_pv_gemm"] = _event_us(lambda: K.matmul(att, vt.transpose(-2, -1), out=y_heads), reps)
         parts["proj_gemm"] = _event_us(lambda: K.matmul(y, blk["proj_wt"].T, bias=blk["proj_b"], residual=x3, out=y), reps)
         parts["fc_gemm_gelu"] = us
         parts["fc2_gemm"] = _event_us(lambda: K.matmul(out.view(self.B, self.T, 4 * C), blk["fc2_wt"].T, bias=blk["fc2_b"], residual=x3, out=y), reps)

@@ -1,0 +1,77 @@
+"""The fused attention kernel (scores, softmax and PV in one launch) against the fp32 composite of the
+reference's GPT-2 block (examples/gpt2.py:168-186), through the C ABI. Tolerance 2e-2 (16-bit inputs)."""
+import math
+
+import numpy as np
+import pytest
+import torch
+
+from pequegrad_b200 import kernels as K
+
+pytestmark = pytest.mark.gpu
+
+
+def composite(q, k, v, causal, scale):
+    s = (q.float() @ k.float().transpose(-2, -1)) * scale
+    if causal:
+        T, Tk = s.shape[-2:]
+        s = s.masked_fill(~torch.tril(torch.ones(T, Tk, dtype=torch.bool, device=s.device)), float("-inf"))
+    return torch.softmax(s, -1) @ v.float()
+
+
+def check(got, want, what):
+    err = (got.float() - want).abs().max().item()
+    assert err <= 2e-2 * max(1.0, want.abs().max().item()), f"{what}: max abs error {err}"
+    assert K.device_error() == 0
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.bfloat16])
+@pytest.mark.parametrize("B,H,T,causal", [(1, 1, 128, False), (2, 3, 256, True), (1, 2, 1024, True), (2, 2, 200, True),
+                                          (1, 2, 72, False), (3, 1, 1, True), (1, 1, 65, True), (1, 4, 129, False)])
+def test_attention_matches_the_composite(B, H, T, causal, dtype):
+    g = torch.Generator(device="cuda").manual_seed(3)
+    q, k, v = (torch.randn((B, H, T, 64), generator=g, device="cuda").to(dtype) for _ in range(3))
+    check(K.attention(q, k, v, causal=causal), composite(q, k, v, causal, 0.125), f"{B}x{H}x{T}")
+
+
+def test_large_scores_and_scale():
+    # scores of magnitude ~50: the running max moves between key blocks, so the rows of O are rescaled in tensor memory
+    g = torch.Generator(device="cuda").manual_seed(4)
+    q, k, v = (torch.randn((2, 2, 512, 64), generator=g, device="cuda") for _ in range(3))
+    q, k, v = (q * 3).half(), (k * 3).half(), v.half()
+    for scale in (0.125, 0.5):
+        check(K.attention(q, k, v, scale=scale, causal=True), composite(q, k, v, True, scale), f"scale {scale}")
+    # keys sorted so that every later block raises the max of every row
+    k2 = (torch.arange(512, device="cuda").float()[None, None, :, None] * 0.02 * torch.ones(64, device="cuda")).half().expand(2, 2, 512, 64).contiguous()
+    q2 = torch.ones((2, 2, 512, 64), device="cuda").half()
+    check(K.attention(q2, k2, v, causal=False), composite(q2, k2, v, False, 0.125), "monotone keys")
+
+
+def test_heads_inside_packed_buffers_and_cross_lengths():
+    # q, k, v as slices of a packed [B, T, 3C] buffer, output written into [B, T, C]: the GPT-2 layout
+    B, T, H = 2, 384, 12
+    g = torch.Generator(device="cuda").manual_seed(5)
+    qkv = torch.randn((B, T, 3 * H * 64), generator=g, device="cuda").half()
+    q, k, v = (qkv[:, :, i * H * 64:(i + 1) * H * 64].view(B, T, H, 64).permute(0, 2, 1, 3) for i in range(3))
+    y = torch.zeros((B, T, H * 64), device="cuda", dtype=torch.float16)
+    K.attention(q, k, v, causal=True, out=y.view(B, T, H, 64).permute(0, 2, 1, 3))
+    want = composite(q, k, v, True, 0.125).permute(0, 2, 1, 3).reshape(B, T, H * 64)
+    check(y, want, "packed")
+    # more keys than queries, no mask; 3-D tensors
+    q3 = torch.randn((4, 100, 64), generator=g, device="cuda").half()
+    k3, v3 = (torch.randn((4, 300, 64), generator=g, device="cuda").half() for _ in range(2))
+    check(K.attention(q3, k3, v3), composite(q3, k3, v3, False, 0.125), "cross lengths")
+
+
+def test_attention_errors():
+    q = torch.zeros((1, 1, 16, 32), device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="head dim of 64"):
+        K.attention(q, q, q)
+    q = torch.zeros((1, 1, 16, 64), device="cuda", dtype=torch.float32)
+    with pytest.raises(RuntimeError, match="not implemented for"):
+        K.attention(q, q, q)
+    q = torch.zeros((1, 1, 16, 64), device="cuda", dtype=torch.float16)
+    with pytest.raises(ValueError, match="disagree"):
+        K.attention(q, q[:, :, :8], q)
+    with pytest.raises(ValueError, match="scale"):
+        K.attention(q, q, q, scale=-1.0)

@@ -40,7 +40,8 @@ def test_quantized_mlp_class_matches_the_oracle_pipeline():
 
 
 @pytest.mark.parametrize("cfg,B,T", [(G.GPT2Config(n_layer=2, n_head=2, n_embd=128, vocab_size=1000, block_size=64), 3, 64),
-                                     (G.GPT2Config(n_layer=3, n_head=4, n_embd=256, vocab_size=517, block_size=128), 2, 96)])
+                                     (G.GPT2Config(n_layer=3, n_head=4, n_embd=256, vocab_size=517, block_size=128), 2, 100),
+                                     (G.GPT2Config(n_layer=2, n_head=4, n_embd=128, vocab_size=300, block_size=64), 2, 48)])
 def test_gpt2_small_configs_match_fp32_reference(cfg, B, T):
     w = G.init_weights(cfg, seed=5)
     # non-trivial LayerNorm parameters and biases so that every epilogue operand matters
@@ -52,13 +53,15 @@ def test_gpt2_small_configs_match_fp32_reference(cfg, B, T):
             if k.endswith("_g"):
                 w[f"h{i}"][k] = (1 + rng.standard_normal(v.shape) * 0.02).astype(np.float32)
     idx = rng.integers(0, cfg.vocab_size, (B, T)).astype(np.int32)
-    model = G.GPT2(cfg, w)
-    logits = model.forward(torch.from_numpy(idx).cuda())
-    assert K.device_error() == 0
     want = G.reference_forward(cfg, w, idx)
-    got = logits.float().cpu().numpy()
-    assert got.shape == want.shape
-    assert_close(got, want, 2e-2, 2e-2 * float(np.abs(want).max()), "logits")
+    # head dim 64 runs the fused attention kernel; every config also runs attention as four kernels
+    for fused in ([True, False] if T % 8 == 0 else [True]):
+        model = G.GPT2(cfg, w, fused_attention=fused)
+        logits = model.forward(torch.from_numpy(idx).cuda())
+        assert K.device_error() == 0
+        got = logits.float().cpu().numpy()
+        assert got.shape == want.shape
+        assert_close(got, want, 2e-2, 2e-2 * float(np.abs(want).max()), f"logits (fused attention: {model.fused_attention})")
 
 
 def test_gpt2_small_full_architecture_one_sequence():
