@@ -290,6 +290,13 @@ PGB_API int pgb_attention(const pgb_tensor *q, const pgb_tensor *k, const pgb_te
  *   acc_i32       [M, N] int32 raw accumulators, or NULL
  *   out_absmax_dev  if not NULL, max |out| is folded into it with atomicMax (the caller zeroes
  *                 it), ready to be the next layer's a_absmax_dev
+ * Two more modes let a hidden layer hand int8 activations to the next layer without ever
+ * writing its fp32 output (same accumulators and arithmetic, so the int8 values are the ones
+ * the three-step route absmax -> pgb_quantize_i8 would give):
+ *   out == NULL, acc_i32 == NULL, out_absmax_dev != NULL   only max |out| is computed;
+ *   out of dtype int8 (more than 128 output channels, 16-byte aligned rows): out =
+ *                 clip(rint(v / s), -127, 127) with s = max(*out_absmax_dev, 1e-6) / 127, where
+ *                 *out_absmax_dev is READ here: the result of an earlier output-less pass
  */
 PGB_API int pgb_qlinear_i8(const pgb_tensor *a, const pgb_tensor *w, const float *w_scale, float a_scale,
                            const float *a_absmax_dev, const pgb_tensor *bias, int relu, const pgb_tensor *out,

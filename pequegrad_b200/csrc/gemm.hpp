@@ -24,7 +24,8 @@ struct GemmEpilogue {
   int res_dtype;
   int64_t res_ld, res_batch, res_batch0;  // row pitch, inner and outer batch strides (elements)
   void *out;      // or null
-  int out_dtype;  // f32 / f16 / bf16
+  int out_dtype;  // f32 / f16 / bf16; i8 (i8 kind only): v is quantised with requant_absmax
+  const float *requant_absmax;  // device scalar: q = clip(rint(v / (max(*requant_absmax, 1e-6) / 127)), -127, 127)
   int64_t ldc, out_batch, out_batch0;
   int32_t *acc_out;  // raw int32 accumulators (i8 only), or null
   int64_t ld_acc;

@@ -176,9 +176,15 @@ PGB_API int pgb_qlinear_i8(const pgb_tensor *a, const pgb_tensor *w, const float
     err = as_mat(*out, "the output", O);
     if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
     if (O.rows != M || O.cols != N || O.batch != 1) { set_error("qlinear: the output must be [M,N]"); return PGB_ERR_INVALID_ARG; }
-    if (out->dtype != PGB_F32 && out->dtype != PGB_F16 && out->dtype != PGB_BF16) {
+    if (out->dtype != PGB_F32 && out->dtype != PGB_F16 && out->dtype != PGB_BF16 && out->dtype != PGB_I8) {
       set_error(std::string("qlinear output not implemented for ") + dtype_name(out->dtype));
       return PGB_ERR_UNSUPPORTED;
+    }
+    if (out->dtype == PGB_I8) {
+      // requantising mode: the absmax of this layer's output is an INPUT (from an earlier output-less pass)
+      if (!out_absmax_dev) { set_error("qlinear: an int8 output is quantised with the device absmax, which is missing"); return PGB_ERR_INVALID_ARG; }
+      e.requant_absmax = out_absmax_dev;
+      e.absmax = nullptr;
     }
     e.out = out->data;
     e.out_dtype = out->dtype;
@@ -192,7 +198,7 @@ PGB_API int pgb_qlinear_i8(const pgb_tensor *a, const pgb_tensor *w, const float
     e.acc_out = (int32_t *)acc_i32->data;
     e.ld_acc = C.ld;
   }
-  if (!out && !acc_i32) { set_error("qlinear: nothing to write"); return PGB_ERR_INVALID_ARG; }
+  if (!out && !acc_i32 && !out_absmax_dev) { set_error("qlinear: nothing to write"); return PGB_ERR_INVALID_ARG; }
   if (!device_present()) return PGB_ERR_CUDA;
   e.alpha = 1.f;
   return run_gemm_tc(GEMM_I8, A.ptr, A.ld, 0, 0, W.ptr, W.ld, 0, 0, M, N, K, 1, 1, e, (cudaStream_t)stream);

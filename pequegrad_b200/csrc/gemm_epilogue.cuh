@@ -178,6 +178,8 @@ __device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, const CU
       if (p.out_tma == 4) { gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, 4>(p, omap, PGB_EPI_ARGS); break; } \
       if constexpr (KIND != GEMM_I8) {                                                                  \
         if (p.out_tma == 2) { gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, 2>(p, omap, PGB_EPI_ARGS); break; } \
+      } else if constexpr (BN == 256) {                                                                 \
+        if (p.out_tma == 1) { gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, 1>(p, omap, PGB_EPI_ARGS); break; } \
       }                                                                                                 \
     }                                                                                                   \
     gemm_epilogue_tiles<KIND, BN, ACT, BIAS, RES>(p, tmem_base, reinterpret_cast<uint32_t *>(stage), stash, half, acc_full, acc_empty, abort_flag, q, \

@@ -3,7 +3,8 @@
 // time, applies the fused epilogue in registers, writes its rows into a 32-row x 128-byte box in
 // shared memory (128B swizzle, so the 16-byte writes of a warp hit 32 distinct banks) and one lane
 // issues a TMA tile store of the box. The tensor map clips ragged bottom / right edges.
-// A box is 32 fp32 columns or 64 16-bit columns, so 16-bit outputs store after every second chunk.
+// A box is 32 fp32, 64 16-bit or 128 int8 columns, so 16-bit outputs store after every second chunk
+// and int8 outputs (the i8 kind's requantisation for the next layer) after every fourth.
 // Two boxes per warp: a store drains while the next box is being filled.
 // The residual (laid out like the output) is read straight into registers, 16 bytes per load,
 // one chunk ahead of its use.
@@ -85,7 +86,13 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
   float local_max = 0.f;
   const bool want_max = e.absmax != nullptr;
   const bool is_h = e.out_dtype == PGB_F16;
+  const bool no_out = e.out == nullptr;
   const float alpha = e.alpha;
+  float rq_s = 1.f, rq_r = 1.f;
+  if (OES == 1) {
+    rq_s = fmaxf(__ldg(e.requant_absmax), 1e-6f) / 127.0f;
+    rq_r = 1.0f / rq_s;
+  }
   constexpr int HALF = BN / 2;  // columns per epilogue warp of a lane group
   const int cbeg = half * HALF, cend = cbeg + HALF;
   uint32_t g = 0;  // boxes stored by this warp so far; box buffer = g & 1
@@ -155,8 +162,9 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
 #pragma unroll
         for (int i = 0; i < 32; ++i) local_max = fmaxf(local_max, fabsf(x[i]));
       }
-      if (row0 >= p.M) return;  // the whole warp is below the bottom edge
-      const int sub = OES == 2 ? (((c0 - cbeg) >> 5) & 1) : 0;
+      if (row0 >= p.M || no_out) return;  // the whole warp is below the bottom edge, or only the absmax is wanted
+      // 32 columns fill a whole 128-byte box row for 4-byte outputs, half of one for 2-byte, a quarter for int8
+      const int sub = OES == 4 ? 0 : (((c0 - cbeg) >> 5) & (OES == 2 ? 1 : 3));
       uint8_t *box = stage + (g & 1u) * kStoreBoxBytes;
       if (sub == 0) {
         // the store that last read this box was issued two boxes ago
@@ -170,14 +178,23 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
         for (int j = 0; j < 8; ++j)
           *reinterpret_cast<uint4 *>(rowp + ((j ^ sw) << 4)) = make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
                                                                          __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3]));
-      } else {
+      } else if (OES == 2) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           *reinterpret_cast<uint4 *>(rowp + (((sub * 4 + j) ^ sw) << 4)) =
               make_uint4(pack2(x[8 * j], x[8 * j + 1], is_h), pack2(x[8 * j + 2], x[8 * j + 3], is_h), pack2(x[8 * j + 4], x[8 * j + 5], is_h),
                          pack2(x[8 * j + 6], x[8 * j + 7], is_h));
+      } else {
+        // int8 requantisation for the next layer: the exact rounding of v / s_next
+#pragma unroll
+        for (int j = 0; j < 2; ++j)
+          *reinterpret_cast<uint4 *>(rowp + (((sub * 2 + j) ^ sw) << 4)) =
+              make_uint4(quant_i8_pack4(x[16 * j], x[16 * j + 1], x[16 * j + 2], x[16 * j + 3], rq_s, rq_r),
+                         quant_i8_pack4(x[16 * j + 4], x[16 * j + 5], x[16 * j + 6], x[16 * j + 7], rq_s, rq_r),
+                         quant_i8_pack4(x[16 * j + 8], x[16 * j + 9], x[16 * j + 10], x[16 * j + 11], rq_s, rq_r),
+                         quant_i8_pack4(x[16 * j + 12], x[16 * j + 13], x[16 * j + 14], x[16 * j + 15], rq_s, rq_r));
       }
-      if (OES == 4 || sub == 1 || c0 + 32 >= lim) {
+      if (OES == 4 || (OES == 2 && sub == 1) || (OES == 1 && sub == 3) || c0 + 32 >= lim) {
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {

@@ -151,6 +151,22 @@ __device__ __forceinline__ void tma_store_wait_all() { asm volatile("cp.async.bu
 // makes this thread's generic-proxy writes to shared memory visible to the async proxy (TMA)
 __device__ __forceinline__ void fence_proxy_async() { asm volatile("fence.proxy.async.shared::cta;" ::: "memory"); }
 
+// clip(rint(x / s), -127, 127) with the IEEE quotient's rounding, r = RN(1 / s). The quotient comes from one
+// Newton step on x * r (within one ulp of x / s); only when that lands within 1e-4 of a rounding boundary,
+// or is not finite, does the IEEE division run. (div.rn itself takes a slow path for zero numerators,
+// which is half of a ReLU output.)
+__device__ __forceinline__ float quant_i8_exact(float x, float s, float r) {
+  const float y0 = x * r;
+  const float y = fmaf(fmaf(-y0, s, x), r, y0);
+  float k = rintf(y);
+  if (!(fabsf(y - k) <= 0.4999f)) k = rintf(__fdiv_rn(x, s));
+  return fminf(fmaxf(k, -127.f), 127.f);
+}
+__device__ __forceinline__ uint32_t quant_i8_pack4(float a, float b, float c, float d, float s, float r) {
+  return ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(a, s, r)) | ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(b, s, r) << 8) |
+         ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(c, s, r) << 16) | ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(d, s, r) << 24);
+}
+
 __device__ __forceinline__ float gelu_tanh(float x) {
   // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3))) with tanh(z) = 2 / (1 + exp(-2z)) - 1, i.e.
   // x / (1 + exp(-2z))  (pequegrad/ops.py:109-118, 159-164). exp and the reciprocal are the hardware

@@ -1,13 +1,13 @@
 // Dynamic per-tensor int8 quantisation of activations (absmax, then quantise).
 // The reference has no int8 type; its example scales by max|.| floored at 1e-6
 // (examples/quantized_mlp.py:28-34), which these kernels keep.
-#include "gemm.hpp"
+#include "gemm_ptx.cuh"
 #include "reduce_common.cuh"
 
 namespace pgb {
 
 // absmax: one pass, atomicMax on the bit pattern. quantize: q = clip(rint(x / s), -127, 127),
-// s = max(absmax, 1e-6) / 127, true fp32 division, round half to even.
+// s = max(absmax, 1e-6) / 127, the rounding of the true fp32 quotient, round half to even.
 __global__ void __launch_bounds__(256) absmax_f32_kernel(const float *__restrict__ x, int64_t n, float *out) {
   float m = 0.f;
   const int64_t stride = (int64_t)gridDim.x * 256 * 4;
@@ -24,23 +24,12 @@ __global__ void __launch_bounds__(256) absmax_f32_kernel(const float *__restrict
   if ((threadIdx.x & 31) == 0 && m > 0.f) atomicMax(reinterpret_cast<unsigned int *>(out), __float_as_uint(m));
 }
 
-__device__ __forceinline__ uint32_t quantize4(const float4 v, float s) {
-  const float f[4] = {v.x, v.y, v.z, v.w};
-  uint32_t pk = 0;
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    float r = rintf(__fdiv_rn(f[e], s));
-    r = fminf(fmaxf(r, -127.f), 127.f);
-    pk |= ((uint32_t)(uint8_t)(int8_t)(int)r) << (8 * e);
-  }
-  return pk;
-}
-
 // One float4 in, one packed word out per thread and step: a warp reads 512 and writes 128 contiguous
 // bytes. Four independent steps are in flight per thread.
 __global__ void __launch_bounds__(256) quantize_i8_kernel(const float *__restrict__ x, int64_t n, const float *__restrict__ absmax,
                                                           float scale_host, int8_t *__restrict__ q) {
   const float s = absmax ? fmaxf(__ldg(absmax), 1e-6f) / 127.0f : scale_host;
+  const float r = 1.0f / s;
   const int64_t nvec = n >> 2;
   const int64_t stride = (int64_t)gridDim.x * 256;
   const float4 *x4 = reinterpret_cast<const float4 *>(x);
@@ -51,15 +40,16 @@ __global__ void __launch_bounds__(256) quantize_i8_kernel(const float *__restric
 #pragma unroll
     for (int u = 0; u < 4; ++u) v[u] = __ldcs(x4 + i + u * stride);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) q4[i + u * stride] = quantize4(v[u], s);
+    for (int u = 0; u < 4; ++u) q4[i + u * stride] = quant_i8_pack4(v[u].x, v[u].y, v[u].z, v[u].w, s, r);
   }
-  for (; i < nvec; i += stride) q4[i] = quantize4(__ldcs(x4 + i), s);
+  for (; i < nvec; i += stride) {
+    const float4 v = __ldcs(x4 + i);
+    q4[i] = quant_i8_pack4(v.x, v.y, v.z, v.w, s, r);
+  }
   // the last n % 4 elements
   if (blockIdx.x == 0 && threadIdx.x < (n & 3)) {
     const int64_t j = (nvec << 2) + threadIdx.x;
-    float r = rintf(__fdiv_rn(x[j], s));
-    r = fminf(fmaxf(r, -127.f), 127.f);
-    q[j] = (int8_t)(int)r;
+    q[j] = (int8_t)(int)quant_i8_exact(x[j], s, r);
   }
 }
 

@@ -93,13 +93,15 @@ bool encode_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, co
 static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, int64_t N, int64_t nb0, int64_t nb1) {
   EncodeTiledFn fn = encode_fn();
   if (!fn || !e.out) return false;
-  const int es = e.out_dtype == PGB_F32 ? 4 : 2;
+  const int es = e.out_dtype == PGB_F32 ? 4 : (e.out_dtype == PGB_I8 ? 1 : 2);
   int64_t bs1 = e.out_batch, bs0 = e.out_batch0;
   if (nb1 <= 1) bs1 = M * e.ldc;
   if (nb0 <= 1) bs0 = std::max<int64_t>(nb1, 1) * bs1;
   if ((reinterpret_cast<uintptr_t>(e.out) & 15) || (e.ldc * es) % 16 || (bs1 * es) % 16 || (bs0 * es) % 16 || e.ldc < N) return false;
-  const CUtensorMapDataType dt = e.out_dtype == PGB_F32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
-                                                        : (e.out_dtype == PGB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  const CUtensorMapDataType dt = e.out_dtype == PGB_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                 : e.out_dtype == PGB_I8  ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : e.out_dtype == PGB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                                          : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)std::max<int64_t>(nb1, 1), (cuuint64_t)std::max<int64_t>(nb0, 1)};
   const cuuint64_t strides[3] = {(cuuint64_t)(e.ldc * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
   const cuuint32_t box[4] = {(cuuint32_t)(128 / es), 32, 1, 1};
@@ -169,14 +171,21 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   // TMA-store epilogue: the output (and the residual, read with 16-byte loads in the output's dtype) must be aligned for it;
   // raw int32 accumulators and 32-column tiles stay on the plain-store epilogue
   CUtensorMap mo = ma;
-  const int oes = epi.out_dtype == PGB_F32 ? 4 : 2;
-  bool fast = bn >= 128 && epi.out && !epi.acc_out && !(kind == GEMM_I8 && oes != 4) && !getenv("PGB_GEMM_PLAIN_STORES");
+  const bool absmax_only = !epi.out && !epi.acc_out && epi.absmax;
+  const int oes = absmax_only ? 4 : (epi.out_dtype == PGB_F32 ? 4 : (epi.out_dtype == PGB_I8 ? 1 : 2));
+  bool fast = bn >= 128 && (epi.out || absmax_only) && !epi.acc_out && !getenv("PGB_GEMM_PLAIN_STORES");
+  if (kind == GEMM_I8 && oes == 2) fast = false;
+  if (oes == 1 && (kind != GEMM_I8 || bn != 256 || !epi.requant_absmax)) fast = false;
   if (fast && epi.residual) {
     const int64_t rb1 = nb1 <= 1 ? 0 : epi.res_batch, rb0 = nb0 <= 1 ? 0 : epi.res_batch0;
     fast = epi.res_dtype == epi.out_dtype && !(reinterpret_cast<uintptr_t>(epi.residual) & 15) && (epi.res_ld * oes) % 16 == 0 &&
            (rb1 * oes) % 16 == 0 && (rb0 * oes) % 16 == 0;
   }
-  if (fast) fast = make_output_map(&mo, epi, M, N, nb0, nb1);
+  if (fast && !absmax_only) fast = make_output_map(&mo, epi, M, N, nb0, nb1);
+  if (oes == 1 && !fast) {
+    set_error("qlinear: an int8 output needs more than 128 output channels, a 16-byte aligned base and row pitch, and a device absmax");
+    return PGB_ERR_UNSUPPORTED;
+  }
   p.out_tma = fast ? oes : 0;
   p.res_vec = fast && epi.residual;
   const int64_t num_tiles = tiles_m * tiles_n * batch;

@@ -8,8 +8,12 @@ place of its fp32 fake quantisation (examples/quantized_mlp.py:28-48):
                xq = clip(rint(x / s_x), -127, 127); the absmax never leaves the GPU
   layer        acc = xq . Wq^T in int32 (tcgen05 kind::i8), then
                h = relu(acc * (s_x * s_w[n]) + b[n]) in fp32; the last layer has no ReLU
-Per layer that is: quantise kernel, GEMM kernel with fused dequant + bias + ReLU +
-absmax of its own output (which is the next layer's activation absmax).
+A hidden layer never writes its fp32 output: the GEMM runs twice on the same int8
+operands, first with an epilogue that only folds max|h| into a device scalar, then
+with one that quantises h for the next layer and stores int8 (a quarter of the fp32
+bytes). The accumulators and the epilogue arithmetic are the same in both, so the
+int8 activations equal those of the materialising route (`keep=True`: quantise
+kernel, GEMM with fp32 output and fused absmax), which the parity tests check.
 """
 from __future__ import annotations
 
@@ -56,13 +60,20 @@ class QuantizedMLP:
         amax = b["amax"]
         amax[1:].zero_()  # slot i holds max|input of layer i|; the GEMM epilogues fold into slots 1..
         K.absmax(x, out=amax[0:1])
-        h = x
+        xq = K.quantize_i8(x, absmax_dev=amax[0:1], out=b["q"][0])
         kept = []
         n = len(self.layers)
         for i, (wq, ws, bias) in enumerate(self.layers):
-            xq = K.quantize_i8(h, absmax_dev=amax[i:i + 1], out=b["q"][i])
-            h, _ = K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=i < n - 1, out=b["h"][i],
-                                out_absmax=amax[i + 1:i + 2] if i < n - 1 else None)
+            last = i == n - 1
+            fused = not keep and not last and self.layers[i][0].shape[0] > 128 and self.layers[i][0].shape[0] % 16 == 0
+            if fused:
+                K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=True, want_out=False, out_absmax=amax[i + 1:i + 2])
+                xq, _ = K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=True, out=b["q"][i + 1], out_absmax=amax[i + 1:i + 2])
+                continue
+            h, _ = K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=not last, out=b["h"][i],
+                                out_absmax=amax[i + 1:i + 2] if not last else None)
             if keep:
                 kept.append((xq, h))
+            if not last:
+                xq = K.quantize_i8(h, absmax_dev=amax[i + 1:i + 2], out=b["q"][i + 1])
         return (h, kept) if keep else h

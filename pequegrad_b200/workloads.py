@@ -144,8 +144,9 @@ class Gpt2:
         self.logits_buf = torch.empty((self.B, self.T, self.model.vocab_ld), dtype=torch.float16, device=dev)
         self.units_per_step = self.B * self.T
         C, L_, V, T = self.cfg.n_embd, self.cfg.n_layer, self.cfg.vocab_size, self.T
-        # multiply-adds x 2 per token: the four Linear layers of a block, both attention GEMMs over the full [T, T] square, the lm_head
-        self.flops_per_token = 2.0 * (L_ * (C * 3 * C + C * C + 2 * C * 4 * C) + C * V) + 2.0 * 2.0 * T * C * L_
+        # multiply-adds x 2 per token: the four Linear layers of a block, the lm_head, and both attention GEMMs over the
+        # causal half of the [T, T] square (the average query row sees (T + 1) / 2 keys)
+        self.flops_per_token = 2.0 * (L_ * (C * 3 * C + C * C + 2 * C * 4 * C) + C * V) + 2.0 * 2.0 * ((T + 1) / 2.0) * C * L_
         self.config = {"batch_per_gpu": self.B, "seq_len": T, "flops_per_token": self.flops_per_token,
                        "l2": "activations of a layer (50 to 805 MB) and the 3.3 GB of logits are larger than the 126 MB L2"}
 

@@ -173,3 +173,48 @@ def test_matmul_errors_follow_the_reference():
         K.matmul(h, h)  # [K, N] with N contiguous: not built yet
     with pytest.raises(ValueError):
         K.matmul(h, torch.zeros((24, 8), device="cuda", dtype=torch.float16).T)
+
+
+@pytest.mark.parametrize("M,N,K_", [(513, 1024, 784), (1000, 144, 256), (128, 4112, 64), (65, 272, 1040)])
+def test_int8_layer_without_fp32_output(M, N, K_):
+    """The TMA-store epilogues of the i8 kind: fp32 output, absmax-only pass, int8 requantising pass. All bit-exact:
+    the int8 activations must equal what absmax -> quantise of the fp32 output gives."""
+    rng = np.random.default_rng(43)
+    a = rng.integers(-127, 128, (M, K_)).astype(np.int8)
+    w = rng.integers(-127, 128, (N, K_)).astype(np.int8)
+    ws = (rng.random(N) * 0.01 + 1e-3).astype(np.float32)
+    b = (rng.standard_normal(N) * 0.05).astype(np.float32)
+    a_scale = np.float32(0.0123)
+    want = oracle.dequant_bias_act(oracle.gemm_i8(a, w), ws, a_scale, b, True)
+    amax_want = oracle.absmax(want)
+    q_want = oracle.quantize_i8(want, oracle.quant_scale(amax_want))
+    A, W, WS, B = cu(a), cu(w), cu(ws), cu(b)
+    amax = torch.zeros(1, device="cuda")
+    out, _ = K.qlinear_i8(A, W, WS, a_scale=float(a_scale), bias=B, relu=True, out_absmax=amax)
+    assert np.array_equal(out.cpu().numpy(), want)
+    assert amax.item() == amax_want
+    amax2 = torch.zeros(1, device="cuda")
+    K.qlinear_i8(A, W, WS, a_scale=float(a_scale), bias=B, relu=True, want_out=False, out_absmax=amax2)
+    assert amax2.item() == amax_want
+    q = torch.full((M, N), 99, dtype=torch.int8, device="cuda")
+    K.qlinear_i8(A, W, WS, a_scale=float(a_scale), bias=B, relu=True, out=q, out_absmax=amax2)
+    assert np.array_equal(q.cpu().numpy(), q_want)
+    assert K.device_error() == 0
+    # and the stand-alone quantiser on a ReLU output (half zeros) and on values that sit on rounding boundaries
+    assert np.array_equal(K.quantize_i8(out, absmax_dev=amax).cpu().numpy(), q_want)
+    s = np.float32(0.37)
+    ties = (np.arange(-130, 131, dtype=np.float32) + np.float32(0.5)) * s
+    x = np.concatenate([ties, np.nextafter(ties, np.float32(np.inf)), np.nextafter(ties, np.float32(-np.inf)), np.zeros(7, np.float32)])
+    x = np.resize(x, 4096).astype(np.float32)
+    assert np.array_equal(K.quantize_i8(cu(x), scale=float(s)).cpu().numpy(), oracle.quantize_i8(x, s))
+
+
+def test_int8_output_needs_wide_aligned_rows():
+    a = torch.zeros((64, 64), dtype=torch.int8, device="cuda")
+    w = torch.zeros((64, 64), dtype=torch.int8, device="cuda")
+    ws = torch.ones(64, device="cuda")
+    q = torch.zeros((64, 64), dtype=torch.int8, device="cuda")
+    with pytest.raises(RuntimeError, match="more than 128 output channels"):
+        K.qlinear_i8(a, w, ws, a_scale=1.0, out=q, out_absmax=torch.ones(1, device="cuda"))
+    with pytest.raises(ValueError, match="device absmax"):
+        K.qlinear_i8(a, w, ws, a_scale=1.0, out=q)
