@@ -1,13 +1,14 @@
 // Epilogue of the tcgen05 GEMM for outputs that TMA can store (16-byte aligned base and pitches):
 // each epilogue warp drains 32 TMEM lanes (32 rows) of the finished accumulator 32 columns at a
-// time, applies the fused epilogue in registers, writes its rows into a 32-row x 128-byte box in
-// shared memory (128B swizzle, so the 16-byte writes of a warp hit 32 distinct banks) and one lane
-// issues a TMA tile store of the box. The tensor map clips ragged bottom / right edges.
-// A box is 32 fp32, 64 16-bit or 128 int8 columns, so 16-bit outputs store after every second chunk
-// and int8 outputs (the i8 kind's requantisation for the next layer) after every fourth.
-// Two boxes per warp: a store drains while the next box is being filled.
-// The residual (laid out like the output) is read straight into registers, 16 bytes per load,
-// one chunk ahead of its use.
+// time, applies the fused epilogue in registers, writes its rows into a 32-row box in shared
+// memory (swizzled, so the 16-byte writes of a warp hit 32 distinct banks) and one lane issues a
+// TMA tile store of the box. The tensor map clips ragged bottom / right edges.
+// Sixteen epilogue warps: four per TMEM lane quadrant, each with a quarter of the tile's columns, so
+// that every scheduler has four warps to hide the TMEM-load, shared-memory and store latencies of
+// one another (two warps per scheduler ran at a quarter of the issue rate). A box row is the warp's
+// share of a row: 128 bytes (128B swizzle) or 64 bytes (64B swizzle); narrow dtypes fill it with
+// two 32-column chunks. The residual (laid out like the output) is read straight into registers,
+// 16 bytes per load, while the TMEM load is in flight.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -73,10 +74,21 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool is_h) {
   return *reinterpret_cast<const uint32_t *>(&b);
 }
 
+// Bytes of one box row: the warp's share of the tile's columns, at most one 128-byte swizzle atom.
+template <int BN, int OES>
+struct BoxCfg {
+  static constexpr int kCols = BN / kEpiGroups;  // columns per epilogue warp
+  static constexpr int kRowBytes = kCols * OES < 128 ? kCols * OES : 128;
+  static constexpr int kChunkBytes = 32 * OES;                    // one 32-column chunk of a row
+  static constexpr int kChunksPerBox = kRowBytes / kChunkBytes;   // 1, 2 (or 4)
+  static_assert(kRowBytes == 128 || kRowBytes == 64, "box rows are one 128-byte or one 64-byte swizzle atom");
+};
+
 template <int KIND, int BN, int ACT, bool BIAS, bool RES, int OES>
 __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtensorMap *omap, uint32_t tmem_base, uint8_t *stage, float *stash,
-                                               int half, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag, int q, int lane,
+                                               int group, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag, int q, int lane,
                                                int num_tiles, int tiles_per_batch) {
+  using Box = BoxCfg<BN, OES>;
   const GemmEpilogue &e = p.epi;
   float a_scale = e.a_scale;
   if (KIND == GEMM_I8 && e.a_scale_dev) {
@@ -93,9 +105,8 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     rq_s = fmaxf(__ldg(e.requant_absmax), 1e-6f) / 127.0f;
     rq_r = 1.0f / rq_s;
   }
-  constexpr int HALF = BN / 2;  // columns per epilogue warp of a lane group
-  const int cbeg = half * HALF, cend = cbeg + HALF;
-  uint32_t g = 0;  // boxes stored by this warp so far; box buffer = g & 1
+  const int cbeg = group * Box::kCols, cend = cbeg + Box::kCols;
+  float *sc_stash = stash, *bi_stash = stash + Box::kCols;  // this warp's columns: scale, then bias
   int it = 0;
   for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
     const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
@@ -104,23 +115,20 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     const int buf = it & 1;
     // column operands of this tile, fetched while the MMAs are still running
     __syncwarp();
-    for (int c = cbeg + lane; c < cend; c += 32) {
-      const int col = n0 + c;
+    for (int c = lane; c < Box::kCols; c += 32) {
+      const int col = n0 + cbeg + c;
       const bool okc = col < p.N;
-      if (KIND == GEMM_I8) stash[c] = e.col_scale ? __fmul_rn(a_scale, okc ? __ldg(e.col_scale + col) : 0.f) : a_scale;
-      if (BIAS) stash[256 + c] = (okc && e.bias) ? load_as<float>(e.bias, e.bias_dtype, col) : 0.f;
+      if (KIND == GEMM_I8) sc_stash[c] = e.col_scale ? __fmul_rn(a_scale, okc ? __ldg(e.col_scale + col) : 0.f) : a_scale;
+      if (BIAS) bi_stash[c] = (okc && e.bias) ? load_as<float>(e.bias, e.bias_dtype, col) : 0.f;
     }
     __syncwarp();
     const int row0 = m0 + q * 32, row = row0 + lane;
     const bool row_ok = row < p.M;
     const int lim = min(cend, p.N - n0);  // end of this warp's columns that exist (warp-uniform)
     const uint8_t *res_row = nullptr;
-    ResChunk<OES> ra, rb;
-    if (RES) {
+    if (RES)
       res_row = reinterpret_cast<const uint8_t *>(e.residual) +
                 ((int64_t)wb * e.res_batch0 + (int64_t)zb * e.res_batch + (int64_t)row * e.res_ld + n0) * OES;
-      if (cbeg < lim) res_load<OES>(ra, res_row + cbeg * OES, row_ok, lim - cbeg);  // does not depend on the accumulator
-    }
     bool ok = true;
     if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -130,16 +138,22 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     }
     tc_fence_after();
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
-
-    auto release_acc = [&]() {
-      // every TMEM load of this tile has landed in registers: hand the buffer back to the MMA warp
-      tc_fence_before();
-      __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
-    };
-    auto run = [&](const uint32_t(&v)[32], const ResChunk<OES> &rc, int c0) {
+    bool released = false;
+    for (int c0 = cbeg; c0 < lim; c0 += 32) {
+      uint32_t v[32];
+      ResChunk<OES> rc;
+      tmem_ld32_issue(taddr + c0, v);
+      if (RES) res_load<OES>(rc, res_row + c0 * OES, row_ok, lim - c0);  // in flight together with the TMEM load
+      tmem_ld_wait();
+      if (c0 + 32 >= lim) {
+        // every TMEM load of this tile has landed in registers: hand the buffer back to the MMA warp
+        tc_fence_before();
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        released = true;
+      }
       float x[32];
-      const float *sc = stash + c0, *bi = stash + 256 + c0;
+      const float *sc = sc_stash + (c0 - cbeg), *bi = bi_stash + (c0 - cbeg);
 #pragma unroll
       for (int i = 0; i < 32; i += 4) {
         float4 s4 = make_float4(0.f, 0.f, 0.f, 0.f), b4 = s4;
@@ -162,76 +176,50 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
 #pragma unroll
         for (int i = 0; i < 32; ++i) local_max = fmaxf(local_max, fabsf(x[i]));
       }
-      if (row0 >= p.M || no_out) return;  // the whole warp is below the bottom edge, or only the absmax is wanted
-      // 32 columns fill a whole 128-byte box row for 4-byte outputs, half of one for 2-byte, a quarter for int8
-      const int sub = OES == 4 ? 0 : (((c0 - cbeg) >> 5) & (OES == 2 ? 1 : 3));
-      uint8_t *box = stage + (g & 1u) * kStoreBoxBytes;
+      if (row0 >= p.M || no_out) continue;  // the whole warp is below the bottom edge, or only the absmax is wanted
+      const int sub = ((c0 - cbeg) >> 5) % Box::kChunksPerBox;
       if (sub == 0) {
-        // the store that last read this box was issued two boxes ago
-        if (lane == 0) tma_store_wait_read<1>();
+        // the previous store of this warp must have read the box before it is overwritten
+        if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
       }
-      uint8_t *rowp = box + lane * 128;
-      const int sw = lane & 7;
+      uint8_t *rowp = stage + lane * Box::kRowBytes;
+      const int sw = Box::kRowBytes == 128 ? (lane & 7) : ((lane >> 1) & 3);  // 128B / 64B swizzle of the 16-byte chunk index
+      constexpr int CP = Box::kChunkBytes / 16;                              // 16-byte pieces per 32-column chunk
       if (OES == 4) {
 #pragma unroll
         for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4 *>(rowp + ((j ^ sw) << 4)) = make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
-                                                                         __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3]));
+          *reinterpret_cast<uint4 *>(rowp + (((sub * CP + j) ^ sw) << 4)) = make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
+                                                                                      __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3]));
       } else if (OES == 2) {
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4 *>(rowp + (((sub * 4 + j) ^ sw) << 4)) =
+          *reinterpret_cast<uint4 *>(rowp + (((sub * CP + j) ^ sw) << 4)) =
               make_uint4(pack2(x[8 * j], x[8 * j + 1], is_h), pack2(x[8 * j + 2], x[8 * j + 3], is_h), pack2(x[8 * j + 4], x[8 * j + 5], is_h),
                          pack2(x[8 * j + 6], x[8 * j + 7], is_h));
       } else {
         // int8 requantisation for the next layer: the exact rounding of v / s_next
 #pragma unroll
         for (int j = 0; j < 2; ++j)
-          *reinterpret_cast<uint4 *>(rowp + (((sub * 2 + j) ^ sw) << 4)) =
+          *reinterpret_cast<uint4 *>(rowp + (((sub * CP + j) ^ sw) << 4)) =
               make_uint4(quant_i8_pack4(x[16 * j], x[16 * j + 1], x[16 * j + 2], x[16 * j + 3], rq_s, rq_r),
                          quant_i8_pack4(x[16 * j + 4], x[16 * j + 5], x[16 * j + 6], x[16 * j + 7], rq_s, rq_r),
                          quant_i8_pack4(x[16 * j + 8], x[16 * j + 9], x[16 * j + 10], x[16 * j + 11], rq_s, rq_r),
                          quant_i8_pack4(x[16 * j + 12], x[16 * j + 13], x[16 * j + 14], x[16 * j + 15], rq_s, rq_r));
       }
-      if (OES == 4 || (OES == 2 && sub == 1) || (OES == 1 && sub == 3) || c0 + 32 >= lim) {
+      if (sub == Box::kChunksPerBox - 1 || c0 + 32 >= lim) {
         fence_proxy_async();
         __syncwarp();
         if (lane == 0) {
-          tma_store_4d(omap, box, n0 + c0 - sub * 32, row0, zb, wb);
+          tma_store_4d(omap, stage, n0 + c0 - sub * 32, row0, zb, wb);
           tma_store_commit();
         }
-        ++g;
       }
-    };
-
-    uint32_t va[32], vb[32];
-    if (cbeg < lim) {
-      tmem_ld32_issue(taddr + cbeg, va);
-      for (int c0 = cbeg; c0 < lim; c0 += 64) {
-        tmem_ld_wait();
-        const bool more1 = c0 + 32 < lim;
-        if (more1) {
-          tmem_ld32_issue(taddr + c0 + 32, vb);
-          if (RES) res_load<OES>(rb, res_row + (c0 + 32) * OES, row_ok, lim - c0 - 32);
-        } else {
-          release_acc();
-        }
-        run(va, ra, c0);
-        if (more1) {
-          tmem_ld_wait();
-          const bool more2 = c0 + 64 < lim;
-          if (more2) {
-            tmem_ld32_issue(taddr + c0 + 64, va);
-            if (RES) res_load<OES>(ra, res_row + (c0 + 64) * OES, row_ok, lim - c0 - 64);
-          } else {
-            release_acc();
-          }
-          run(vb, rb, c0 + 32);
-        }
-      }
-    } else {
-      release_acc();  // none of this warp's columns exist in this tile
+    }
+    if (!released) {  // none of this warp's columns exist in this tile
+      tc_fence_before();
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&acc_empty[buf]);
     }
   }
   // shared memory must outlive the reads of the last stores
@@ -241,6 +229,24 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     for (int m = 16; m > 0; m >>= 1) local_max = fmaxf(local_max, __shfl_xor_sync(0xffffffffu, local_max, m));
     // non-negative floats order like their bit patterns
     if (lane == 0 && local_max > 0.f) atomicMax(reinterpret_cast<unsigned int *>(e.absmax), __float_as_uint(local_max));
+  }
+}
+
+// A warp with no share of the tile in the plain-store epilogue still takes part in the accumulator hand-over.
+static __device__ __noinline__ void gemm_epilogue_idle(const GemmParams &p, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag, int lane,
+                                                int num_tiles) {
+  int it = 0;
+  for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+    const int buf = it & 1;
+    bool ok = true;
+    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
+    ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+    if (!ok) {
+      if (lane == 0) report_error(p, abort_flag, 3);
+      break;
+    }
+    __syncwarp();
+    if (lane == 0) mbar_arrive(&acc_empty[buf]);
   }
 }
 

@@ -8,14 +8,16 @@ namespace pgb {
 constexpr int kBM = 128;
 constexpr int kSlabBytes = 128;  // bytes of K per stage = one 128B swizzle atom row
 constexpr int kTileABytes = kBM * kSlabBytes;
-constexpr int kEpiWarps = 8;  // two per TMEM lane group, each takes half of the tile's columns
+constexpr int kEpiGroups = 4;              // column groups: epilogue warps per TMEM lane quadrant
+constexpr int kEpiWarps = 4 * kEpiGroups;  // each takes a quarter of the tile's columns for its 32 rows
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kStagePitch = 36;  // words per staged row: 32 + 4 keeps 128-bit accesses conflict-free
-constexpr int kStoreBoxBytes = 32 * 128;  // the TMA-store box of one epilogue warp: 32 rows x 128 bytes (128B swizzle)
-constexpr int kEpiWarpStageBytes = 2 * kStoreBoxBytes;  // two boxes per warp, so a store drains while the next box is filled
-constexpr int kEpiStageBytes = kEpiWarps * kEpiWarpStageBytes;
-static_assert(kEpiWarpStageBytes >= 32 * kStagePitch * 4, "the plain-store path stages one 32 x 36-word block in the same area");
-constexpr int kColStashBytes = kEpiWarps * 2 * 256 * 4;  // per epilogue warp: scale and bias of the tile's columns
+constexpr int kStoreBoxBytes = 32 * 128;  // the TMA-store box of one epilogue warp: 32 rows x (at most) 128 bytes
+constexpr int kEpiStageBytes = kEpiWarps * kStoreBoxBytes;
+constexpr int kPlainWarps = 8;  // the plain-store epilogue splits a tile's columns in two: eight warps work, eight only hand over
+constexpr int kPlainStageBytes = 32 * kStagePitch * 4;
+static_assert(kPlainWarps * kPlainStageBytes <= kEpiStageBytes, "the plain-store path stages 32 x 36-word blocks in the same area");
+constexpr int kColStashBytes = kPlainWarps * 2 * 256 * 4;  // per plain-store warp: scale and bias of the tile's columns (the TMA path needs less)
 constexpr int kSmemBudget = 150 * 1024;  // for the operand ring
 
 template <int BN>

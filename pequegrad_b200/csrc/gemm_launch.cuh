@@ -109,10 +109,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
     }
   } else {
     const int q = warp & 3;   // a warp may read TMEM lanes 32*(warp%4) .. +31
-    const int ew = warp - 2;  // 0..7; warps ew and ew+4 share a lane group and split the columns
+    const int ew = warp - 2;  // 0..15; the four warps of a lane quadrant split the tile's columns
     if (lane == 0 && p.out_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
-    gemm_epilogue_warp<KIND, BN>(p, &tmap_out, tmem_base, epi_stage + ew * kEpiWarpStageBytes, col_stash + ew * 512, ew >> 2, acc_full, acc_empty,
-                                 abort_flag, q, lane, num_tiles, tiles_per_batch);
+    gemm_epilogue_warp<KIND, BN>(p, &tmap_out, tmem_base, epi_stage, col_stash, ew, acc_full, acc_empty, abort_flag, q, lane, num_tiles,
+                                 tiles_per_batch);
   }
   tc_fence_before();
   __syncthreads();

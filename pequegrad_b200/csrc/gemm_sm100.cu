@@ -15,7 +15,7 @@
 // loops over 128 x BN tiles of C:
 //   warp 0     TMA producer: 128-byte-wide K slabs of A and B per stage, 128B swizzle
 //   warp 1     allocates TMEM, issues tcgen05.mma (one thread), commits to mbarriers
-//   warps 2-9  epilogue: tcgen05.ld the accumulator (one row per thread), apply the fused
+//   warps 2-17 epilogue: tcgen05.ld the accumulator (one row per thread), apply the fused
 //              epilogue in registers, write 32-row x 128-byte boxes to shared memory and
 //              TMA-store them (plain coalesced stores for outputs TMA cannot address)
 // The accumulator is double-buffered in TMEM (2 x BN columns), so the epilogue
@@ -90,7 +90,7 @@ bool encode_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, co
 
 // The output as a 4-D tensor map for TMA tile stores: {N, M, nb1, nb0} with a {128 bytes, 32 rows, 1, 1} box, 128B swizzle.
 // Returns false (and leaves the plain-store epilogue in charge) when the layout does not meet TMA's alignment rules.
-static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, int64_t N, int64_t nb0, int64_t nb1) {
+static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, int64_t N, int64_t nb0, int64_t nb1, int bn) {
   EncodeTiledFn fn = encode_fn();
   if (!fn || !e.out) return false;
   const int es = e.out_dtype == PGB_F32 ? 4 : (e.out_dtype == PGB_I8 ? 1 : 2);
@@ -104,10 +104,13 @@ static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, 
                                                           : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)std::max<int64_t>(nb1, 1), (cuuint64_t)std::max<int64_t>(nb0, 1)};
   const cuuint64_t strides[3] = {(cuuint64_t)(e.ldc * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
-  const cuuint32_t box[4] = {(cuuint32_t)(128 / es), 32, 1, 1};
+  // one box row = an epilogue warp's share of a tile row, at most one 128-byte swizzle atom (BoxCfg in gemm_epilogue_tma.cuh)
+  const int row_bytes = std::min(128, bn / kEpiGroups * es);
+  const cuuint32_t box[4] = {(cuuint32_t)(row_bytes / es), 32, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(map, dt, 4, e.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return fn(map, dt, 4, e.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+            row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
+            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // The device error word that a kernel sets when one of its bounded waits runs out (one per device).
@@ -181,7 +184,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
     fast = epi.res_dtype == epi.out_dtype && !(reinterpret_cast<uintptr_t>(epi.residual) & 15) && (epi.res_ld * oes) % 16 == 0 &&
            (rb1 * oes) % 16 == 0 && (rb0 * oes) % 16 == 0;
   }
-  if (fast && !absmax_only) fast = make_output_map(&mo, epi, M, N, nb0, nb1);
+  if (fast && !absmax_only) fast = make_output_map(&mo, epi, M, N, nb0, nb1, bn);
   if (oes == 1 && !fast) {
     set_error("qlinear: an int8 output needs more than 128 output channels, a 16-byte aligned base and row pitch, and a device absmax");
     return PGB_ERR_UNSUPPORTED;
