@@ -165,32 +165,32 @@ __device__ __noinline__ void gemm_epilogue_tiles(const GemmParams &p, uint32_t t
   }
 }
 
-// Chooses the specialisation once per kernel: the TMA-store epilogue when the host found the output
-// (and residual) aligned for it, else the plain-store one above.
+// Chooses the specialisation once per kernel. TMA_EPI kernels hold only the TMA-store epilogues (p.out_tma = the
+// output's element size), the others only the plain-store one above.
 // ew = epilogue warp 0..15: TMEM lane quadrant q = warp % 4, column group ew / 4.
-template <int KIND, int BN>
+template <int KIND, int BN, bool TMA_EPI>
 __device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, const CUtensorMap *omap, uint32_t tmem_base, uint8_t *stage_base,
                                                    float *stash_base, int ew, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag,
                                                    int q, int lane, int num_tiles, int tiles_per_batch) {
-#define PGB_EPI_TMA(ACT, BIAS, RES, OES)                                                                                              \
-  gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, OES>(p, omap, tmem_base, stage_base + ew * kStoreBoxBytes, stash_base + ew * 128, ew >> 2, acc_full, \
-                                                   acc_empty, abort_flag, q, lane, num_tiles, tiles_per_batch)
+#define PGB_EPI_TMA(ACT, BIAS, RES, OES)                                                                                                \
+  gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, OES>(p, omap, tmem_base, stage_base + ew * kStoreBoxBytes, stash_base, ew >> 2, acc_full, acc_empty, \
+                                                   abort_flag, q, lane, num_tiles, tiles_per_batch)
 #define PGB_EPI(ACT, BIAS, RES)                                                                                           \
   do {                                                                                                                    \
-    if constexpr (BN >= 128) {                                                                                            \
-      if (p.out_tma == 4) { PGB_EPI_TMA(ACT, BIAS, RES, 4); break; }                                                      \
+    if constexpr (TMA_EPI) {                                                                                              \
       if constexpr (KIND != GEMM_I8) {                                                                                    \
         if (p.out_tma == 2) { PGB_EPI_TMA(ACT, BIAS, RES, 2); break; }                                                    \
       } else if constexpr (BN == 256) {                                                                                   \
         if (p.out_tma == 1) { PGB_EPI_TMA(ACT, BIAS, RES, 1); break; }                                                    \
       }                                                                                                                   \
-    }                                                                                                                     \
-    if (ew < kPlainWarps)                                                                                                 \
+      PGB_EPI_TMA(ACT, BIAS, RES, 4);                                                                                     \
+    } else if (ew < kPlainWarps) {                                                                                        \
       gemm_epilogue_tiles<KIND, BN, ACT, BIAS, RES>(p, tmem_base, reinterpret_cast<uint32_t *>(stage_base + ew * kPlainStageBytes), \
                                                     stash_base + ew * 512, ew >> 2, acc_full, acc_empty, abort_flag, q, lane, num_tiles, \
                                                     tiles_per_batch);                                                     \
-    else                                                                                                                  \
+    } else {                                                                                                              \
       gemm_epilogue_idle(p, acc_full, acc_empty, abort_flag, lane, num_tiles);                                            \
+    }                                                                                                                     \
   } while (0)
   const bool bias = p.epi.bias != nullptr, res = p.epi.residual != nullptr;
   const int act = p.epi.act;

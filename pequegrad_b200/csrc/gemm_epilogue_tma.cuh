@@ -5,10 +5,11 @@
 // TMA tile store of the box. The tensor map clips ragged bottom / right edges.
 // Sixteen epilogue warps: four per TMEM lane quadrant, each with a quarter of the tile's columns, so
 // that every scheduler has four warps to hide the TMEM-load, shared-memory and store latencies of
-// one another (two warps per scheduler ran at a quarter of the issue rate). A box row is the warp's
-// share of a row: 128 bytes (128B swizzle) or 64 bytes (64B swizzle); narrow dtypes fill it with
-// two 32-column chunks. The residual (laid out like the output) is read straight into registers,
-// 16 bytes per load, while the TMEM load is in flight.
+// one another (two warps per scheduler ran at a quarter of the issue rate). A box is 32 rows x 64
+// bytes (64B swizzle): 16 fp32, 32 16-bit or 64 int8 columns, 2 KB per warp, which leaves room for a
+// fourth stage in the operand ring. The tile's dequant scales and biases sit in shared memory once
+// per CTA. The residual (laid out like the output) is read straight into registers, 16 bytes per
+// load, while the TMEM load is in flight.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -74,21 +75,14 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool is_h) {
   return *reinterpret_cast<const uint32_t *>(&b);
 }
 
-// Bytes of one box row: the warp's share of the tile's columns, at most one 128-byte swizzle atom.
-template <int BN, int OES>
-struct BoxCfg {
-  static constexpr int kCols = BN / kEpiGroups;  // columns per epilogue warp
-  static constexpr int kRowBytes = kCols * OES < 128 ? kCols * OES : 128;
-  static constexpr int kChunkBytes = 32 * OES;                    // one 32-column chunk of a row
-  static constexpr int kChunksPerBox = kRowBytes / kChunkBytes;   // 1, 2 (or 4)
-  static_assert(kRowBytes == 128 || kRowBytes == 64, "box rows are one 128-byte or one 64-byte swizzle atom");
-};
+// Barrier of the four warps (one per TMEM lane quadrant) that share a column group. Ids 1..4; id 0 is __syncthreads.
+__device__ __forceinline__ void group_barrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 
 template <int KIND, int BN, int ACT, bool BIAS, bool RES, int OES>
 __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtensorMap *omap, uint32_t tmem_base, uint8_t *stage, float *stash,
                                                int group, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag, int q, int lane,
                                                int num_tiles, int tiles_per_batch) {
-  using Box = BoxCfg<BN, OES>;
+  constexpr int COLS = BN / kEpiGroups;  // columns per epilogue warp: 64 or 32
   const GemmEpilogue &e = p.epi;
   float a_scale = e.a_scale;
   if (KIND == GEMM_I8 && e.a_scale_dev) {
@@ -105,23 +99,30 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     rq_s = fmaxf(__ldg(e.requant_absmax), 1e-6f) / 127.0f;
     rq_r = 1.0f / rq_s;
   }
-  const int cbeg = group * Box::kCols, cend = cbeg + Box::kCols;
-  float *sc_stash = stash, *bi_stash = stash + Box::kCols;  // this warp's columns: scale, then bias
+  const int cbeg = group * COLS, cend = cbeg + COLS;
+  // the tile's column operands, one copy per CTA: [0,256) dequant scale, [256,512) bias; this group owns [cbeg, cend)
+  float *sc_stash = stash + cbeg, *bi_stash = stash + 256 + cbeg;
+  // 64-byte box rows with the 64B swizzle: 16-byte piece j of row r sits at piece j ^ ((r >> 1) & 3)
+  uint8_t *rowp = stage + lane * 64;
+  const int sw = (lane >> 1) & 3;
+  bool dead = false;  // a wait ran out: keep taking part in the group barriers, do nothing else
   int it = 0;
   for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
     const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
     const int m0 = (rem / p.tiles_n) * kBM, n0 = (rem % p.tiles_n) * BN;
     const int zb = bz % p.nb1, wb = bz / p.nb1;
     const int buf = it & 1;
-    // column operands of this tile, fetched while the MMAs are still running
-    __syncwarp();
-    for (int c = lane; c < Box::kCols; c += 32) {
-      const int col = n0 + cbeg + c;
+    // Column operands of this tile, fetched while the MMAs are still running. The four warps of the group each
+    // fetch a quarter of the group's columns; the barriers keep a fast warp from overwriting what a slow one still reads.
+    group_barrier(group);
+    if (lane < COLS / 4) {
+      const int c = q * (COLS / 4) + lane, col = n0 + cbeg + c;
       const bool okc = col < p.N;
       if (KIND == GEMM_I8) sc_stash[c] = e.col_scale ? __fmul_rn(a_scale, okc ? __ldg(e.col_scale + col) : 0.f) : a_scale;
       if (BIAS) bi_stash[c] = (okc && e.bias) ? load_as<float>(e.bias, e.bias_dtype, col) : 0.f;
     }
-    __syncwarp();
+    group_barrier(group);
+    if (dead) continue;
     const int row0 = m0 + q * 32, row = row0 + lane;
     const bool row_ok = row < p.M;
     const int lim = min(cend, p.N - n0);  // end of this warp's columns that exist (warp-uniform)
@@ -134,10 +135,12 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) {
       if (lane == 0) report_error(p, abort_flag, 3);
-      break;
+      dead = true;
+      continue;
     }
     tc_fence_after();
     const uint32_t taddr = tmem_base + ((uint32_t)(q * 32) << 16) + (uint32_t)(buf * BN);
+    const bool store = !no_out && row0 < p.M;  // else only the absmax is wanted, or the whole warp is below the bottom edge
     bool released = false;
     for (int c0 = cbeg; c0 < lim; c0 += 32) {
       uint32_t v[32];
@@ -176,44 +179,53 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
 #pragma unroll
         for (int i = 0; i < 32; ++i) local_max = fmaxf(local_max, fabsf(x[i]));
       }
-      if (row0 >= p.M || no_out) continue;  // the whole warp is below the bottom edge, or only the absmax is wanted
-      const int sub = ((c0 - cbeg) >> 5) % Box::kChunksPerBox;
-      if (sub == 0) {
-        // the previous store of this warp must have read the box before it is overwritten
+      if (!store) continue;
+      // a box may be refilled once the previous store of this warp has read it
+      auto begin_box = [&]() {
         if (lane == 0) tma_store_wait_read<0>();
         __syncwarp();
-      }
-      uint8_t *rowp = stage + lane * Box::kRowBytes;
-      const int sw = Box::kRowBytes == 128 ? (lane & 7) : ((lane >> 1) & 3);  // 128B / 64B swizzle of the 16-byte chunk index
-      constexpr int CP = Box::kChunkBytes / 16;                              // 16-byte pieces per 32-column chunk
+      };
+      auto end_box = [&](int col) {
+        fence_proxy_async();
+        __syncwarp();
+        if (lane == 0) {
+          tma_store_4d(omap, stage, col, row0, zb, wb);
+          tma_store_commit();
+        }
+      };
       if (OES == 4) {
+        // 32 fp32 columns = two boxes of 16
 #pragma unroll
-        for (int j = 0; j < 8; ++j)
-          *reinterpret_cast<uint4 *>(rowp + (((sub * CP + j) ^ sw) << 4)) = make_uint4(__float_as_uint(x[4 * j]), __float_as_uint(x[4 * j + 1]),
-                                                                                      __float_as_uint(x[4 * j + 2]), __float_as_uint(x[4 * j + 3]));
+        for (int hb = 0; hb < 2; ++hb) {
+          if (hb == 1 && n0 + c0 + 16 >= p.N) break;  // the second half lies beyond the right edge
+          begin_box();
+#pragma unroll
+          for (int j = 0; j < 4; ++j)
+            *reinterpret_cast<uint4 *>(rowp + ((j ^ sw) << 4)) =
+                make_uint4(__float_as_uint(x[hb * 16 + 4 * j]), __float_as_uint(x[hb * 16 + 4 * j + 1]), __float_as_uint(x[hb * 16 + 4 * j + 2]),
+                           __float_as_uint(x[hb * 16 + 4 * j + 3]));
+          end_box(n0 + c0 + hb * 16);
+        }
       } else if (OES == 2) {
+        begin_box();
 #pragma unroll
         for (int j = 0; j < 4; ++j)
-          *reinterpret_cast<uint4 *>(rowp + (((sub * CP + j) ^ sw) << 4)) =
+          *reinterpret_cast<uint4 *>(rowp + ((j ^ sw) << 4)) =
               make_uint4(pack2(x[8 * j], x[8 * j + 1], is_h), pack2(x[8 * j + 2], x[8 * j + 3], is_h), pack2(x[8 * j + 4], x[8 * j + 5], is_h),
                          pack2(x[8 * j + 6], x[8 * j + 7], is_h));
+        end_box(n0 + c0);
       } else {
-        // int8 requantisation for the next layer: the exact rounding of v / s_next
+        // int8 requantisation for the next layer (the exact rounding of v / s_next): two chunks fill a box
+        const int sub = ((c0 - cbeg) >> 5) & 1;
+        if (sub == 0) begin_box();
 #pragma unroll
         for (int j = 0; j < 2; ++j)
-          *reinterpret_cast<uint4 *>(rowp + (((sub * CP + j) ^ sw) << 4)) =
+          *reinterpret_cast<uint4 *>(rowp + (((sub * 2 + j) ^ sw) << 4)) =
               make_uint4(quant_i8_pack4(x[16 * j], x[16 * j + 1], x[16 * j + 2], x[16 * j + 3], rq_s, rq_r),
                          quant_i8_pack4(x[16 * j + 4], x[16 * j + 5], x[16 * j + 6], x[16 * j + 7], rq_s, rq_r),
                          quant_i8_pack4(x[16 * j + 8], x[16 * j + 9], x[16 * j + 10], x[16 * j + 11], rq_s, rq_r),
                          quant_i8_pack4(x[16 * j + 12], x[16 * j + 13], x[16 * j + 14], x[16 * j + 15], rq_s, rq_r));
-      }
-      if (sub == Box::kChunksPerBox - 1 || c0 + 32 >= lim) {
-        fence_proxy_async();
-        __syncwarp();
-        if (lane == 0) {
-          tma_store_4d(omap, stage, n0 + c0 - sub * 32, row0, zb, wb);
-          tma_store_commit();
-        }
+        if (sub == 1 || c0 + 32 >= lim) end_box(n0 + c0 - sub * 32);
       }
     }
     if (!released) {  // none of this warp's columns exist in this tile

@@ -11,22 +11,33 @@ constexpr int kTileABytes = kBM * kSlabBytes;
 constexpr int kEpiGroups = 4;              // column groups: epilogue warps per TMEM lane quadrant
 constexpr int kEpiWarps = 4 * kEpiGroups;  // each takes a quarter of the tile's columns for its 32 rows
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
-constexpr int kStagePitch = 36;  // words per staged row: 32 + 4 keeps 128-bit accesses conflict-free
-constexpr int kStoreBoxBytes = 32 * 128;  // the TMA-store box of one epilogue warp: 32 rows x (at most) 128 bytes
-constexpr int kEpiStageBytes = kEpiWarps * kStoreBoxBytes;
-constexpr int kPlainWarps = 8;  // the plain-store epilogue splits a tile's columns in two: eight warps work, eight only hand over
+constexpr int kStagePitch = 36;  // plain-store path: words per staged row, 32 + 4 keeps 128-bit accesses conflict-free
+constexpr int kSmemLimit = 232448;  // 227 KB: the most dynamic shared memory one CTA can have
+constexpr int kBarrierBytes = 256;
+// TMA-store epilogue: one 32-row x 64-byte box (64B swizzle) per warp, one copy of the tile's column operands per CTA
+constexpr int kStoreBoxBytes = 32 * 64;
+constexpr int kTmaStageBytes = kEpiWarps * kStoreBoxBytes;
+constexpr int kTmaStashBytes = 2 * 256 * 4;  // scale[256], bias[256]
+// plain-store epilogue: splits a tile's columns in two, so eight warps work and eight only hand the accumulator over
+constexpr int kPlainWarps = 8;
 constexpr int kPlainStageBytes = 32 * kStagePitch * 4;
-static_assert(kPlainWarps * kPlainStageBytes <= kEpiStageBytes, "the plain-store path stages 32 x 36-word blocks in the same area");
-constexpr int kColStashBytes = kPlainWarps * 2 * 256 * 4;  // per plain-store warp: scale and bias of the tile's columns (the TMA path needs less)
-constexpr int kSmemBudget = 150 * 1024;  // for the operand ring
+constexpr int kPlainStashBytes = kPlainWarps * 2 * 256 * 4;
 
-template <int BN>
+// The operand ring takes whatever the epilogue leaves of the 227 KB: with 128 x 256 tiles (48 KB per stage) four
+// stages beside the TMA-store epilogue, three beside the plain-store one. The ring's depth is what bounds the
+// mainloop (a refill takes ~2000 cycles, a stage is consumed in 512): three stages ran the tensor pipe at 41-52 %,
+// four at 28 % more.
+template <int BN, bool TMA_EPI>
 struct TileCfg {
   static constexpr int kTileBBytes = BN * kSlabBytes;
   static constexpr int kStageBytes = kTileABytes + kTileBBytes;
-  static constexpr int kStages = (kSmemBudget / kStageBytes) > 8 ? 8 : (kSmemBudget / kStageBytes);
+  static constexpr int kEpiStageBytes = TMA_EPI ? kTmaStageBytes : kPlainWarps * kPlainStageBytes;
+  static constexpr int kStashBytes = TMA_EPI ? kTmaStashBytes : kPlainStashBytes;
+  static constexpr int kRingBudget = kSmemLimit - kBarrierBytes - kEpiStageBytes - kStashBytes;
+  static constexpr int kStages = (kRingBudget / kStageBytes) > 8 ? 8 : (kRingBudget / kStageBytes);
   static constexpr int kTmemCols = (2 * BN) < 32 ? 32 : 2 * BN;  // two accumulators; a power of two >= 32
-  static constexpr int kSmem = kStages * kStageBytes + kEpiStageBytes + kColStashBytes + 1024 /*alignment slack*/ + 512 /*barriers*/;
+  static constexpr int kSmem = kStages * kStageBytes + kEpiStageBytes + kStashBytes + kBarrierBytes;
+  static_assert(kStages >= 2, "the operand ring needs at least two stages");
 };
 
 struct GemmParams {

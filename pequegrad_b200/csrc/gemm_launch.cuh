@@ -8,23 +8,26 @@
 
 namespace pgb {
 
-template <int KIND, int BN>
+// TMA_EPI: the output is stored with TMA tile stores (small epilogue staging, deeper operand ring); else the
+// plain-store epilogue for outputs TMA cannot address.
+template <int KIND, int BN, bool TMA_EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const __grid_constant__ CUtensorMap tmap_b,
                                                                     const __grid_constant__ CUtensorMap tmap_out,
                                                                     const __grid_constant__ GemmParams p) {
-  using Cfg = TileCfg<BN>;
+  using Cfg = TileCfg<BN, TMA_EPI>;
   constexpr int STAGES = Cfg::kStages;
-  extern __shared__ uint8_t smem_raw[];
+  extern __shared__ __align__(1024) uint8_t smem[];  // the 128B-swizzled tiles need 1024-byte alignment
   // a kernel of an earlier launch gave up on a wait: do nothing until the host has read and cleared the error
   if (*(volatile int *)p.err != 0) return;
-  // 1024-byte alignment for the 128B-swizzled tiles
-  const uint32_t raw = smem_u32(smem_raw);
-  uint8_t *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
+  if (smem_u32(smem) & 1023u) {  // never seen; every thread takes this exit together
+    if (threadIdx.x == 0) atomicCAS(p.err, 0, (7 << 16) | (int)(blockIdx.x & 0xffff));
+    return;
+  }
   uint8_t *tiles = smem;
   uint8_t *epi_stage = smem + STAGES * Cfg::kStageBytes;  // 1024-aligned: every stage is a multiple of 1024 bytes
-  float *col_stash = reinterpret_cast<float *>(smem + STAGES * Cfg::kStageBytes + kEpiStageBytes);
-  uint64_t *bars = reinterpret_cast<uint64_t *>(smem + STAGES * Cfg::kStageBytes + kEpiStageBytes + kColStashBytes);
+  float *col_stash = reinterpret_cast<float *>(epi_stage + Cfg::kEpiStageBytes);
+  uint64_t *bars = reinterpret_cast<uint64_t *>(epi_stage + Cfg::kEpiStageBytes + Cfg::kStashBytes);
   uint64_t *full = bars;                   // [STAGES]  TMA -> MMA
   uint64_t *empty = bars + STAGES;         // [STAGES]  MMA -> TMA
   uint64_t *acc_full = bars + 2 * STAGES;  // [2]       MMA -> epilogue
@@ -111,36 +114,41 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
     const int q = warp & 3;   // a warp may read TMEM lanes 32*(warp%4) .. +31
     const int ew = warp - 2;  // 0..15; the four warps of a lane quadrant split the tile's columns
     if (lane == 0 && p.out_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
-    gemm_epilogue_warp<KIND, BN>(p, &tmap_out, tmem_base, epi_stage, col_stash, ew, acc_full, acc_empty, abort_flag, q, lane, num_tiles,
-                                 tiles_per_batch);
+    gemm_epilogue_warp<KIND, BN, TMA_EPI>(p, &tmap_out, tmem_base, epi_stage, col_stash, ew, acc_full, acc_empty, abort_flag, q, lane, num_tiles,
+                                          tiles_per_batch);
   }
   tc_fence_before();
   __syncthreads();
   if (warp == 1) tmem_dealloc(tmem_base, Cfg::kTmemCols);
 }
 
-template <int KIND, int BN>
+template <int KIND, int BN, bool TMA_EPI>
 static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const GemmParams &p, int grid, cudaStream_t stream) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
-    attr_err = cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN>::kSmem);
+    attr_err = cudaFuncSetAttribute(gemm_tc_kernel<KIND, BN, TMA_EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, TileCfg<BN, TMA_EPI>::kSmem);
   });
   if (attr_err != cudaSuccess) {
     set_error(std::string("matmul: cannot raise the shared-memory limit: ") + cudaGetErrorString(attr_err));
     return PGB_ERR_CUDA;
   }
-  gemm_tc_kernel<KIND, BN><<<grid, kGemmThreads, TileCfg<BN>::kSmem, stream>>>(ma, mb, mo, p);
+  gemm_tc_kernel<KIND, BN, TMA_EPI><<<grid, kGemmThreads, TileCfg<BN, TMA_EPI>::kSmem, stream>>>(ma, mb, mo, p);
   count_launch();
   return check_launch("gemm_tc_kernel");
 }
 
+// p.out_tma != 0 selects the TMA-store kernel (128- and 256-column tiles only).
 template <int KIND>
 int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const GemmParams &p, int grid,
                    cudaStream_t stream) {
-  if (bn == 256) return launch_gemm<KIND, 256>(ma, mb, mo, p, grid, stream);
-  if (bn == 128) return launch_gemm<KIND, 128>(ma, mb, mo, p, grid, stream);
-  return launch_gemm<KIND, 32>(ma, mb, mo, p, grid, stream);
+  if (p.out_tma) {
+    if (bn == 256) return launch_gemm<KIND, 256, true>(ma, mb, mo, p, grid, stream);
+    return launch_gemm<KIND, 128, true>(ma, mb, mo, p, grid, stream);
+  }
+  if (bn == 256) return launch_gemm<KIND, 256, false>(ma, mb, mo, p, grid, stream);
+  if (bn == 128) return launch_gemm<KIND, 128, false>(ma, mb, mo, p, grid, stream);
+  return launch_gemm<KIND, 32, false>(ma, mb, mo, p, grid, stream);
 }
 
 }  // namespace pgb

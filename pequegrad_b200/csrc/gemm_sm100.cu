@@ -104,13 +104,12 @@ static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, 
                                                           : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)std::max<int64_t>(nb1, 1), (cuuint64_t)std::max<int64_t>(nb0, 1)};
   const cuuint64_t strides[3] = {(cuuint64_t)(e.ldc * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
-  // one box row = an epilogue warp's share of a tile row, at most one 128-byte swizzle atom (BoxCfg in gemm_epilogue_tma.cuh)
-  const int row_bytes = std::min(128, bn / kEpiGroups * es);
-  const cuuint32_t box[4] = {(cuuint32_t)(row_bytes / es), 32, 1, 1};
+  // the epilogue's box: 32 rows x 64 bytes, 64B swizzle (gemm_epilogue_tma.cuh)
+  (void)bn;
+  const cuuint32_t box[4] = {(cuuint32_t)(64 / es), 32, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(map, dt, 4, e.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-            row_bytes == 128 ? CU_TENSOR_MAP_SWIZZLE_128B : CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE,
-            CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return fn(map, dt, 4, e.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
+            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
 }
 
 // The device error word that a kernel sets when one of its bounded waits runs out (one per device).
