@@ -7,6 +7,8 @@
 // 480-501). Here a warp keeps its row in registers: one read and one write of
 // the tensor. The arithmetic follows the composites step by step (true
 // division, biased variance, eps added before the square root).
+#include <type_traits>
+
 #include "reduce_common.cuh"
 #include "vec.cuh"
 
@@ -32,20 +34,21 @@ __device__ __forceinline__ float warp_sum(float v) {
   return v;
 }
 
-// e^d for d <= 0 as 2^(d * log2 e) on the special-function unit: one multiply and one ex2.approx
-// (2 ulp). The rounding of the product adds |d| * 1e-7 relative error, below 2e-6 for |d| < 20;
-// e^(-inf) = 0, so masked elements need no special case.
-__device__ __forceinline__ float exp_nonpos(float d) {
+// 2^t on the special-function unit (2 ulp); 2^(-inf) = 0, so masked elements need no special case.
+__device__ __forceinline__ float ex2_approx(float t) {
   float r;
-  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(d * 1.4426950408889634f));
+  asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(t));
   return r;
 }
+// e^d for d <= 0 as 2^(d * log2 e). The rounding of the product adds |d| * 1e-7 relative error,
+// below 2e-6 for |d| < 20.
+__device__ __forceinline__ float exp_nonpos(float d) { return ex2_approx(d * 1.4426950408889634f); }
 
 // One warp per row, the row held in NV vectors of V elements per lane. With a causal mask the
 // vectors that lie wholly above the diagonal are neither loaded nor exponentiated (the test is
 // warp-uniform); they are stored as zeros.
 template <typename IoT, int V, int NV>
-__global__ void __launch_bounds__(256) softmax_warp_kernel(const __grid_constant__ RowsParams p) {
+__global__ void __launch_bounds__(256, 5) softmax_warp_kernel(const __grid_constant__ RowsParams p) {
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
@@ -101,6 +104,99 @@ __global__ void __launch_bounds__(256) softmax_warp_kernel(const __grid_constant
 #pragma unroll
       for (int e = 0; e < V; ++e) o[e] = v[u][e] * inv;
       store_vec<IoT, float, V>(yr + c, o);
+    }
+  }
+}
+
+// 16-bit rows of up to 16 * 256 columns: the row stays in its packed form, 4 registers per 8 elements, so that
+// six CTAs fit on an SM (the fp32-register kernel above ran at 62 % occupancy and was bound by instruction issue
+// and load latency, not by DRAM). Max on packed pairs (exact), exp in fp32 as one fused multiply-add and one
+// ex2.approx per element, the sum in fp32; the unnormalised p in (0, 1] is packed back to 16 bits and scaled by
+// 1 / sum with a packed multiply: three 16-bit roundings, ~1.5e-3 relative, inside the 2e-2 of 16-bit outputs.
+template <typename IoT, int NV>
+__global__ void __launch_bounds__(256, (NV <= 4 ? 6 : (NV <= 8 ? 4 : 2))) softmax_warp16_kernel(const __grid_constant__ RowsParams p) {
+  constexpr bool IS_H = std::is_same<IoT, __half>::value;
+  using T2 = typename std::conditional<IS_H, __half2, __nv_bfloat162>::type;
+  constexpr uint32_t NINF = IS_H ? 0xFC00u : 0xFF80u, NINF2 = NINF | (NINF << 16);
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const IoT *xr = (const IoT *)p.x + row * p.C;
+  IoT *yr = (IoT *)p.y + row * p.C;
+  const int C = (int)p.C;
+  int L = C;
+  if (p.causal_rows > 0) {
+    const int64_t r = p.rows <= 0xffffffffLL ? (int64_t)((uint32_t)row % (uint32_t)p.causal_rows) : row % p.causal_rows;
+    L = (int)min((int64_t)C, r + 1);
+  }
+  uint32_t w[NV][4];
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int c = (u * 32 + lane) * 8;
+    uint4 r = make_uint4(NINF2, NINF2, NINF2, NINF2);
+    if (c < L) r = __ldcs(reinterpret_cast<const uint4 *>(xr + c));
+    w[u][0] = r.x; w[u][1] = r.y; w[u][2] = r.z; w[u][3] = r.w;
+    if (c < L && c + 8 > L) {  // the one lane whose vector straddles the mask
+      const int n = L - c;     // 1..7 elements take part
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const int vj = n - 2 * j;
+        if (vj <= 0) w[u][j] = NINF2;
+        else if (vj == 1) w[u][j] = (w[u][j] & 0xffffu) | (NINF << 16);
+      }
+    }
+  }
+  T2 m2;
+  {
+    const uint32_t init = NINF2;
+    m2 = *reinterpret_cast<const T2 *>(&init);
+  }
+#pragma unroll
+  for (int u = 0; u < NV; ++u)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) m2 = __hmax2(m2, *reinterpret_cast<const T2 *>(&w[u][j]));
+  float2 mf;
+  if constexpr (IS_H) mf = __half22float2(m2);
+  else mf = __bfloat1622float2(m2);
+  const float m = warp_max(fmaxf(mf.x, mf.y));
+  const float ml = m * 1.4426950408889634f;
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    if (u * 256 < L) {  // warp-uniform: vectors wholly above the diagonal are not exponentiated
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        float2 f;
+        if constexpr (IS_H) f = __half22float2(*reinterpret_cast<const T2 *>(&w[u][j]));
+        else f = __bfloat1622float2(*reinterpret_cast<const T2 *>(&w[u][j]));
+        const float p0 = ex2_approx(fmaf(f.x, 1.4426950408889634f, -ml)), p1 = ex2_approx(fmaf(f.y, 1.4426950408889634f, -ml));
+        s += p0 + p1;
+        T2 pk;
+        if constexpr (IS_H) pk = __floats2half2_rn(p0, p1);
+        else pk = __floats2bfloat162_rn(p0, p1);
+        w[u][j] = *reinterpret_cast<const uint32_t *>(&pk);
+      }
+    } else {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) w[u][j] = 0u;
+    }
+  }
+  s = warp_sum(s);
+  const float inv = 1.0f / s;
+  T2 inv2;
+  if constexpr (IS_H) inv2 = __floats2half2_rn(inv, inv);
+  else inv2 = __floats2bfloat162_rn(inv, inv);
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int c = (u * 32 + lane) * 8;
+    if (c < C) {
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const T2 q = __hmul2(*reinterpret_cast<const T2 *>(&w[u][j]), inv2);
+        o[j] = *reinterpret_cast<const uint32_t *>(&q);
+      }
+      *reinterpret_cast<uint4 *>(yr + c) = make_uint4(o[0], o[1], o[2], o[3]);
     }
   }
 }
@@ -251,7 +347,8 @@ static int rows_launch(const RowsParams &p, cudaStream_t stream) {
   if (p.rows > 2147483647LL * 8) return PGB_ERR_UNSUPPORTED;
   const char *name = SOFTMAX ? "softmax_warp_kernel" : "layernorm_warp_kernel";
 #define PGB_ROWS_CASE(NV)                                                                   \
-  if (SOFTMAX) softmax_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p);               \
+  if constexpr (SOFTMAX && sizeof(IoT) == 2) softmax_warp16_kernel<IoT, NV><<<wgrid, 256, 0, stream>>>(p); \
+  else if constexpr (SOFTMAX) softmax_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p); \
   else layernorm_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p)
   if (vec && per_lane_vecs <= 16) {
     if (per_lane_vecs <= 1) { PGB_ROWS_CASE(1); }
