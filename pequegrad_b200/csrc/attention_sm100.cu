@@ -4,7 +4,7 @@
 // additive causal mask, softmax (pequegrad/ops.py:259-267), att @ v, which runs as four kernel chains and
 // materialises the [B, H, T, T] scores twice. Here the scores never leave the SM:
 //   one CTA per (batch, head, block of 128 query rows); keys and values stream in blocks of 64
-//   warp 0      TMA producer: Q once, then K and V blocks into two rings (128B swizzle, no multicast)
+//   warp 0      TMA producer: Q once, then K and V blocks into two rings (128B swizzle, per-CTA loads only)
 //   warp 1      allocates TMEM and issues tcgen05.mma (one thread):
 //                 S = Q K^T    128 x 64 x 64, fp32 in TMEM, double-buffered
 //                 O += P V     128 x 64 x 64, fp32 in TMEM; V is read as an MN-major operand, so it needs no transpose

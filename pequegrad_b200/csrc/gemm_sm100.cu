@@ -1,5 +1,5 @@
 // Dense contractions on the 5th-generation tensor cores: tcgen05.mma with the
-// accumulators in TMEM, operands staged in shared memory by TMA (no multicast),
+// accumulators in TMEM, operands staged in shared memory by TMA (every CTA loads its own tiles),
 // mbarrier pipelines, warp-specialised roles, persistent CTAs. One kernel
 // template, two instruction kinds:
 //   kind::i8   int8 x int8 -> int32   (quantized linear, fused dequant + bias + ReLU)
