@@ -244,7 +244,7 @@ PGB_API int pgb_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, con
  * Replaces MatMul::dispatch_cuda (csrc/cuda/matmul.cu:72-163: cuBLAS strided-batched
  * GEMM; for half inputs the reference accumulates in fp16, here the accumulator
  * is fp32) and FusedLinearBiasAct::dispatch_cuda (csrc/cuda/other.cu:19-166).
- *   a         [.., M, K], f16 or bf16, K contiguous
+ *   a         [.., M, K], f16 or bf16 with K contiguous (fp32: see below)
  *   b         [.., K, N] VIEW whose K dim is the contiguous one, i.e. the transposed
  *             view of an [.., N, K] array (a Linear weight stored transposed once,
  *             or k.transpose(-2,-1) in attention); a 2-D b is shared by all batches of a;
@@ -255,8 +255,13 @@ PGB_API int pgb_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, con
  *             2 GELU, tanh form (pequegrad/ops.py:109-118)
  *   residual  same shape as out, or NULL
  *   out       [.., M, N] f16 / bf16 / f32, N contiguous
- * Row pitches must be multiples of 16 bytes. fp32 / fp64 / int32 operands return
- * PGB_ERR_UNSUPPORTED ("matmul_cuda not implemented for ...").
+ * Row pitches must be multiples of 16 bytes.
+ * fp32 operands (the reference's cublasSgemm path, csrc/cuda/matmul.cu:100-120) are accepted with ANY
+ * strides for a and b: both are split into tf32 big / small parts and packed K-major into a
+ * stream-ordered scratch buffer, and one tf32 tensor-core GEMM over [small|big|big] x
+ * [big|small|big] sums three products per term in the fp32 accumulator: the error stays below
+ * 1e-5 * sum_k |a_ik b_kj| (the classical fp32 dot-product bound for K = 170), ~1e-6 of it in practice.
+ * fp64 / int32 operands return PGB_ERR_UNSUPPORTED ("matmul_cuda not implemented for ...").
  */
 PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, float alpha,
                        const pgb_tensor *residual, const pgb_tensor *out, void *stream);

@@ -30,7 +30,7 @@ NVCC_FLAGS = [
 # + - * / must round as the reference's separate kernels do: no contraction
 EXACT_FLAGS = ["-fmad=false"]
 # files whose arithmetic is not compared bit-for-bit (tensor-core GEMMs)
-FMAD_OK = {"gemm_kind_i8.cu", "gemm_kind_f16.cu", "gemm_kind_bf16.cu"}
+FMAD_OK = {"gemm_kind_i8.cu", "gemm_kind_f16.cu", "gemm_kind_bf16.cu", "gemm_kind_tf32.cu"}
 
 
 def _nvcc() -> str:

@@ -7,7 +7,8 @@
 
 namespace pgb {
 
-enum { GEMM_I8 = 0, GEMM_F16 = 1, GEMM_BF16 = 2 };
+enum { GEMM_I8 = 0, GEMM_F16 = 1, GEMM_BF16 = 2, GEMM_TF32 = 3 };
+inline int gemm_elem_size(int kind) { return kind == GEMM_I8 ? 1 : (kind == GEMM_TF32 ? 4 : 2); }
 enum { ACT_NONE = 0, ACT_RELU = 1, ACT_GELU_TANH = 2 };
 
 // What happens to the accumulator of C[m, n] before it is stored.
@@ -36,6 +37,12 @@ struct GemmEpilogue {
 // (bs0 / bs1 = strides of the outer / inner batch dim).
 int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_bs1, const void *b, int64_t ldb, int64_t b_bs0, int64_t b_bs1,
                 int64_t M, int64_t N, int64_t K, int64_t nb0, int64_t nb1, const GemmEpilogue &epi, cudaStream_t stream);
+// out[b, r, :] = [small | big | big] (second_small = false) or [big | small | big] (true) of in[b, r, 0..K), each
+// segment Kp wide (zero padded): big = x rounded to tf32, small = (x - big) rounded to tf32. Concatenated along K,
+// a tf32 GEMM of two such operands sums small*big + big*small + big*big: near-fp32 accuracy from three tf32 products.
+// Leading dims (up to 6) and the row / column strides of `in` are arbitrary; strides in elements.
+int run_pack_tf32x3(const float *in, float *out, int n_lead, const int64_t *lead_size, const int64_t *lead_stride, int64_t rows, int64_t K,
+                    int64_t Kp, int64_t row_stride, int64_t col_stride, bool second_small, cudaStream_t stream);
 int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream);
 int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float scale, int8_t *q, cudaStream_t stream);
 int read_gemm_error(int *out, bool reset);

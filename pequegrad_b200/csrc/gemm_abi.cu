@@ -65,6 +65,118 @@ static std::string as_mat(const pgb_tensor &t, const char *what, Mat &m, bool ne
   return "";
 }
 
+// fp32 matmul: both operands are re-laid-out as K-major [big | big | small] / [big | small | big] splits
+// (gemm_pack.cu) in a stream-ordered scratch buffer, then one tf32 GEMM of contraction length 3 * Kp runs.
+// Any strides are accepted for a and b, since they are packed anyway.
+static int matmul_f32(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, float alpha, const pgb_tensor *residual,
+                      const pgb_tensor *out, cudaStream_t stream) {
+  if (a->ndim < 2 || b->ndim < 2 || out->ndim != a->ndim) { set_error("matmul: operands need at least 2 dims and the output the rank of a"); return PGB_ERR_INVALID_ARG; }
+  const int nla = a->ndim - 2;
+  if (nla > 6) { set_error("matmul: at most 6 batch dims"); return PGB_ERR_UNSUPPORTED; }
+  const int64_t M = a->shape[nla], K = a->shape[nla + 1], N = b->shape[b->ndim - 1];
+  if (b->shape[b->ndim - 2] != K) { set_error("matmul: contraction dims differ"); return PGB_ERR_INVALID_ARG; }
+  const bool shared_b = b->ndim == 2;
+  if (!shared_b && b->ndim != a->ndim) { set_error("matmul: batch dims differ"); return PGB_ERR_INVALID_ARG; }
+  int64_t nbatch = 1;
+  for (int d = 0; d < nla; ++d) {
+    if (out->shape[d] != a->shape[d] || (!shared_b && b->shape[d] != a->shape[d]) || (residual && residual->shape[d] != a->shape[d])) {
+      set_error("matmul: batch dims differ");
+      return PGB_ERR_INVALID_ARG;
+    }
+    nbatch *= a->shape[d];
+  }
+  for (const pgb_tensor *t : {a, b})
+    for (int d = 0; d < t->ndim; ++d)
+      if (t->stride_bytes[d] % 4 || t->stride_bytes[d] < 0) { set_error("matmul: bad stride"); return PGB_ERR_INVALID_ARG; }
+  if (out->dtype != PGB_F32 && out->dtype != PGB_F16 && out->dtype != PGB_BF16) {
+    set_error(std::string("matmul output not implemented for ") + dtype_name(out->dtype));
+    return PGB_ERR_UNSUPPORTED;
+  }
+  Mat O, R{};
+  std::string err = as_mat(*out, "the output", O, false);
+  if (err.empty() && residual) err = as_mat(*residual, "the residual", R, false);
+  if (!err.empty()) { set_error(err); return PGB_ERR_UNSUPPORTED; }
+  if (O.rows != M || O.cols != N || (residual && (residual->ndim != out->ndim || R.rows != M || R.cols != N))) {
+    set_error("matmul: output shape does not match");
+    return PGB_ERR_INVALID_ARG;
+  }
+  if (M == 0 || N == 0 || nbatch == 0) return PGB_OK;
+  if (K == 0) { set_error("matmul: empty contraction dim"); return PGB_ERR_INVALID_ARG; }
+  // batch layout of the output: folded into M (shared b, contiguous batches) or at most two strided dims
+  int64_t gM = M, nb0 = 1, nb1 = 1, obs0 = 0, obs1 = 0, rbs0 = 0, rbs1 = 0;
+  bool fold = false;
+  if (nla > 0) {
+    int64_t cnt = 1, st = 0;
+    auto folds = [&](const pgb_tensor &t, const Mat &m) { return merge_leading(t, nla, &cnt, &st) && (cnt == 1 || st == m.rows * m.ld); };
+    fold = shared_b && folds(*out, O) && (!residual || folds(*residual, R));
+    if (fold) {
+      gM = M * nbatch;
+    } else {
+      bool found = false;
+      for (int sp = 0; sp <= nla && !found; ++sp) {
+        int64_t c0, c1, d0, d1;
+        bool ok = merge_dims(*out, 0, sp, &c0, &obs0) && merge_dims(*out, sp, nla, &c1, &obs1);
+        if (ok && residual) ok = merge_dims(*residual, 0, sp, &d0, &rbs0) && merge_dims(*residual, sp, nla, &d1, &rbs1);
+        // the packed operands are contiguous over the leading dims in order, so the split must cover them in order too
+        int64_t e0 = 1, e1 = 1;
+        for (int d = 0; d < sp; ++d) e0 *= a->shape[d];
+        for (int d = sp; d < nla; ++d) e1 *= a->shape[d];
+        if (ok && c0 == e0 && c1 == e1) { nb0 = c0; nb1 = c1; found = true; }
+      }
+      if (!found) { set_error("matmul: the batch dims of the output do not reduce to two strided dims"); return PGB_ERR_UNSUPPORTED; }
+    }
+  }
+  GemmEpilogue e{};
+  e.act = act;
+  e.alpha = alpha;
+  e.out = out->data;
+  e.out_dtype = out->dtype;
+  e.ldc = O.ld;
+  e.out_batch = obs1;
+  e.out_batch0 = obs0;
+  if (bias) {
+    if (numel_of(*bias) != N || !is_contiguous(*bias) || dtype_size(bias->dtype) == 0) {
+      set_error("matmul: the bias must be a contiguous vector of the output width");
+      return PGB_ERR_INVALID_ARG;
+    }
+    e.bias = bias->data;
+    e.bias_dtype = bias->dtype;
+  }
+  if (residual) {
+    e.residual = residual->data;
+    e.res_dtype = residual->dtype;
+    e.res_ld = R.ld;
+    e.res_batch = rbs1;
+    e.res_batch0 = rbs0;
+  }
+  if (!device_present()) return PGB_ERR_CUDA;
+  const int64_t Kp = (K + 31) / 32 * 32;  // whole 128-byte slabs per segment
+  const int64_t nbB = (shared_b && fold) || nla == 0 ? 1 : nbatch;
+  const int64_t a_elems = nbatch * M * 3 * Kp, b_elems = nbB * N * 3 * Kp;
+  float *scratch = nullptr;
+  if (cudaMallocAsync(&scratch, (size_t)(a_elems + b_elems) * sizeof(float), stream) != cudaSuccess) {
+    cudaGetLastError();
+    set_error("matmul: cannot allocate the scratch buffer for the split fp32 operands");
+    return PGB_ERR_CUDA;
+  }
+  int64_t lsz[6], lst[6], bst[6];
+  for (int d = 0; d < nla; ++d) {
+    lsz[d] = a->shape[d];
+    lst[d] = a->stride_bytes[d] / 4;
+    bst[d] = shared_b ? 0 : b->stride_bytes[d] / 4;  // a shared b that cannot be folded is replicated per batch
+  }
+  int st = run_pack_tf32x3((const float *)a->data, scratch, nla, lsz, lst, M, K, Kp, a->stride_bytes[nla] / 4, a->stride_bytes[nla + 1] / 4, false,
+                           stream);
+  if (st == PGB_OK)
+    st = run_pack_tf32x3((const float *)b->data, scratch + a_elems, nbB == 1 ? 0 : nla, lsz, bst, N, K, Kp, b->stride_bytes[b->ndim - 1] / 4,
+                         b->stride_bytes[b->ndim - 2] / 4, true, stream);
+  if (st == PGB_OK)
+    st = run_gemm_tc(GEMM_TF32, scratch, 3 * Kp, nb1 * M * 3 * Kp, M * 3 * Kp, scratch + a_elems, 3 * Kp, nbB == 1 ? 0 : nb1 * N * 3 * Kp,
+                     nbB == 1 ? 0 : N * 3 * Kp, gM, N, 3 * Kp, nb0, nb1, e, stream);
+  cudaFreeAsync(scratch, stream);
+  return st;
+}
+
 }  // namespace pgb
 
 using namespace pgb;
@@ -208,6 +320,8 @@ PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tenso
                        const pgb_tensor *out, void *stream) {
   if (!a || !b || !out) { set_error("matmul: null operand"); return PGB_ERR_INVALID_ARG; }
   if (a->dtype != b->dtype) { set_error("matmul: operand dtypes differ"); return PGB_ERR_INVALID_ARG; }
+  if (act < 0 || act > 2) { set_error("matmul: unknown activation"); return PGB_ERR_INVALID_ARG; }
+  if (a->dtype == PGB_F32) return matmul_f32(a, b, bias, act, alpha, residual, out, (cudaStream_t)stream);
   if (a->dtype != PGB_F16 && a->dtype != PGB_BF16) {
     // reference wording, csrc/cuda/matmul.cu:157-160
     set_error(std::string("matmul_cuda not implemented for ") + dtype_name(a->dtype));

@@ -57,13 +57,13 @@ __device__ __forceinline__ void report_error(const GemmParams &p, volatile int *
 }
 
 // Instruction descriptor: c format [4,6) (1 = f32, 2 = s32), a format [7,10), b format [10,13)
-// (f16 kinds: 0 f16, 1 bf16; i8: 1 = signed), a/b major [15],[16] (0 = K-major),
+// (f16 kinds: 0 f16, 1 bf16; tf32 kind: 2; i8: 1 = signed), a/b major [15],[16] (0 = K-major),
 // N >> 3 at [17,23), M >> 4 at [24,29).
 template <int KIND, int BN>
 __device__ __forceinline__ uint32_t make_idesc() {
   uint32_t d = 0;
   const uint32_t cfmt = (KIND == GEMM_I8) ? 2u : 1u;
-  const uint32_t abfmt = (KIND == GEMM_F16) ? 0u : 1u;  // i8 signed = 1, bf16 = 1, f16 = 0
+  const uint32_t abfmt = (KIND == GEMM_F16) ? 0u : (KIND == GEMM_TF32 ? 2u : 1u);  // f16 = 0, bf16 = 1, tf32 = 2; i8 signed = 1
   d |= cfmt << 4;
   d |= abfmt << 7;
   d |= abfmt << 10;

@@ -36,7 +36,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-  constexpr int ES = (KIND == GEMM_I8) ? 1 : 2;
+  constexpr int ES = (KIND == GEMM_I8) ? 1 : (KIND == GEMM_TF32 ? 4 : 2);
   constexpr int SLAB_ELEMS = kSlabBytes / ES;
   const int tiles_per_batch = p.tiles_m * p.tiles_n;
   const int num_tiles = tiles_per_batch * p.batch;

@@ -4,6 +4,7 @@
 // template, two instruction kinds:
 //   kind::i8   int8 x int8 -> int32   (quantized linear, fused dequant + bias + ReLU)
 //   kind::f16  f16 / bf16 -> f32      (matmul / linear with bias, ReLU / GELU, residual)
+//   kind::tf32 tf32 -> f32            (fp32 matmul as three tf32 products of split operands, gemm_pack.cu)
 //
 // Replaces MatMul::dispatch_cuda (cuBLAS strided-batched GEMM with a handle
 // created and destroyed per call, and fp16 ACCUMULATION for half inputs,
@@ -53,7 +54,7 @@ static int make_operand_map(CUtensorMap *map, const void *ptr, int kind, int64_t
                             int64_t bs0, int64_t bs1, int box_rows, const char *what) {
   EncodeTiledFn fn = encode_fn();
   if (!fn) { set_error("matmul: cuTensorMapEncodeTiled is not available from this driver"); return PGB_ERR_CUDA; }
-  const int es = kind == GEMM_I8 ? 1 : 2;
+  const int es = gemm_elem_size(kind);
   // a batch dim of extent 1 has no stride of its own: give it a valid one
   if (nb1 <= 1) bs1 = rows * ld_elems;
   if (nb0 <= 1) bs0 = std::max<int64_t>(nb1, 1) * bs1;
@@ -61,8 +62,10 @@ static int make_operand_map(CUtensorMap *map, const void *ptr, int kind, int64_t
     set_error(std::string("matmul: operand ") + what + " must be 16-byte aligned with row and batch pitches that are multiples of 16 bytes");
     return PGB_ERR_UNSUPPORTED;
   }
-  const CUtensorMapDataType dt = kind == GEMM_I8 ? CU_TENSOR_MAP_DATA_TYPE_UINT8
-                                                 : (kind == GEMM_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16 : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16);
+  const CUtensorMapDataType dt = kind == GEMM_I8     ? CU_TENSOR_MAP_DATA_TYPE_UINT8
+                                 : kind == GEMM_F16  ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
+                                 : kind == GEMM_TF32 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
+                                                     : CU_TENSOR_MAP_DATA_TYPE_BFLOAT16;
   const cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(nb1, 1), (cuuint64_t)std::max<int64_t>(nb0, 1)};
   const cuuint64_t strides[3] = {(cuuint64_t)(ld_elems * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
   const cuuint32_t box[4] = {(cuuint32_t)(kSlabBytes / es), (cuuint32_t)box_rows, 1, 1};
@@ -135,6 +138,7 @@ int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, const C
 extern template int launch_gemm_bn<GEMM_I8>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
 extern template int launch_gemm_bn<GEMM_F16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
 extern template int launch_gemm_bn<GEMM_BF16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
+extern template int launch_gemm_bn<GEMM_TF32>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
 
 // a: [nb0, nb1, M, K], b: [nb0, nb1, N, K], both K contiguous; strides in elements.
 int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_bs1, const void *b, int64_t ldb, int64_t b_bs0, int64_t b_bs1,
@@ -161,7 +165,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   p.M = (int)M;
   p.N = (int)N;
   p.K = (int)K;
-  const int es = kind == GEMM_I8 ? 1 : 2;
+  const int es = gemm_elem_size(kind);
   p.num_kb = (int)((K * es + kSlabBytes - 1) / kSlabBytes);
   p.tiles_m = (int)tiles_m;
   p.tiles_n = (int)tiles_n;
@@ -194,6 +198,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   const int grid = (int)std::min<int64_t>(num_tiles, sm_count());
   if (kind == GEMM_I8) return launch_gemm_bn<GEMM_I8>(bn, ma, mb, mo, p, grid, stream);
   if (kind == GEMM_F16) return launch_gemm_bn<GEMM_F16>(bn, ma, mb, mo, p, grid, stream);
+  if (kind == GEMM_TF32) return launch_gemm_bn<GEMM_TF32>(bn, ma, mb, mo, p, grid, stream);
   return launch_gemm_bn<GEMM_BF16>(bn, ma, mb, mo, p, grid, stream);
 }
 

@@ -165,8 +165,8 @@ def test_linear_epilogues_and_batched_attention_shapes():
 
 
 def test_matmul_errors_follow_the_reference():
-    a = torch.zeros((8, 16), device="cuda")
-    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float32"):
+    a = torch.zeros((8, 16), device="cuda", dtype=torch.float64)
+    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float64"):
         K.matmul(a, a.T)
     h = torch.zeros((16, 16), device="cuda", dtype=torch.float16)
     with pytest.raises(RuntimeError, match="K-major"):
@@ -218,3 +218,30 @@ def test_int8_output_needs_wide_aligned_rows():
         K.qlinear_i8(a, w, ws, a_scale=1.0, out=q, out_absmax=torch.ones(1, device="cuda"))
     with pytest.raises(ValueError, match="device absmax"):
         K.qlinear_i8(a, w, ws, a_scale=1.0, out=q)
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [((3, 4), (4, 5)), ((5, 7), (7, 3)), ((2, 3, 4), (2, 4, 5)),   # tests/test_ops.py:257-274
+                                             ((513, 300), (300, 1000)), ((4, 3, 130, 70), (4, 3, 70, 257)), ((6, 200, 64), (64, 96))])
+def test_fp32_matmul_matches_the_cpu_path(shape_a, shape_b):
+    """fp32 matmul (three tf32 products on the tensor cores) against the reference CPU matmul, at the reference tests' 1e-5."""
+    rng = np.random.default_rng(44)
+    a = rng.uniform(0.5, 0.9, shape_a).astype(np.float32)
+    b = rng.uniform(0.5, 0.9, shape_b).astype(np.float32)
+    want = np.matmul(a.astype(np.float64), b.astype(np.float64))
+    got = K.matmul(cu(a), cu(b)).cpu().numpy()
+    assert_close(got, want, 1e-5, 1e-5)
+    if a.ndim == 2:
+        assert_close(got, oracle.matmul_f32(a, b), 1e-5, 1e-5)
+    # N(0,1) operands (sums that cancel), a transposed-view a, a column-major b and a bias + ReLU epilogue
+    a2 = rng.standard_normal(shape_a[:-2] + (shape_a[-1], shape_a[-2])).astype(np.float32)
+    b2 = rng.standard_normal(shape_b[:-2] + (shape_b[-1], shape_b[-2])).astype(np.float32)
+    bias = rng.standard_normal(shape_b[-1]).astype(np.float32)
+    A2, B2 = cu(a2).transpose(-2, -1), cu(b2).transpose(-2, -1)
+    got2 = K.matmul(A2, B2, bias=cu(bias), act=1).cpu().numpy()
+    at, bt = np.swapaxes(a2, -2, -1).astype(np.float64), np.swapaxes(b2, -2, -1).astype(np.float64)
+    ref2 = np.maximum(np.matmul(at, bt) + bias, 0)
+    # componentwise bound relative to sum_k |a_ik b_kj|: the tensor core truncates when it accumulates, so the error is
+    # a few 1e-6 of that sum rather than fp32's sqrt(K) * 6e-8; 1e-5 is the classical fp32 bound for K = 170
+    bound = 1e-5 * np.matmul(np.abs(at), np.abs(bt)) + 1e-6
+    assert (np.abs(got2 - ref2) <= bound).all(), float((np.abs(got2 - ref2) / bound).max())
+    assert K.device_error() == 0
