@@ -245,9 +245,12 @@ PGB_API int pgb_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, con
  * GEMM; for half inputs the reference accumulates in fp16, here the accumulator
  * is fp32) and FusedLinearBiasAct::dispatch_cuda (csrc/cuda/other.cu:19-166).
  *   a         [.., M, K], f16 or bf16 with K contiguous (fp32: see below)
- *   b         [.., K, N] VIEW whose K dim is the contiguous one, i.e. the transposed
- *             view of an [.., N, K] array (a Linear weight stored transposed once,
- *             or k.transpose(-2,-1) in attention); a 2-D b is shared by all batches of a;
+ *   b         [.., K, N]. Read in place when it is the view whose K dim is the contiguous one,
+ *             i.e. the transposed view of an [.., N, K] array (a Linear weight stored transposed
+ *             once, or k.transpose(-2,-1) in attention); any other view of a or b (row-major
+ *             [K, N], pitches that are not multiples of 16 bytes) is first copied K-major into
+ *             a stream-ordered scratch buffer, as the reference contiguises its inputs.
+ *             A 2-D b is shared by all batches of a;
  *             otherwise the leading dims must reduce to at most two strided batch dims
  *   alpha     scale of the product (1 for a plain matmul; 1/sqrt(d) for attention scores,
  *             pequegrad/ops.py:792-818 divides after the matmul)
@@ -255,7 +258,6 @@ PGB_API int pgb_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, con
  *             2 GELU, tanh form (pequegrad/ops.py:109-118)
  *   residual  same shape as out, or NULL
  *   out       [.., M, N] f16 / bf16 / f32, N contiguous
- * Row pitches must be multiples of 16 bytes.
  * fp32 operands (the reference's cublasSgemm path, csrc/cuda/matmul.cu:100-120) are accepted with ANY
  * strides for a and b: both are split into tf32 big / small parts and packed K-major into a
  * stream-ordered scratch buffer, and one tf32 tensor-core GEMM over [small|big|big] x

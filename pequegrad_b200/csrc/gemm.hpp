@@ -43,6 +43,9 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
 // Leading dims (up to 6) and the row / column strides of `in` are arbitrary; strides in elements.
 int run_pack_tf32x3(const float *in, float *out, int n_lead, const int64_t *lead_size, const int64_t *lead_stride, int64_t rows, int64_t K,
                     int64_t Kp, int64_t row_stride, int64_t col_stride, bool second_small, cudaStream_t stream);
+// out[b, r, 0..Kp) = in[b, r, 0..K) (zero padded) for 2-byte elements: a K-major, 16-byte aligned copy of any view.
+int run_pack_copy16(const void *in, void *out, int n_lead, const int64_t *lead_size, const int64_t *lead_stride, int64_t rows, int64_t K, int64_t Kp,
+                    int64_t row_stride, int64_t col_stride, cudaStream_t stream);
 int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream);
 int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float scale, int8_t *q, cudaStream_t stream);
 int read_gemm_error(int *out, bool reset);

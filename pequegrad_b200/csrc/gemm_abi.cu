@@ -65,6 +65,31 @@ static std::string as_mat(const pgb_tensor &t, const char *what, Mat &m, bool ne
   return "";
 }
 
+// True if the [.., rows, K] view can feed the TMA loads as it is: K contiguous, base and every pitch 16-byte aligned.
+static bool tma_ready(const pgb_tensor &t) {
+  const int es = dtype_size(t.dtype), nd = t.ndim;
+  if (reinterpret_cast<uintptr_t>(t.data) & 15) return false;
+  if (t.shape[nd - 1] > 1 && t.stride_bytes[nd - 1] != es) return false;
+  for (int d = 0; d < nd - 1; ++d)
+    if (t.shape[d] > 1 && (t.stride_bytes[d] % 16 || t.stride_bytes[d] <= 0)) return false;
+  return true;
+}
+
+// Describes a packed copy [lead..., rows, K] with row pitch Kp at `ptr` (contiguous over the leading dims).
+static pgb_tensor packed_view(const pgb_tensor &t, void *ptr, int64_t Kp) {
+  pgb_tensor v = t;
+  const int es = dtype_size(t.dtype), nd = t.ndim;
+  v.data = ptr;
+  int64_t pitch = es;
+  v.stride_bytes[nd - 1] = pitch;
+  pitch *= Kp;
+  for (int d = nd - 2; d >= 0; --d) {
+    v.stride_bytes[d] = pitch;
+    pitch *= t.shape[d];
+  }
+  return v;
+}
+
 // fp32 matmul: both operands are re-laid-out as K-major [big | big | small] / [big | small | big] splits
 // (gemm_pack.cu) in a stream-ordered scratch buffer, then one tf32 GEMM of contraction length 3 * Kp runs.
 // Any strides are accepted for a and b, since they are packed anyway.
@@ -336,12 +361,48 @@ PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tenso
   bt.shape[nb - 1] = b->shape[nb - 2];
   bt.stride_bytes[nb - 2] = b->stride_bytes[nb - 1];
   bt.stride_bytes[nb - 1] = b->stride_bytes[nb - 2];
+  // Operands that TMA cannot read as they are (K not the contiguous dim, e.g. a plain row-major [K, N] b, or pitches that
+  // are not multiples of 16 bytes) are copied K-major into a stream-ordered scratch buffer first, as the reference
+  // contiguises its inputs (csrc/cuda/matmul.cu:80-93). Weights laid out [N, K] once and packed qkv views skip this.
+  pgb_tensor a_use = *a;
+  void *scratch = nullptr;
+  {
+    const bool pack_a = !tma_ready(*a), pack_b = !tma_ready(bt);
+    if ((pack_a || pack_b) && a->shape[a->ndim - 1] == bt.shape[nb - 1] && a->ndim - 2 <= 6 && nb - 2 <= 6 && device_present()) {
+      const int64_t K = a->shape[a->ndim - 1], Kp = (K + 7) / 8 * 8;
+      auto elems = [&](const pgb_tensor &t) { int64_t n = Kp; for (int d = 0; d < t.ndim - 1; ++d) n *= t.shape[d]; return (n + 7) / 8 * 8; };
+      const int64_t na = pack_a ? elems(*a) : 0, nbe = pack_b ? elems(bt) : 0;
+      if (na + nbe > 0) {
+        if (cudaMallocAsync(&scratch, (size_t)(na + nbe) * 2, (cudaStream_t)stream) != cudaSuccess) {
+          cudaGetLastError();
+          set_error("matmul: cannot allocate the scratch buffer for the operand re-layout");
+          return PGB_ERR_CUDA;
+        }
+        auto pack = [&](const pgb_tensor &t, void *dst) {
+          int64_t lsz[6], lst[6];
+          const int nl = t.ndim - 2;
+          for (int d = 0; d < nl; ++d) { lsz[d] = t.shape[d]; lst[d] = t.stride_bytes[d] / 2; }
+          return run_pack_copy16(t.data, dst, nl, lsz, lst, t.shape[nl], K, Kp, t.stride_bytes[nl] / 2, t.stride_bytes[nl + 1] / 2, (cudaStream_t)stream);
+        };
+        int st = PGB_OK;
+        if (pack_a) { st = pack(*a, scratch); a_use = packed_view(*a, scratch, Kp); }
+        if (st == PGB_OK && pack_b) {
+          void *dst = (uint16_t *)scratch + na;
+          st = pack(bt, dst);
+          bt = packed_view(bt, dst, Kp);
+        }
+        if (st != PGB_OK) { cudaFreeAsync(scratch, (cudaStream_t)stream); return st; }
+      }
+    }
+  }
+  struct ScratchGuard {
+    void *p; cudaStream_t s;
+    ~ScratchGuard() { if (p) cudaFreeAsync(p, s); }
+  } guard{scratch, (cudaStream_t)stream};
+  a = &a_use;
   Mat A, B, O;
   std::string err = as_mat(*a, "a", A, false);
-  if (err.empty()) {
-    err = as_mat(bt, "b", B, false);
-    if (!err.empty()) err = "matmul: b must be K-major (pass the transposed view of an [N,K] array); N-major b is not built yet";
-  }
+  if (err.empty()) err = as_mat(bt, "b", B, false);
   if (err.empty()) err = as_mat(*out, "the output", O, false);
   Mat R{};
   if (err.empty() && residual) err = as_mat(*residual, "the residual", R, false);

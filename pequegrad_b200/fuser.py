@@ -52,18 +52,11 @@ def _view(node: T.Tensor, buf: torch.Tensor) -> torch.Tensor:
 
 
 def _matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    def k_major(t, want_last):
-        # the GEMM wants the contraction dim contiguous in memory
-        stride = t.stride(-1) if want_last else t.stride(-2)
-        if stride == 1 or t.shape[-1 if want_last else -2] == 1:
-            return t
-        src = t if want_last else t.transpose(-2, -1)
-        (c,) = K.fused_elementwise([src], [("LOAD", 0)])
-        return c if want_last else c.transpose(-2, -1)
+    # any view goes: the library reads K-major operands in place and re-lays-out the others itself
     if b.dim() > 2 and b.shape[:-2] != a.shape[:-2]:
         batch = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
         a, b = a.expand(batch + a.shape[-2:]), b.expand(batch + b.shape[-2:])
-    return K.matmul(k_major(a, True), k_major(b, False))
+    return K.matmul(a, b)
 
 
 def _emit_leaf(node: T.Tensor, fuse: bool) -> torch.Tensor:

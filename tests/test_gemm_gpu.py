@@ -169,8 +169,6 @@ def test_matmul_errors_follow_the_reference():
     with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float64"):
         K.matmul(a, a.T)
     h = torch.zeros((16, 16), device="cuda", dtype=torch.float16)
-    with pytest.raises(RuntimeError, match="K-major"):
-        K.matmul(h, h)  # [K, N] with N contiguous: not built yet
     with pytest.raises(ValueError):
         K.matmul(h, torch.zeros((24, 8), device="cuda", dtype=torch.float16).T)
 
@@ -244,4 +242,26 @@ def test_fp32_matmul_matches_the_cpu_path(shape_a, shape_b):
     # a few 1e-6 of that sum rather than fp32's sqrt(K) * 6e-8; 1e-5 is the classical fp32 bound for K = 170
     bound = 1e-5 * np.matmul(np.abs(at), np.abs(bt)) + 1e-6
     assert (np.abs(got2 - ref2) <= bound).all(), float((np.abs(got2 - ref2) / bound).max())
+    assert K.device_error() == 0
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_half_matmul_accepts_any_view(dt):
+    """Plain row-major [K, N] b, a transposed a, a contraction length that is not a multiple of 8, sliced bases: the
+    operands that the tensor-map loads cannot read in place are re-laid-out first (the reference contiguises them)."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    r = lambda *s_: (torch.randn(s_, generator=g, device="cuda") * 0.5).to(dt)  # noqa: E731
+    cases = [
+        (r(200, 300), r(300, 130)),                                  # row-major b
+        (r(77, 61), r(61, 45)),                                      # K = 61: pitches of 122 bytes
+        (r(96, 40).T, r(96, 72)),                                    # a is a transposed view
+        (r(3, 50, 64), r(3, 64, 33)),                                # batched, row-major b
+        (r(2, 3, 40, 24)[..., 1:], r(2, 3, 24, 16)[..., 1:, :]),     # sliced: unaligned bases, K = 23
+        (r(4, 30, 48), r(48, 20)),                                   # shared row-major weight
+    ]
+    for a, b in cases:
+        got = K.matmul(a, b).float()
+        want = a.float() @ b.float()
+        tol = 2e-2 * max(1.0, want.abs().max().item())
+        assert got.shape == want.shape and (got - want).abs().max().item() <= tol, (tuple(a.shape), tuple(b.shape))
     assert K.device_error() == 0

@@ -109,7 +109,7 @@ def test_composites_eager_and_jit():
     assert_close(fuser.jit(pg.gelu)(pg.Tensor(x)).numpy(), want, 1e-5)
 
 
-def test_matmul_half_and_reference_error_for_float32():
+def test_matmul_half_float_and_reference_error_for_float64():
     rng = np.random.default_rng(3)
     a = rng.standard_normal((5, 64, 128)).astype(np.float16)
     w = rng.standard_normal((128, 96)).astype(np.float16)
@@ -120,5 +120,10 @@ def test_matmul_half_and_reference_error_for_float32():
     got = (pg.Tensor(a) @ pg.Tensor(b)).numpy().astype(np.float32)
     want = a.astype(np.float32) @ b.astype(np.float32)
     assert_close(got, want, 2e-2, 2e-2 * float(np.abs(want).max()))
-    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float32"):
-        (pg.Tensor(a.astype(np.float32)) @ pg.Tensor(w.astype(np.float32))).eval()
+    # fp32 runs on the tensor cores as three tf32 products per term
+    a32, w32 = a.astype(np.float32), w.astype(np.float32)
+    got = (pg.Tensor(a32) @ pg.Tensor(w32)).numpy()
+    want = a32.astype(np.float64) @ w32.astype(np.float64)
+    assert np.abs(got - want).max() <= 1e-5 * float((np.abs(a32) @ np.abs(w32)).max())
+    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float64"):
+        (pg.Tensor(a.astype(np.float64)) @ pg.Tensor(w.astype(np.float64))).eval()
