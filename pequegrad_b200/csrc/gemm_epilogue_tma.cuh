@@ -94,10 +94,11 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
   const bool is_h = e.out_dtype == PGB_F16;
   const bool no_out = e.out == nullptr;
   const float alpha = e.alpha;
-  float rq_s = 1.f, rq_r = 1.f;
+  float rq_s = 1.f, rq_r = 1.f, rq_thr = 0.f;
   if (OES == 1) {
     rq_s = fmaxf(__ldg(e.requant_absmax), 1e-6f) / 127.0f;
     rq_r = 1.0f / rq_s;
+    rq_thr = 0.49999f * rq_s;
   }
   const int cbeg = group * COLS, cend = cbeg + COLS;
   // the tile's column operands, one copy per CTA: [0,256) dequant scale, [256,512) bias; this group owns [cbeg, cend)
@@ -219,12 +220,20 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
         const int sub = ((c0 - cbeg) >> 5) & 1;
         if (sub == 0) begin_box();
 #pragma unroll
-        for (int j = 0; j < 2; ++j)
-          *reinterpret_cast<uint4 *>(rowp + (((sub * 2 + j) ^ sw) << 4)) =
-              make_uint4(quant_i8_pack4(x[16 * j], x[16 * j + 1], x[16 * j + 2], x[16 * j + 3], rq_s, rq_r),
-                         quant_i8_pack4(x[16 * j + 4], x[16 * j + 5], x[16 * j + 6], x[16 * j + 7], rq_s, rq_r),
-                         quant_i8_pack4(x[16 * j + 8], x[16 * j + 9], x[16 * j + 10], x[16 * j + 11], rq_s, rq_r),
-                         quant_i8_pack4(x[16 * j + 12], x[16 * j + 13], x[16 * j + 14], x[16 * j + 15], rq_s, rq_r));
+        for (int j = 0; j < 2; ++j) {
+          bool recheck = false;
+          uint32_t w[4];
+#pragma unroll
+          for (int g = 0; g < 4; ++g)
+            w[g] = quant_i8_fast4<ACT == ACT_RELU>(x[16 * j + 4 * g], x[16 * j + 4 * g + 1], x[16 * j + 4 * g + 2], x[16 * j + 4 * g + 3], rq_s, rq_r,
+                                                   rq_thr, recheck);
+          if (recheck) {  // some value sits next to a rounding boundary (about one in 60 000): the IEEE division decides
+#pragma unroll
+            for (int g = 0; g < 4; ++g)
+              w[g] = quant_i8_pack4(x[16 * j + 4 * g], x[16 * j + 4 * g + 1], x[16 * j + 4 * g + 2], x[16 * j + 4 * g + 3], rq_s, rq_r);
+          }
+          *reinterpret_cast<uint4 *>(rowp + (((sub * 2 + j) ^ sw) << 4)) = make_uint4(w[0], w[1], w[2], w[3]);
+        }
         if (sub == 1 || c0 + 32 >= lim) end_box(n0 + c0 - sub * 32);
       }
     }

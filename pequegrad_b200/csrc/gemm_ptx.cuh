@@ -172,6 +172,29 @@ __device__ __forceinline__ uint32_t quant_i8_pack4(float a, float b, float c, fl
   return ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(a, s, r)) | ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(b, s, r) << 8) |
          ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(c, s, r) << 16) | ((uint32_t)(uint8_t)(int8_t)(int)quant_i8_exact(d, s, r) << 24);
 }
+// The cheap route to the same four bytes, for the common case: k = rint(clamp(x * r)) by adding 1.5 * 2^23 (the sum's low
+// mantissa byte is k in two's complement, rounding is to nearest even), then the residual x - k * s from one fused
+// multiply-add certifies k: |x - k s| <= 0.49999 s means x / s is at least 1e-5 away from the rounding boundaries, farther
+// than the rounding of the fp32 quotient can move it (4e-6 for |k| < 128), so rint of the IEEE quotient is the same k.
+// Anything else (a boundary, a clamped value, NaN) raises `recheck` and the caller redoes the group with quant_i8_pack4.
+// NONNEG: the values are outputs of a ReLU, so only the upper clamp is needed.
+template <bool NONNEG>
+__device__ __forceinline__ uint32_t quant_i8_fast4(float a, float b, float c, float d, float s, float r, float thr, bool &recheck) {
+  const float kMagic = 12582912.f;  // 1.5 * 2^23
+  const float x[4] = {a, b, c, d};
+  uint32_t t[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    float y = fminf(x[i] * r, 127.f);
+    if (!NONNEG) y = fmaxf(y, -127.f);
+    const float ti = y + kMagic;
+    const float kf = ti - kMagic;
+    recheck |= !(fabsf(fmaf(-kf, s, x[i])) <= thr);
+    t[i] = __float_as_uint(ti);
+  }
+  const uint32_t lo = __byte_perm(t[0], t[1], 0x0040), hi = __byte_perm(t[2], t[3], 0x0040);
+  return __byte_perm(lo, hi, 0x5410);
+}
 
 __device__ __forceinline__ float gelu_tanh(float x) {
   // 0.5 x (1 + tanh(sqrt(2/pi) (x + 0.044715 x^3)))

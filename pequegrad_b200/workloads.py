@@ -78,33 +78,32 @@ class Mlp:
         self.host_out.copy_(self.out, non_blocking=True)
 
     def roofline(self, pk, reps):
-        """The 1024 -> 1024 layer's GEMM (int8 x int8 -> int32, fused dequant + bias + ReLU + absmax, fp32 out) timed alone."""
-        import torch
+        """The 1024 -> 1024 hidden layer's GEMM as the pipeline runs it: the absmax-only pass and the pass that stores
+        requantised int8 (the slower of the two is the reported kernel), plus the fp32-output variant for comparison."""
         from . import kernels as K
         wq, ws, bias = self.mlp.layers[1]
         b = self.mlp._buffers(self.rows, self.X.device)
-        xq, out, amax = b["q"][1], b["h"][1], b["amax"]
-        other = b["h"][0]
-
-        def gemm():
-            K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, out=out, out_absmax=amax[2:3])
-
-        us = _event_us(gemm, reps, flush=lambda: other.zero_())
+        xq, amax = b["q"][1], b["amax"]
+        flush = lambda: b["h"][0].zero_()  # noqa: E731  268 MB: nothing of the operands stays in L2
+        t_abs = _event_us(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, want_out=False, out_absmax=amax[2:3]), reps, flush)
+        t_q = _event_us(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, out=b["q"][2], out_absmax=amax[2:3]), reps, flush)
+        t_f = _event_us(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, out=b["h"][1]), reps, flush)
         ops = 2.0 * self.rows * 1024 * 1024
         peak = 2 * pk["f16"]
+        us = max(t_abs, t_q)
         ach = ops / (us * 1e-6) / 1e12
-        per_layer = {}
-        for i, (wq_i, ws_i, bias_i) in enumerate(self.mlp.layers):
-            def g_i(i=i, wq_i=wq_i, ws_i=ws_i, bias_i=bias_i):
-                K.qlinear_i8(b["q"][i], wq_i, ws_i, a_absmax=amax[i:i + 1], bias=bias_i, relu=i < 2, out=b["h"][i])
-            def q_i(i=i):
-                K.quantize_i8(self.X if i == 0 else b["h"][i - 1], absmax_dev=amax[i:i + 1], out=b["q"][i])
-            per_layer[f"layer{i}"] = {"gemm_us": round(_event_us(g_i, reps), 1), "quantize_us": round(_event_us(q_i, reps), 1)}
-        return {"bound": "tensor", "kernel": "gemm_tc_kernel<i8> 65536x1024x1024 + dequant/bias/ReLU/absmax epilogue", "achieved": round(ach, 1),
-                "peak": peak, "unit": "TOP/s", "frac": round(ach / peak, 4),
+        tops = lambda t: round(ops / (t * 1e-6) / 1e12, 1)  # noqa: E731
+        other = {"absmax_f32_us": round(_event_us(lambda: K.absmax(self.X, out=amax[0:1]), reps), 1),
+                 "quantize_input_us": round(_event_us(lambda: K.quantize_i8(self.X, absmax_dev=amax[0:1], out=b["q"][0]), reps), 1),
+                 "quantize_hidden_us (materialising route only)": round(_event_us(lambda: K.quantize_i8(b["h"][1], absmax_dev=amax[2:3], out=b["q"][2]), reps), 1)}
+        return {"bound": "tensor", "kernel": "gemm_tc_kernel<i8> %dx1024x1024, %s epilogue" % (self.rows, "int8-requantising" if t_q >= t_abs else "absmax-only"),
+                "achieved": round(ach, 1), "peak": peak, "unit": "TOP/s", "frac": round(ach / peak, 4),
                 "peak_source": pk["source"] + " bf16 GEMM rate x 2 (int8 issues at twice the 16-bit rate on the same pipe)",
                 "traffic": None, "us": round(us, 1), "algorithmic_ops_per_launch": ops,
-                "hbm_bytes_per_launch": self.rows * 1024 * 5 + 1024 * 1024, "per_layer": per_layer}
+                "variants": {"absmax_only": {"us": round(t_abs, 1), "tops": tops(t_abs), "frac": round(tops(t_abs) / peak, 4)},
+                             "int8_out": {"us": round(t_q, 1), "tops": tops(t_q), "frac": round(tops(t_q) / peak, 4)},
+                             "fp32_out (268 MB written)": {"us": round(t_f, 1), "tops": tops(t_f), "frac": round(tops(t_f) / peak, 4)}},
+                "other_kernels": other}
 
     def cpu_sample(self, budget_s, threads):
         """The int8 pipeline of the CPU restatement on blocks of 2048 rows until the budget is spent."""
