@@ -19,6 +19,7 @@
 #include <algorithm>
 #include <cmath>
 #include <cstdlib>
+#include <cstring>
 #include <mutex>
 #include <string>
 
@@ -64,6 +65,28 @@ __device__ __forceinline__ float ex2f(float x) {
   float r;
   asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(r) : "f"(x));
   return r;
+}
+
+__device__ __forceinline__ float max3(float a, float b, float c) {
+  float d;
+  asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+  return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+  uint64_t ua, ub, uc, ud;
+  memcpy(&ua, &a, 8); memcpy(&ub, &b, 8); memcpy(&uc, &c, 8);
+  asm("fma.rn.f32x2 %0, %1, %2, %3;" : "=l"(ud) : "l"(ua), "l"(ub), "l"(uc));
+  float2 d;
+  memcpy(&d, &ud, 8);
+  return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+  uint64_t ua, ub, ud;
+  memcpy(&ua, &a, 8); memcpy(&ub, &b, 8);
+  asm("add.rn.f32x2 %0, %1, %2;" : "=l"(ud) : "l"(ua), "l"(ub));
+  float2 d;
+  memcpy(&d, &ud, 8);
+  return d;
 }
 
 __device__ __forceinline__ uint32_t pack_pair(float lo, float hi, bool is_h) {
@@ -216,21 +239,26 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
           if ((p.causal && key > qrow) || key >= p.Tk) s[i] = -INFINITY;
         }
       }
-      float mx = s[0];
+      float mx = max3(s[0], s[1], s[2]);  // three-input max: 32 instructions for the 64 scores
 #pragma unroll
-      for (int i = 1; i < 64; ++i) mx = fmaxf(mx, s[i]);
+      for (int i = 3; i + 1 < 64; i += 2) mx = max3(mx, s[i], s[i + 1]);
+      mx = fmaxf(mx, s[63]);
       const float m_new = fmaxf(m, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no key yet: every p is 0
       const float alpha = ex2f((m - m_use) * c);
       const float mc = m_use * c;
-      float sum = 0.f;
+      // exponent arguments and the row sum on the packed fp32 pipe (two lanes of work per instruction)
+      const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
+      float2 sum2 = make_float2(0.f, 0.f);
       uint32_t pk[32];
 #pragma unroll
       for (int i = 0; i < 64; i += 2) {
-        const float p0 = ex2f(fmaf(s[i], c, -mc)), p1 = ex2f(fmaf(s[i + 1], c, -mc));
-        sum += p0 + p1;
-        pk[i >> 1] = pack_pair(p0, p1, is_h);
+        const float2 t = fma2(make_float2(s[i], s[i + 1]), c2, nmc2);
+        const float2 pp = make_float2(ex2f(t.x), ex2f(t.y));
+        sum2 = add2(sum2, pp);
+        pk[i >> 1] = pack_pair(pp.x, pp.y, is_h);
       }
+      const float sum = sum2.x + sum2.y;
       l = l * alpha + sum;
       m = m_new;
       if (j > 0) {
