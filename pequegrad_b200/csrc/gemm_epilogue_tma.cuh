@@ -45,7 +45,7 @@ template <int OES>
 __device__ __forceinline__ void res_load(ResChunk<OES> &rc, const uint8_t *ptr, bool row_ok, int n_valid) {
   if (n_valid >= 32) {
 #pragma unroll
-    for (int j = 0; j < (OES == 4 ? 8 : 4); ++j) rc.r[j] = row_ok ? reinterpret_cast<const uint4 *>(ptr)[j] : make_uint4(0, 0, 0, 0);
+    for (int j = 0; j < (OES == 4 ? 8 : 4); ++j) rc.r[j] = row_ok ? __ldcs(reinterpret_cast<const uint4 *>(ptr) + j) : make_uint4(0, 0, 0, 0);
   } else {
     res_load_edge<OES>(rc, ptr, row_ok ? n_valid : 0);
   }
