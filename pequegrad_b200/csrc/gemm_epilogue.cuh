@@ -169,12 +169,13 @@ __device__ __noinline__ void gemm_epilogue_tiles(const GemmParams &p, uint32_t t
 // output's element size), the others only the plain-store one above.
 // ew = epilogue warp 0..15: TMEM lane quadrant q = warp % 4, column group ew / 4.
 template <int KIND, int BN, bool TMA_EPI>
-__device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, const CUtensorMap *omap, uint32_t tmem_base, uint8_t *stage_base,
-                                                   float *stash_base, int ew, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag,
-                                                   int q, int lane, int num_tiles, int tiles_per_batch) {
+__device__ __forceinline__ void gemm_epilogue_warp(const GemmParams &p, const CUtensorMap *omap, const CUtensorMap *rmap, uint32_t tmem_base,
+                                                   uint8_t *stage_base, float *stash_base, uint64_t *res_bar, int ew, uint64_t *acc_full,
+                                                   uint64_t *acc_empty, volatile int *abort_flag, int q, int lane, int num_tiles,
+                                                   int tiles_per_batch) {
 #define PGB_EPI_TMA(ACT, BIAS, RES, OES)                                                                                                \
-  gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, OES>(p, omap, tmem_base, stage_base + ew * kStoreBoxBytes, stash_base, ew >> 2, acc_full, acc_empty, \
-                                                   abort_flag, q, lane, num_tiles, tiles_per_batch)
+  gemm_epilogue_tma<KIND, BN, ACT, BIAS, RES, OES>(p, omap, rmap, tmem_base, stage_base + ew * kStoreBoxBytes, stash_base, res_bar, ew >> 2, acc_full, \
+                                                   acc_empty, abort_flag, q, lane, num_tiles, tiles_per_batch)
 #define PGB_EPI(ACT, BIAS, RES)                                                                                           \
   do {                                                                                                                    \
     if constexpr (TMA_EPI) {                                                                                              \

@@ -8,8 +8,7 @@
 // one another (two warps per scheduler ran at a quarter of the issue rate). A box is 32 rows x 64
 // bytes (64B swizzle): 16 fp32, 32 16-bit or 64 int8 columns, 2 KB per warp, which leaves room for a
 // fourth stage in the operand ring. The tile's dequant scales and biases sit in shared memory once
-// per CTA. The residual (laid out like the output) is read straight into registers, 16 bytes per
-// load, while the TMEM load is in flight.
+// per CTA. The residual (laid out like the output) comes through the TMA unit into the same box.
 #pragma once
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
@@ -17,54 +16,6 @@
 #include "gemm_kernel.cuh"
 
 namespace pgb {
-
-template <int OES>
-struct ResChunk {
-  uint4 r[OES == 4 ? 8 : 4];  // 32 residual elements of this thread's row
-};
-
-// Edge chunk: element-wise guarded loads (columns >= n_valid read as zero).
-template <int OES>
-__device__ __noinline__ void res_load_edge(ResChunk<OES> &rc, const uint8_t *ptr, int n_valid) {
-  uint32_t w[OES == 4 ? 32 : 16];
-#pragma unroll
-  for (int i = 0; i < 32; ++i) {
-    if (OES == 4) {
-      w[OES == 4 ? i : 0] = i < n_valid ? reinterpret_cast<const uint32_t *>(ptr)[i] : 0u;
-    } else {
-      const uint32_t h = i < n_valid ? (uint32_t) reinterpret_cast<const uint16_t *>(ptr)[i] : 0u;
-      if (i & 1) w[OES == 4 ? 0 : i >> 1] |= h << 16;
-      else w[OES == 4 ? 0 : i >> 1] = h;
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < (OES == 4 ? 8 : 4); ++j) rc.r[j] = make_uint4(w[4 * j], w[4 * j + 1], w[4 * j + 2], w[4 * j + 3]);
-}
-
-template <int OES>
-__device__ __forceinline__ void res_load(ResChunk<OES> &rc, const uint8_t *ptr, bool row_ok, int n_valid) {
-  if (n_valid >= 32) {
-#pragma unroll
-    for (int j = 0; j < (OES == 4 ? 8 : 4); ++j) rc.r[j] = row_ok ? __ldcs(reinterpret_cast<const uint4 *>(ptr) + j) : make_uint4(0, 0, 0, 0);
-  } else {
-    res_load_edge<OES>(rc, ptr, row_ok ? n_valid : 0);
-  }
-}
-
-template <int OES>
-__device__ __forceinline__ float res_get(const ResChunk<OES> &rc, int i, bool is_h) {
-  if (OES == 4) {
-    const uint4 &q = rc.r[i >> 2];
-    const uint32_t w = (i & 3) == 0 ? q.x : (i & 3) == 1 ? q.y : (i & 3) == 2 ? q.z : q.w;
-    return __uint_as_float(w);
-  } else {
-    const uint4 &q = rc.r[i >> 3];
-    const int k = (i >> 1) & 3;
-    const uint32_t w = k == 0 ? q.x : k == 1 ? q.y : k == 2 ? q.z : q.w;
-    const uint16_t h = (uint16_t)((i & 1) ? (w >> 16) : (w & 0xffffu));
-    return is_h ? __half2float(__ushort_as_half(h)) : __bfloat162float(__ushort_as_bfloat16(h));
-  }
-}
 
 __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool is_h) {
   if (is_h) {
@@ -79,9 +30,9 @@ __device__ __forceinline__ uint32_t pack2(float lo, float hi, bool is_h) {
 __device__ __forceinline__ void group_barrier(int group) { asm volatile("bar.sync %0, 128;" ::"r"(group + 1) : "memory"); }
 
 template <int KIND, int BN, int ACT, bool BIAS, bool RES, int OES>
-__device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtensorMap *omap, uint32_t tmem_base, uint8_t *stage, float *stash,
-                                               int group, uint64_t *acc_full, uint64_t *acc_empty, volatile int *abort_flag, int q, int lane,
-                                               int num_tiles, int tiles_per_batch) {
+__device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtensorMap *omap, const CUtensorMap *rmap, uint32_t tmem_base,
+                                               uint8_t *stage, float *stash, uint64_t *res_bar, int group, uint64_t *acc_full, uint64_t *acc_empty,
+                                               volatile int *abort_flag, int q, int lane, int num_tiles, int tiles_per_batch) {
   constexpr int COLS = BN / kEpiGroups;  // columns per epilogue warp: 64 or 32
   const GemmEpilogue &e = p.epi;
   float a_scale = e.a_scale;
@@ -107,6 +58,7 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
   uint8_t *rowp = stage + lane * 64;
   const int sw = (lane >> 1) & 3;
   bool dead = false;  // a wait ran out: keep taking part in the group barriers, do nothing else
+  uint32_t res_phase = 0;  // parity of this warp's residual barrier
   int it = 0;
   for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
     const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
@@ -127,10 +79,10 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     const int row0 = m0 + q * 32, row = row0 + lane;
     const bool row_ok = row < p.M;
     const int lim = min(cend, p.N - n0);  // end of this warp's columns that exist (warp-uniform)
-    const uint8_t *res_row = nullptr;
-    if (RES)
-      res_row = reinterpret_cast<const uint8_t *>(e.residual) +
-                ((int64_t)wb * e.res_batch0 + (int64_t)zb * e.res_batch + (int64_t)row * e.res_ld + n0) * OES;
+    if (RES && lane == 0 && row0 < p.M) {
+      // this warp's share of the residual tile goes to L2 through the TMA unit while the MMAs still run
+      for (int c = cbeg; c < lim; c += 64 / OES) tma_prefetch_4d(rmap, n0 + c, row0, zb, wb);
+    }
     bool ok = true;
     if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
@@ -145,9 +97,26 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     bool released = false;
     for (int c0 = cbeg; c0 < lim; c0 += 32) {
       uint32_t v[32];
-      ResChunk<OES> rc;
+      // The residual box (same 32 rows x 64 bytes as the output box) is fetched by the TMA unit into the warp's box while
+      // the accumulator chunk is loaded and processed. (Loading it with ordinary global loads cost ~0.4 us per MB of
+      // residual whatever the access pattern: with nearly all of the SM's memory carved out as shared memory, the
+      // load / store unit's miss path is a trickle.)
+      auto res_request = [&](int col) {
+        if (lane == 0) {
+          tma_store_wait_read<0>();  // the previous store of this warp has read the box
+          mbar_expect_tx(res_bar, kStoreBoxBytes);
+          tma_load_4d(stage, rmap, col, row0, zb, wb, res_bar);
+        }
+      };
+      auto res_arrived = [&]() -> bool {
+        bool got = true;
+        if (lane == 0) got = mbar_wait(res_bar, res_phase, abort_flag);
+        got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
+        res_phase ^= 1u;
+        return got;
+      };
+      if (RES && store) res_request(n0 + c0);
       tmem_ld32_issue(taddr + c0, v);
-      if (RES) res_load<OES>(rc, res_row + c0 * OES, row_ok, lim - c0);  // in flight together with the TMEM load
       tmem_ld_wait();
       if (c0 + 32 >= lim) {
         // every TMEM load of this tile has landed in registers: hand the buffer back to the MMA warp
@@ -172,7 +141,6 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
           if (BIAS) t = __fadd_rn(t, b[k]);
           if (ACT == ACT_RELU) t = t > 0.f ? t : 0.f;
           if (ACT == ACT_GELU_TANH) t = gelu_tanh(t);
-          if (RES) t = __fadd_rn(t, res_get<OES>(rc, i + k, is_h));
           x[i + k] = t;
         }
       }
@@ -199,7 +167,18 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
 #pragma unroll
         for (int hb = 0; hb < 2; ++hb) {
           if (hb == 1 && n0 + c0 + 16 >= p.N) break;  // the second half lies beyond the right edge
-          begin_box();
+          if (RES) {
+            if (hb == 1) res_request(n0 + c0 + 16);
+            if (!res_arrived()) { if (lane == 0) report_error(p, abort_flag, 5); dead = true; break; }
+#pragma unroll
+            for (int j = 0; j < 4; ++j) {
+              const uint4 rv = *reinterpret_cast<const uint4 *>(rowp + ((j ^ sw) << 4));
+              x[hb * 16 + 4 * j] += __uint_as_float(rv.x); x[hb * 16 + 4 * j + 1] += __uint_as_float(rv.y);
+              x[hb * 16 + 4 * j + 2] += __uint_as_float(rv.z); x[hb * 16 + 4 * j + 3] += __uint_as_float(rv.w);
+            }
+          } else {
+            begin_box();
+          }
 #pragma unroll
           for (int j = 0; j < 4; ++j)
             *reinterpret_cast<uint4 *>(rowp + ((j ^ sw) << 4)) =
@@ -207,8 +186,26 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
                            __float_as_uint(x[hb * 16 + 4 * j + 3]));
           end_box(n0 + c0 + hb * 16);
         }
+        if (dead) break;
       } else if (OES == 2) {
-        begin_box();
+        if (RES) {
+          if (!res_arrived()) { if (lane == 0) report_error(p, abort_flag, 5); dead = true; break; }
+#pragma unroll
+          for (int j = 0; j < 4; ++j) {
+            const uint4 rv = *reinterpret_cast<const uint4 *>(rowp + ((j ^ sw) << 4));
+            const uint32_t w[4] = {rv.x, rv.y, rv.z, rv.w};
+#pragma unroll
+            for (int k = 0; k < 4; ++k) {
+              float2 f;
+              if (is_h) f = __half22float2(*reinterpret_cast<const __half2 *>(&w[k]));
+              else f = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162 *>(&w[k]));
+              x[8 * j + 2 * k] += f.x;
+              x[8 * j + 2 * k + 1] += f.y;
+            }
+          }
+        } else {
+          begin_box();
+        }
 #pragma unroll
         for (int j = 0; j < 4; ++j)
           *reinterpret_cast<uint4 *>(rowp + ((j ^ sw) << 4)) =

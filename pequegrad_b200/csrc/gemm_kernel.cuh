@@ -13,7 +13,7 @@ constexpr int kEpiWarps = 4 * kEpiGroups;  // each takes a quarter of the tile's
 constexpr int kGemmThreads = 64 + 32 * kEpiWarps;
 constexpr int kStagePitch = 36;  // plain-store path: words per staged row, 32 + 4 keeps 128-bit accesses conflict-free
 constexpr int kSmemLimit = 232448;  // 227 KB: the most dynamic shared memory one CTA can have
-constexpr int kBarrierBytes = 256;
+constexpr int kBarrierBytes = 512;  // up to 8 + 8 ring barriers, 4 accumulator barriers, 16 residual barriers, two words
 // TMA-store epilogue: one 32-row x 64-byte box (64B swizzle) per warp, one copy of the tile's column operands per CTA
 constexpr int kStoreBoxBytes = 32 * 64;
 constexpr int kTmaStageBytes = kEpiWarps * kStoreBoxBytes;

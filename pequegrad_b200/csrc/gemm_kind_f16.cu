@@ -2,5 +2,5 @@
 #include "gemm_launch.cuh"
 
 namespace pgb {
-template int launch_gemm_bn<GEMM_F16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
+template int launch_gemm_bn<GEMM_F16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
 }  // namespace pgb

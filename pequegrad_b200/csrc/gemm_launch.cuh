@@ -14,6 +14,7 @@ template <int KIND, int BN, bool TMA_EPI>
 __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_constant__ CUtensorMap tmap_a,
                                                                     const __grid_constant__ CUtensorMap tmap_b,
                                                                     const __grid_constant__ CUtensorMap tmap_out,
+                                                                    const __grid_constant__ CUtensorMap tmap_res,
                                                                     const __grid_constant__ GemmParams p) {
   using Cfg = TileCfg<BN, TMA_EPI>;
   constexpr int STAGES = Cfg::kStages;
@@ -32,7 +33,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   uint64_t *empty = bars + STAGES;         // [STAGES]  MMA -> TMA
   uint64_t *acc_full = bars + 2 * STAGES;  // [2]       MMA -> epilogue
   uint64_t *acc_empty = acc_full + 2;      // [2]       epilogue -> MMA
-  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(acc_empty + 2);
+  uint64_t *res_bars = acc_empty + 2;      // [kEpiWarps] TMA -> epilogue warp: its residual box has landed
+  uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(res_bars + kEpiWarps);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -44,6 +46,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   if (threadIdx.x == 0) {
     for (int s = 0; s < STAGES; ++s) { mbar_init(&full[s], 1); mbar_init(&empty[s], 1); }
     for (int b = 0; b < 2; ++b) { mbar_init(&acc_full[b], 1); mbar_init(&acc_empty[b], kEpiWarps); }
+    for (int w = 0; w < kEpiWarps; ++w) mbar_init(&res_bars[w], 1);
     *abort_flag = 0;
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
@@ -113,9 +116,12 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
   } else {
     const int q = warp & 3;   // a warp may read TMEM lanes 32*(warp%4) .. +31
     const int ew = warp - 2;  // 0..15; the four warps of a lane quadrant split the tile's columns
-    if (lane == 0 && p.out_tma) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
-    gemm_epilogue_warp<KIND, BN, TMA_EPI>(p, &tmap_out, tmem_base, epi_stage, col_stash, ew, acc_full, acc_empty, abort_flag, q, lane, num_tiles,
-                                          tiles_per_batch);
+    if (lane == 0 && p.out_tma) {
+      asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_out) : "memory");
+      if (p.epi.residual) asm volatile("prefetch.tensormap [%0];" ::"l"(&tmap_res) : "memory");
+    }
+    gemm_epilogue_warp<KIND, BN, TMA_EPI>(p, &tmap_out, &tmap_res, tmem_base, epi_stage, col_stash, res_bars + ew, ew, acc_full, acc_empty, abort_flag,
+                                          q, lane, num_tiles, tiles_per_batch);
   }
   tc_fence_before();
   __syncthreads();
@@ -123,7 +129,7 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
 }
 
 template <int KIND, int BN, bool TMA_EPI>
-static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const GemmParams &p, int grid, cudaStream_t stream) {
+static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const CUtensorMap &mr, const GemmParams &p, int grid, cudaStream_t stream) {
   static std::once_flag once;
   static cudaError_t attr_err = cudaSuccess;
   std::call_once(once, [] {
@@ -133,22 +139,22 @@ static int launch_gemm(const CUtensorMap &ma, const CUtensorMap &mb, const CUten
     set_error(std::string("matmul: cannot raise the shared-memory limit: ") + cudaGetErrorString(attr_err));
     return PGB_ERR_CUDA;
   }
-  gemm_tc_kernel<KIND, BN, TMA_EPI><<<grid, kGemmThreads, TileCfg<BN, TMA_EPI>::kSmem, stream>>>(ma, mb, mo, p);
+  gemm_tc_kernel<KIND, BN, TMA_EPI><<<grid, kGemmThreads, TileCfg<BN, TMA_EPI>::kSmem, stream>>>(ma, mb, mo, mr, p);
   count_launch();
   return check_launch("gemm_tc_kernel");
 }
 
 // p.out_tma != 0 selects the TMA-store kernel (128- and 256-column tiles only).
 template <int KIND>
-int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const GemmParams &p, int grid,
+int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const CUtensorMap &mr, const GemmParams &p, int grid,
                    cudaStream_t stream) {
   if (p.out_tma) {
-    if (bn == 256) return launch_gemm<KIND, 256, true>(ma, mb, mo, p, grid, stream);
-    return launch_gemm<KIND, 128, true>(ma, mb, mo, p, grid, stream);
+    if (bn == 256) return launch_gemm<KIND, 256, true>(ma, mb, mo, mr, p, grid, stream);
+    return launch_gemm<KIND, 128, true>(ma, mb, mo, mr, p, grid, stream);
   }
-  if (bn == 256) return launch_gemm<KIND, 256, false>(ma, mb, mo, p, grid, stream);
-  if (bn == 128) return launch_gemm<KIND, 128, false>(ma, mb, mo, p, grid, stream);
-  return launch_gemm<KIND, 32, false>(ma, mb, mo, p, grid, stream);
+  if (bn == 256) return launch_gemm<KIND, 256, false>(ma, mb, mo, mr, p, grid, stream);
+  if (bn == 128) return launch_gemm<KIND, 128, false>(ma, mb, mo, mr, p, grid, stream);
+  return launch_gemm<KIND, 32, false>(ma, mb, mo, mr, p, grid, stream);
 }
 
 }  // namespace pgb

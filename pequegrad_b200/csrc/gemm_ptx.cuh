@@ -46,6 +46,10 @@ __device__ __forceinline__ void tma_load_4d(void *smem_dst, const CUtensorMap *t
       "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
       : "memory");
 }
+// Asks the TMA unit to bring a tile into L2 (no shared-memory destination, nothing to wait for).
+__device__ __forceinline__ void tma_prefetch_4d(const CUtensorMap *tmap, int x, int y, int z, int w) {
+  asm volatile("cp.async.bulk.prefetch.tensor.4d.L2.global.tile [%0, {%1, %2, %3, %4}];" ::"l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w) : "memory");
+}
 __device__ __forceinline__ void tmem_alloc(uint32_t *smem_result, uint32_t ncols) {
   asm volatile("tcgen05.alloc.cta_group::1.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(smem_u32(smem_result)), "r"(ncols) : "memory");
   asm volatile("tcgen05.relinquish_alloc_permit.cta_group::1.sync.aligned;" ::: "memory");

@@ -93,14 +93,21 @@ bool encode_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, co
 
 // The output as a 4-D tensor map for TMA tile stores: {N, M, nb1, nb0} with a {128 bytes, 32 rows, 1, 1} box, 128B swizzle.
 // Returns false (and leaves the plain-store epilogue in charge) when the layout does not meet TMA's alignment rules.
+static bool make_box_map(CUtensorMap *map, void *ptr, int dtype, int64_t ld, int64_t bs0, int64_t bs1, int64_t M, int64_t N, int64_t nb0, int64_t nb1);
 static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, int64_t N, int64_t nb0, int64_t nb1, int bn) {
+  (void)bn;
+  return make_box_map(map, e.out, e.out_dtype, e.ldc, e.out_batch0, e.out_batch, M, N, nb0, nb1);
+}
+// [nb0, nb1, M, N] with N contiguous -> 4-D tensor map with the epilogue's 32-row x 64-byte box (64B swizzle).
+static bool make_box_map(CUtensorMap *map, void *ptr, int dtype, int64_t ld, int64_t bs0, int64_t bs1, int64_t M, int64_t N, int64_t nb0, int64_t nb1) {
   EncodeTiledFn fn = encode_fn();
-  if (!fn || !e.out) return false;
-  const int es = e.out_dtype == PGB_F32 ? 4 : (e.out_dtype == PGB_I8 ? 1 : 2);
-  int64_t bs1 = e.out_batch, bs0 = e.out_batch0;
-  if (nb1 <= 1) bs1 = M * e.ldc;
+  if (!fn || !ptr) return false;
+  GemmEpilogue e{};
+  e.out = ptr; e.out_dtype = dtype; e.ldc = ld;
+  const int es = dtype == PGB_F32 ? 4 : (dtype == PGB_I8 ? 1 : 2);
+  if (nb1 <= 1) bs1 = M * ld;
   if (nb0 <= 1) bs0 = std::max<int64_t>(nb1, 1) * bs1;
-  if ((reinterpret_cast<uintptr_t>(e.out) & 15) || (e.ldc * es) % 16 || (bs1 * es) % 16 || (bs0 * es) % 16 || e.ldc < N) return false;
+  if ((reinterpret_cast<uintptr_t>(ptr) & 15) || (ld * es) % 16 || (bs1 * es) % 16 || (bs0 * es) % 16 || ld < N) return false;
   const CUtensorMapDataType dt = e.out_dtype == PGB_F32   ? CU_TENSOR_MAP_DATA_TYPE_FLOAT32
                                  : e.out_dtype == PGB_I8  ? CU_TENSOR_MAP_DATA_TYPE_UINT8
                                  : e.out_dtype == PGB_F16 ? CU_TENSOR_MAP_DATA_TYPE_FLOAT16
@@ -108,7 +115,6 @@ static bool make_output_map(CUtensorMap *map, const GemmEpilogue &e, int64_t M, 
   const cuuint64_t dims[4] = {(cuuint64_t)N, (cuuint64_t)M, (cuuint64_t)std::max<int64_t>(nb1, 1), (cuuint64_t)std::max<int64_t>(nb0, 1)};
   const cuuint64_t strides[3] = {(cuuint64_t)(e.ldc * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
   // the epilogue's box: 32 rows x 64 bytes, 64B swizzle (gemm_epilogue_tma.cuh)
-  (void)bn;
   const cuuint32_t box[4] = {(cuuint32_t)(64 / es), 32, 1, 1};
   const cuuint32_t estr[4] = {1, 1, 1, 1};
   return fn(map, dt, 4, e.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
@@ -134,11 +140,12 @@ int *gemm_error_word() {
 
 // one instantiation per instruction kind, each in its own translation unit (gemm_kind_*.cu)
 template <int KIND>
-int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const GemmParams &p, int grid, cudaStream_t stream);
-extern template int launch_gemm_bn<GEMM_I8>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
-extern template int launch_gemm_bn<GEMM_F16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
-extern template int launch_gemm_bn<GEMM_BF16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
-extern template int launch_gemm_bn<GEMM_TF32>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
+int launch_gemm_bn(int bn, const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const CUtensorMap &mr, const GemmParams &p, int grid,
+                   cudaStream_t stream);
+extern template int launch_gemm_bn<GEMM_I8>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
+extern template int launch_gemm_bn<GEMM_F16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
+extern template int launch_gemm_bn<GEMM_BF16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
+extern template int launch_gemm_bn<GEMM_TF32>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
 
 // a: [nb0, nb1, M, K], b: [nb0, nb1, N, K], both K contiguous; strides in elements.
 int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_bs1, const void *b, int64_t ldb, int64_t b_bs0, int64_t b_bs1,
@@ -188,6 +195,9 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
            (rb1 * oes) % 16 == 0 && (rb0 * oes) % 16 == 0;
   }
   if (fast && !absmax_only) fast = make_output_map(&mo, epi, M, N, nb0, nb1, bn);
+  CUtensorMap mr = mo;
+  if (fast && epi.residual)
+    fast = make_box_map(&mr, const_cast<void *>(epi.residual), epi.res_dtype, epi.res_ld, epi.res_batch0, epi.res_batch, M, N, nb0, nb1);
   if (oes == 1 && !fast) {
     set_error("qlinear: an int8 output needs more than 128 output channels, a 16-byte aligned base and row pitch, and a device absmax");
     return PGB_ERR_UNSUPPORTED;
@@ -196,10 +206,10 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   p.res_vec = fast && epi.residual;
   const int64_t num_tiles = tiles_m * tiles_n * batch;
   const int grid = (int)std::min<int64_t>(num_tiles, sm_count());
-  if (kind == GEMM_I8) return launch_gemm_bn<GEMM_I8>(bn, ma, mb, mo, p, grid, stream);
-  if (kind == GEMM_F16) return launch_gemm_bn<GEMM_F16>(bn, ma, mb, mo, p, grid, stream);
-  if (kind == GEMM_TF32) return launch_gemm_bn<GEMM_TF32>(bn, ma, mb, mo, p, grid, stream);
-  return launch_gemm_bn<GEMM_BF16>(bn, ma, mb, mo, p, grid, stream);
+  if (kind == GEMM_I8) return launch_gemm_bn<GEMM_I8>(bn, ma, mb, mo, mr, p, grid, stream);
+  if (kind == GEMM_F16) return launch_gemm_bn<GEMM_F16>(bn, ma, mb, mo, mr, p, grid, stream);
+  if (kind == GEMM_TF32) return launch_gemm_bn<GEMM_TF32>(bn, ma, mb, mo, mr, p, grid, stream);
+  return launch_gemm_bn<GEMM_BF16>(bn, ma, mb, mo, mr, p, grid, stream);
 }
 
 int read_gemm_error(int *out, bool reset) {
