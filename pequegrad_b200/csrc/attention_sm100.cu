@@ -6,13 +6,14 @@
 //   one CTA per (batch, head, block of 128 query rows); keys and values stream in blocks of 64
 //   warp 0      TMA producer: Q once, then K and V blocks into two rings (128B swizzle, per-CTA loads only)
 //   warp 1      allocates TMEM and issues tcgen05.mma (one thread):
-//                 S = Q K^T    128 x 64 x 64, fp32 in TMEM, double-buffered
+//                 S = Q K^T    128 x 64 x 64, fp32 in TMEM
 //                 O += P V     128 x 64 x 64, fp32 in TMEM; V is read as an MN-major operand, so it needs no transpose
 //   warps 2-5   softmax: thread = query row. tcgen05.ld the row of S, mask, online max / sum with exp2 on the
 //               SFU, rescale the row of O in TMEM when its max grew, write P (16-bit) to shared memory in the
 //               K-major 128B-swizzled operand layout for the PV MMA; at the end O / sum -> global
-// Two CTAs fit per SM (about 100 KB of shared memory and 256 TMEM columns each), so one CTA's MMAs run under
-// the other's exponentials. Every wait is bounded; a timeout sets the device error word and the CTA drains.
+// Three CTAs fit per SM (65 KB of shared memory and 128 TMEM columns each), so one CTA's MMAs and loads run
+// under the others' exponentials: the kernel is bound by its softmax warps, and three per scheduler hide the
+// TMEM, barrier and SFU latencies of one another better than two did. Every wait is bounded; a timeout sets the device error word and the CTA drains.
 #include <cuda_bf16.h>
 #include <cuda_fp16.h>
 
@@ -31,11 +32,12 @@ namespace pgb {
 constexpr int kQB = 128;  // query rows per CTA
 constexpr int kKB = 64;   // keys per block
 constexpr int kHD = 64;   // head dim
-constexpr int kKStages = 4, kVStages = 4;
+constexpr int kKStages = 2, kVStages = 2;
 constexpr int kAttnThreads = 192;
 constexpr int kQBytes = kQB * kHD * 2, kKVBytes = kKB * kHD * 2, kPBytes = kQB * kKB * 2;
 constexpr int kAttnSmem = kQBytes + (kKStages + kVStages) * kKVBytes + kPBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
-constexpr int kAttnTmemCols = 256;  // S0 [0,64), S1 [64,128), O [128,192)
+constexpr int kAttnTmemCols = 128;  // S [0,64), O [64,128)
+constexpr int kAttnCtasPerSm = 3;
 
 struct AttnParams {
   int T, Tk, H, B, n_qblk;
@@ -103,7 +105,7 @@ __device__ __forceinline__ void attn_fail(const AttnParams &p, volatile int *abo
   atomicCAS(p.err, 0, ((8 + role) << 16) | (int)(blockIdx.x & 0xffff));
 }
 
-__global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
+__global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_kernel(const __grid_constant__ CUtensorMap map_q,
                                                                         const __grid_constant__ CUtensorMap map_k,
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         const __grid_constant__ AttnParams p) {
@@ -121,9 +123,9 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
   uint64_t *k_empty = k_full + kKStages;     // [kKStages]
   uint64_t *v_full = k_empty + kKStages;     // [kVStages]
   uint64_t *v_empty = v_full + kVStages;     // [kVStages]
-  uint64_t *s_full = v_empty + kVStages;     // [2]  MMA -> softmax
-  uint64_t *s_free = s_full + 2;             // [2]  softmax -> MMA (4 warps)
-  uint64_t *p_full = s_free + 2;             // [1]  softmax -> MMA (4 warps): P written, O rescaled
+  uint64_t *s_full = v_empty + kVStages;     // [1]  MMA -> softmax
+  uint64_t *s_free = s_full + 1;             // [1]  softmax -> MMA (4 warps): S is in registers
+  uint64_t *p_full = s_free + 1;             // [1]  softmax -> MMA (4 warps): P written, O rescaled
   uint64_t *pv_done = p_full + 1;            // [1]  MMA -> softmax: P and V consumed, O updated
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pv_done + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
@@ -141,7 +143,8 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
     mbar_init(q_full, 1);
     for (int s = 0; s < kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
-    for (int s = 0; s < 2; ++s) { mbar_init(&s_full[s], 1); mbar_init(&s_free[s], 4); }
+    mbar_init(s_full, 1);
+    mbar_init(s_free, 4);
     mbar_init(p_full, 4);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
@@ -176,17 +179,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
       const uint64_t dq = make_kmajor_sw128_desc(smem_u32(q_s)), dp = make_kmajor_sw128_desc(smem_u32(p_s));
       bool ok = mbar_wait(q_full, 0, abort_flag);
       if (!ok) attn_fail(p, abort_flag, 3);
-      // S(j) = Q K(j)^T into S buffer j & 1
+      // S(j) = Q K(j)^T; the single S buffer is free once the softmax warps hold S(j-1) in registers
       auto issue_s = [&](int j) -> bool {
-        const int ks = j % kKStages, sb = j & 1;
+        const int ks = j % kKStages;
         if (!mbar_wait(&k_full[ks], (j / kKStages) & 1, abort_flag)) { attn_fail(p, abort_flag, 4); return false; }
-        if (!mbar_wait(&s_free[sb], ((j >> 1) & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 5); return false; }
+        if (!mbar_wait(s_free, (j & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 5); return false; }
         tc_fence_after();
         const uint64_t dk = make_kmajor_sw128_desc(smem_u32(k_s + ks * kKVBytes));
 #pragma unroll
-        for (int kk = 0; kk < 4; ++kk) tc_mma<GEMM_F16>(tmem_base + (uint32_t)(sb * 64), dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
+        for (int kk = 0; kk < 4; ++kk) tc_mma<GEMM_F16>(tmem_base, dq + 2 * kk, dk + 2 * kk, idesc_s, kk != 0);
         tc_commit(&k_empty[ks]);
-        tc_commit(&s_full[sb]);
+        tc_commit(s_full);
         return true;
       };
       if (ok && n_kb > 0) ok = issue_s(0);
@@ -202,7 +205,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
         const uint32_t v_addr = smem_u32(v_s + vs * kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 16 keys per MMA: 32 bytes along P's rows, 16 rows of V
-          tc_mma<GEMM_F16>(tmem_base + 128u, dp + 2 * kk, make_mnmajor_sw128_desc(v_addr + kk * 2048, p.v_lbo), idesc_pv, (j | kk) != 0);
+          tc_mma<GEMM_F16>(tmem_base + 64u, dp + 2 * kk, make_mnmajor_sw128_desc(v_addr + kk * 2048, p.v_lbo), idesc_pv, (j | kk) != 0);
         tc_commit(&v_empty[vs]);
         tc_commit(pv_done);
       }
@@ -216,18 +219,17 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kb; ++j) {
-      const int sb = j & 1;
-      if (lane == 0) ok = mbar_wait(&s_full[sb], (j >> 1) & 1, abort_flag);
+      if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag);
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok) { if (lane == 0) attn_fail(p, abort_flag, 8); break; }
       tc_fence_after();
       uint32_t sa[32], sbv[32];
-      tmem_ld32_issue(lane_addr + (uint32_t)(sb * 64), sa);
-      tmem_ld32_issue(lane_addr + (uint32_t)(sb * 64 + 32), sbv);
+      tmem_ld32_issue(lane_addr, sa);
+      tmem_ld32_issue(lane_addr + 32u, sbv);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&s_free[sb]);
+      if (lane == 0) mbar_arrive(s_free);
       float s[64];
 #pragma unroll
       for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(sa[i]); s[32 + i] = __uint_as_float(sbv[i]); }
@@ -239,26 +241,33 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
           if ((p.causal && key > qrow) || key >= p.Tk) s[i] = -INFINITY;
         }
       }
-      float mx = max3(s[0], s[1], s[2]);  // three-input max: 32 instructions for the 64 scores
+      // three-input max, four independent chains (a single chain of 32 dependent operations left the scheduler idle)
+      float mq[4];
 #pragma unroll
-      for (int i = 3; i + 1 < 64; i += 2) mx = max3(mx, s[i], s[i + 1]);
-      mx = fmaxf(mx, s[63]);
+      for (int g = 0; g < 4; ++g) {
+        mq[g] = max3(s[16 * g], s[16 * g + 1], s[16 * g + 2]);
+#pragma unroll
+        for (int i = 3; i + 1 < 16; i += 2) mq[g] = max3(mq[g], s[16 * g + i], s[16 * g + i + 1]);
+        mq[g] = fmaxf(mq[g], s[16 * g + 15]);
+      }
+      const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
       const float m_new = fmaxf(m, mx);
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no key yet: every p is 0
       const float alpha = ex2f((m - m_use) * c);
       const float mc = m_use * c;
       // exponent arguments and the row sum on the packed fp32 pipe (two lanes of work per instruction)
       const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
-      float2 sum2 = make_float2(0.f, 0.f);
+      float2 sq[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
       uint32_t pk[32];
 #pragma unroll
       for (int i = 0; i < 64; i += 2) {
         const float2 t = fma2(make_float2(s[i], s[i + 1]), c2, nmc2);
         const float2 pp = make_float2(ex2f(t.x), ex2f(t.y));
-        sum2 = add2(sum2, pp);
+        sq[(i >> 1) & 3] = add2(sq[(i >> 1) & 3], pp);  // four independent partial sums
         pk[i >> 1] = pack_pair(pp.x, pp.y, is_h);
       }
-      const float sum = sum2.x + sum2.y;
+      const float2 s01 = add2(sq[0], sq[1]), s23 = add2(sq[2], sq[3]);
+      const float sum = (s01.x + s01.y) + (s23.x + s23.y);
       l = l * alpha + sum;
       m = m_new;
       if (j > 0) {
@@ -272,11 +281,11 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
 #pragma unroll
           for (int half = 0; half < 2; ++half) {
             uint32_t o[32];
-            tmem_ld32_issue(lane_addr + 128u + (uint32_t)(half * 32), o);
+            tmem_ld32_issue(lane_addr + 64u + (uint32_t)(half * 32), o);
             tmem_ld_wait();
 #pragma unroll
             for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(lane_addr + 128u + (uint32_t)(half * 32), o);
+            tmem_st32(lane_addr + 64u + (uint32_t)(half * 32), o);
           }
           tmem_st_wait();
         }
@@ -304,7 +313,7 @@ __global__ void __launch_bounds__(kAttnThreads, 2) attention_fwd_kernel(const __
       for (int half = 0; half < 2; ++half) {
         uint32_t o[32];
         if (n_kb > 0) {
-          tmem_ld32_issue(lane_addr + 128u + (uint32_t)(half * 32), o);
+          tmem_ld32_issue(lane_addr + 64u + (uint32_t)(half * 32), o);
           tmem_ld_wait();
         } else {
 #pragma unroll
