@@ -47,7 +47,6 @@ struct AttnParams {
   void *out;
   int64_t o_row, o_head, o_batch;  // output strides in elements
   int *err;
-  uint32_t v_lbo;
 };
 
 // f16 / bf16 instruction descriptor, M = 128, N = 64, fp32 accumulate; bit 16 = B operand is MN-major
@@ -205,7 +204,7 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
         const uint32_t v_addr = smem_u32(v_s + vs * kKVBytes);
 #pragma unroll
         for (int kk = 0; kk < 4; ++kk)  // 16 keys per MMA: 32 bytes along P's rows, 16 rows of V
-          tc_mma<GEMM_F16>(tmem_base + 64u, dp + 2 * kk, make_mnmajor_sw128_desc(v_addr + kk * 2048, p.v_lbo), idesc_pv, (j | kk) != 0);
+          tc_mma<GEMM_F16>(tmem_base + 64u, dp + 2 * kk, make_mnmajor_sw128_desc(v_addr + kk * 2048, 1024), idesc_pv, (j | kk) != 0);
         tc_commit(&v_empty[vs]);
         tc_commit(pv_done);
       }
@@ -396,8 +395,6 @@ int run_attention(const void *q, const void *k, const void *v, void *out, int is
   p.o_row = o_str[2];
   p.err = gemm_error_word();
   if (!p.err) { set_error("attention: cannot resolve the device error word"); return PGB_ERR_CUDA; }
-  p.v_lbo = 1024;
-  if (const char *e = getenv("PGB_ATTN_VLBO")) p.v_lbo = (uint32_t)atoi(e);  // bring-up aid
   attention_fwd_kernel<<<(unsigned)(B * H * n_qblk), kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, p);
   count_launch();
   return check_launch("attention_fwd_kernel");

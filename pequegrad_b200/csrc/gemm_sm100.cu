@@ -153,11 +153,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   const int64_t batch = nb0 * nb1;
   if (M <= 0 || N <= 0 || batch <= 0) return PGB_OK;
   if (K <= 0) { set_error("matmul: empty contraction dim"); return PGB_ERR_INVALID_ARG; }
-  int bn = N > 128 ? 256 : (N > 32 ? 128 : 32);
-  if (const char *e = getenv("PGB_GEMM_BN")) {  // tuning aid
-    const int v = atoi(e);
-    if (v == 32 || v == 128 || v == 256) bn = v;
-  }
+  const int bn = N > 128 ? 256 : (N > 32 ? 128 : 32);
   const int64_t tiles_m = (M + kBM - 1) / kBM, tiles_n = (N + bn - 1) / bn;
   if (M > 2147483647LL || N > 2147483647LL || K > 2147483647LL || tiles_m * tiles_n * batch > 2147483647LL) {
     set_error("matmul: problem too large for one launch");
@@ -186,7 +182,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   CUtensorMap mo = ma;
   const bool absmax_only = !epi.out && !epi.acc_out && epi.absmax;
   const int oes = absmax_only ? 4 : (epi.out_dtype == PGB_F32 ? 4 : (epi.out_dtype == PGB_I8 ? 1 : 2));
-  bool fast = bn >= 128 && (epi.out || absmax_only) && !epi.acc_out && !getenv("PGB_GEMM_PLAIN_STORES");
+  bool fast = bn >= 128 && (epi.out || absmax_only) && !epi.acc_out;
   if (kind == GEMM_I8 && oes == 2) fast = false;
   if (oes == 1 && (kind != GEMM_I8 || bn != 256 || !epi.requant_absmax)) fast = false;
   if (fast && epi.residual) {

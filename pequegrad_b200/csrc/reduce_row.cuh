@@ -178,11 +178,7 @@ int launch_row_typed(ReduceJob &j, bool ident, const ChainProg<float> &chain) {
   const int64_t per_row = p.R1 * p.C;
   // threads per row: a warp for short rows, half a CTA for medium ones (two rows per CTA
   // halve the per-row combine cost), a whole CTA beyond
-  int G = (per_row <= 2048) ? 32 : (per_row <= 16384 ? 128 : 256);
-  if (const char *e = getenv("PGB_ROW_G")) {  // tuning aid
-    const int g = atoi(e);
-    if (g == 32 || g == 128 || g == 256) G = g;
-  }
+  const int G = (per_row <= 2048) ? 32 : (per_row <= 16384 ? 128 : 256);
   const int V = vec ? VFULL : 1;
   int64_t S = 1;
   p.chunk = p.C;

@@ -131,3 +131,42 @@ def test_compute_calls_fail_loudly_without_a_device():
     from pequegrad_b200 import kernels as K
     with pytest.raises(RuntimeError):
         K.fused_reduce([torch.zeros(4, 5)], L.SUM, [1])
+
+
+def test_tensor_core_entry_points_validate_their_arguments():
+    """Host-side validation of matmul / qlinear / attention / quantise: shapes, dtypes and layouts are checked before any device call."""
+    lib = L.lib()
+    f16 = lambda shape, strides=None, ptr=4096: _t(shape, strides, dtype=L.F16, es=2, ptr=ptr)  # noqa: E731
+    i8 = lambda shape: _t(shape, None, dtype=L.I8, es=1)  # noqa: E731
+
+    def err(st, code, text):
+        assert st == code, (st, lib.pgb_last_error())
+        assert text in lib.pgb_last_error(), lib.pgb_last_error()
+
+    # matmul: dtype the reference does not have either, mismatching contraction dims, unknown activation
+    a64, o64 = _t((8, 16), dtype=L.F64, es=8), _t((8, 8), dtype=L.F64, es=8)
+    err(lib.pgb_matmul(C.byref(a64), C.byref(_t((16, 8), dtype=L.F64, es=8)), None, 0, 1.0, None, C.byref(o64), None), L.ERR_UNSUPPORTED,
+        b"matmul_cuda not implemented for float64")
+    a, out = f16((8, 16)), f16((8, 24))
+    err(lib.pgb_matmul(C.byref(a), C.byref(f16((24, 8), (1, 24))), None, 0, 1.0, None, C.byref(out), None), L.ERR_INVALID_ARG, b"contraction dims differ")
+    err(lib.pgb_matmul(C.byref(a), C.byref(f16((16, 24), (1, 16))), None, 7, 1.0, None, C.byref(out), None), L.ERR_INVALID_ARG, b"unknown activation")
+    err(lib.pgb_matmul(C.byref(a), C.byref(f16((16, 24), (1, 16))), None, 0, 1.0, None, C.byref(f16((8, 20))), None), L.ERR_INVALID_ARG,
+        b"output shape does not match")
+    # qlinear: int8 operands, something to write, an absmax for an int8 output
+    err(lib.pgb_qlinear_i8(C.byref(a), C.byref(i8((24, 16))), None, 1.0, None, None, 0, C.byref(_t((8, 24))), None, None, None), L.ERR_UNSUPPORTED,
+        b"must be int8")
+    err(lib.pgb_qlinear_i8(C.byref(i8((8, 16))), C.byref(i8((24, 16))), None, 1.0, None, None, 0, None, None, None, None), L.ERR_INVALID_ARG,
+        b"nothing to write")
+    err(lib.pgb_qlinear_i8(C.byref(i8((8, 16))), C.byref(i8((24, 16))), None, 1.0, None, None, 0, C.byref(i8((8, 24))), None, None, None), L.ERR_INVALID_ARG,
+        b"device absmax")
+    err(lib.pgb_qlinear_i8(C.byref(i8((8, 16))), C.byref(i8((24, 32))), None, 1.0, None, None, 0, C.byref(_t((8, 24))), None, None, None), L.ERR_INVALID_ARG,
+        b"contraction dims differ")
+    # attention: head dim, dtype, agreement of the operands, scale
+    q = f16((2, 4, 32, 64))
+    err(lib.pgb_attention(C.byref(f16((2, 4, 32, 32))), C.byref(q), C.byref(q), 0.125, 1, C.byref(q), None), L.ERR_UNSUPPORTED, b"head dim of 64")
+    q32 = _t((2, 4, 32, 64))
+    err(lib.pgb_attention(C.byref(q32), C.byref(q32), C.byref(q32), 0.125, 1, C.byref(q32), None), L.ERR_UNSUPPORTED, b"attention not implemented for float32")
+    err(lib.pgb_attention(C.byref(q), C.byref(f16((2, 4, 16, 64))), C.byref(q), 0.125, 1, C.byref(q), None), L.ERR_INVALID_ARG, b"disagree")
+    # quantise: fp32 in, int8 out, one size
+    err(lib.pgb_quantize_i8(C.byref(_t((8, 16))), None, 0.5, C.byref(i8((8, 8))), None), L.ERR_INVALID_ARG, b"one size")
+    err(lib.pgb_quantize_i8(C.byref(_t((8, 16))), None, 0.0, C.byref(i8((8, 16))), None), L.ERR_INVALID_ARG, b"positive scale")
