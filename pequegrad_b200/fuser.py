@@ -186,6 +186,9 @@ def evaluate(node: T.Tensor, fuse: bool = False):
         (node._buf,) = K.fused_elementwise([], [("IMM", 0, 0, 0, node.attrs["value"])], shape=node.shape, out_dtypes=[node.dtype])
     elif node.op == "matmul":
         node._buf = _matmul(_emit_leaf(node.args[0], fuse), _emit_leaf(node.args[1], fuse))
+    elif node.op == "attention":
+        q, k, v = (_emit_leaf(a, fuse) for a in node.args)
+        node._buf = K.attention(q, k, v, scale=node.attrs["scale"], causal=node.attrs["causal"])
     elif node.op == "softmax_rows":
         node._buf = K.softmax_rows(_emit_leaf(node.args[0], fuse).contiguous(), node.attrs.get("causal", False))
     elif node.op == "layernorm_rows":

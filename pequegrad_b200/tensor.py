@@ -280,3 +280,22 @@ def tanh(x): return 2.0 / (1.0 + exp(-2.0 * x)) - 1.0  # pequegrad/ops.py:159-16
 def gelu(x: Tensor) -> Tensor:
     """tanh approximation, pequegrad/ops.py:109-118."""
     return 0.5 * x * (1.0 + tanh(math.sqrt(2 / math.pi) * (x + 0.044715 * (x ** 3.0))))
+
+
+def scaled_dot_product_attention(query: Tensor, key: Tensor, value: Tensor, mask: Tensor | None = None, is_causal: bool = False) -> Tensor:
+    """pequegrad/ops.py:792-818: softmax(q k^T / sqrt(d_k) [masked with -1e9]) v. Under `jit`, 16-bit operands with a head
+    dim of 64 and no mask tensor become ONE fused attention kernel (which also takes `is_causal`); the composite itself
+    refuses `is_causal` as the reference does ("use a mask")."""
+    from . import fuser
+    d_k = key.shape[-1]
+    if (fuser._fuse_composites and mask is None and d_k == 64 and query.shape[-1] == 64 and value.shape[-1] == 64
+            and query.dtype in (torch.float16, torch.bfloat16) and 2 <= query.ndim <= 4 and query.shape[:-2] == key.shape[:-2] == value.shape[:-2]):
+        return Tensor(op="attention", args=(query, key, value), attrs={"causal": bool(is_causal), "scale": 1.0 / math.sqrt(d_k)},
+                      shape=query.shape, dtype=query.dtype)
+    if is_causal:
+        raise NotImplementedError("Causal attention not implemented yet, use a mask")
+    scores = (query @ key.transpose(-2, -1)) / math.sqrt(d_k)
+    if mask is not None:
+        scores = where(mask, scores, broadcast_to(fill((), scores.dtype, -1e9), scores.shape))
+    return softmax(scores, dim=-1) @ value
+

@@ -127,3 +127,30 @@ def test_matmul_half_float_and_reference_error_for_float64():
     assert np.abs(got - want).max() <= 1e-5 * float((np.abs(a32) @ np.abs(w32)).max())
     with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float64"):
         (pg.Tensor(a.astype(np.float64)) @ pg.Tensor(w.astype(np.float64))).eval()
+
+
+def test_sdpa_composite_and_its_fused_form():
+    """pequegrad/ops.py:792-818 and tests/test_high_level_ops.py:623-639 (sdpa with a tril mask): eager = the composite
+    (matmul, where, softmax, matmul), under jit without a mask tensor = the one-kernel attention."""
+    rng = np.random.default_rng(8)
+    q, k, v = (rng.standard_normal((2, 3, 96, 64)).astype(np.float16) for _ in range(3))
+    tril = np.tril(np.ones((96, 96), dtype=bool))
+    s = (q.astype(np.float32) @ k.astype(np.float32).transpose(0, 1, 3, 2)) / 8.0
+
+    def ref(masked):
+        z = np.where(tril, s, -1e9) if masked else s
+        e = np.exp(z - z.max(-1, keepdims=True))
+        return (e / e.sum(-1, keepdims=True)) @ v.astype(np.float32)
+
+    mask = pg.Tensor(np.broadcast_to(tril, (2, 3, 96, 96)).astype(np.float16)) > 0.5
+    eager = pg.scaled_dot_product_attention(pg.Tensor(q), pg.Tensor(k), pg.Tensor(v), mask=mask).numpy().astype(np.float32)
+    assert_close(eager, ref(True), 2e-2, 2e-2)
+    before = L.lib().pgb_launch_count()
+    fused = fuser.jit(lambda a, b, c: pg.scaled_dot_product_attention(a, b, c, is_causal=True))(pg.Tensor(q), pg.Tensor(k), pg.Tensor(v))
+    got = fused.numpy().astype(np.float32)
+    assert L.lib().pgb_launch_count() - before == 1  # one kernel
+    assert_close(got, ref(True), 2e-2, 2e-2)
+    full = fuser.jit(lambda a, b, c: pg.scaled_dot_product_attention(a, b, c))(pg.Tensor(q), pg.Tensor(k), pg.Tensor(v)).numpy().astype(np.float32)
+    assert_close(full, ref(False), 2e-2, 2e-2)
+    with pytest.raises(NotImplementedError, match="use a mask"):
+        pg.scaled_dot_product_attention(pg.Tensor(q), pg.Tensor(k), pg.Tensor(v), is_causal=True)
