@@ -353,6 +353,7 @@ static int rows_launch(const RowsParams &p, cudaStream_t stream) {
   if (vec && per_lane_vecs <= 16) {
     if (per_lane_vecs <= 1) { PGB_ROWS_CASE(1); }
     else if (per_lane_vecs <= 2) { PGB_ROWS_CASE(2); }
+    else if (per_lane_vecs <= 3) { PGB_ROWS_CASE(3); }
     else if (per_lane_vecs <= 4) { PGB_ROWS_CASE(4); }
     else if (per_lane_vecs <= 6) { PGB_ROWS_CASE(6); }
     else if (per_lane_vecs <= 8) { PGB_ROWS_CASE(8); }
