@@ -263,7 +263,8 @@ PGB_API int pgb_embedding_rows(const pgb_tensor *ids, const pgb_tensor *wte, con
  * stream-ordered scratch buffer, and one tf32 tensor-core GEMM over [small|big|big] x
  * [big|small|big] sums three products per term in the fp32 accumulator: the error stays below
  * 1e-5 * sum_k |a_ik b_kj| (the classical fp32 dot-product bound for K = 170), ~1e-6 of it in practice.
- * fp64 / int32 operands return PGB_ERR_UNSUPPORTED ("matmul_cuda not implemented for ...").
+ * fp64 operands (cublasDgemm in the reference) run on the fp64 units, any strides, fp64 bias / residual / output.
+ * int32 operands return PGB_ERR_UNSUPPORTED ("matmul_cuda not implemented for int32"), as in the reference.
  */
 PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, float alpha,
                        const pgb_tensor *residual, const pgb_tensor *out, void *stream);

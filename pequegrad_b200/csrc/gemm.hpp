@@ -46,6 +46,10 @@ int run_pack_tf32x3(const float *in, float *out, int n_lead, const int64_t *lead
 // out[b, r, 0..Kp) = in[b, r, 0..K) (zero padded) for 2-byte elements: a K-major, 16-byte aligned copy of any view.
 int run_pack_copy16(const void *in, void *out, int n_lead, const int64_t *lead_size, const int64_t *lead_stride, int64_t rows, int64_t K, int64_t Kp,
                     int64_t row_stride, int64_t col_stride, cudaStream_t stream);
+// fp64 matmul on the fp64 units (any strides; strides = {a row, a col, b row, b col, c row, residual row} in elements).
+int run_matmul_f64(const double *a, const double *b, double *c, const double *bias, const double *res, int64_t M, int64_t N, int64_t K,
+                   const int64_t strides[6], int n_lead, const int64_t *lead, const int64_t *a_ls, const int64_t *b_ls, const int64_t *c_ls,
+                   const int64_t *r_ls, double alpha, int act, cudaStream_t stream);
 int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream);
 int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float scale, int8_t *q, cudaStream_t stream);
 int read_gemm_error(int *out, bool reset);

@@ -202,6 +202,46 @@ static int matmul_f32(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor
   return st;
 }
 
+// fp64 matmul: shape checks, then the fp64-unit kernel (matmul_f64.cu) reads every operand through its strides.
+static int matmul_f64(const pgb_tensor *a, const pgb_tensor *b, const pgb_tensor *bias, int act, float alpha, const pgb_tensor *residual,
+                      const pgb_tensor *out, cudaStream_t stream) {
+  if (a->ndim < 2 || b->ndim < 2 || out->ndim != a->ndim) { set_error("matmul: operands need at least 2 dims and the output the rank of a"); return PGB_ERR_INVALID_ARG; }
+  const int nla = a->ndim - 2;
+  if (nla > 6) { set_error("matmul: at most 6 batch dims"); return PGB_ERR_UNSUPPORTED; }
+  const int64_t M = a->shape[nla], K = a->shape[nla + 1], N = b->shape[b->ndim - 1];
+  if (b->shape[b->ndim - 2] != K) { set_error("matmul: contraction dims differ"); return PGB_ERR_INVALID_ARG; }
+  const bool shared_b = b->ndim == 2;
+  if (!shared_b && b->ndim != a->ndim) { set_error("matmul: batch dims differ"); return PGB_ERR_INVALID_ARG; }
+  if (out->dtype != PGB_F64 || (residual && residual->dtype != PGB_F64) || (bias && bias->dtype != PGB_F64)) {
+    set_error("matmul: a float64 matmul takes and gives float64 tensors");
+    return PGB_ERR_INVALID_ARG;
+  }
+  if (out->shape[nla] != M || out->shape[nla + 1] != N || (N > 1 && out->stride_bytes[nla + 1] != 8) ||
+      (residual && (residual->ndim != out->ndim || residual->shape[nla] != M || residual->shape[nla + 1] != N || (N > 1 && residual->stride_bytes[nla + 1] != 8)))) {
+    set_error("matmul: output shape does not match");
+    return PGB_ERR_INVALID_ARG;
+  }
+  if (bias && (numel_of(*bias) != N || !is_contiguous(*bias))) { set_error("matmul: the bias must be a contiguous vector of the output width"); return PGB_ERR_INVALID_ARG; }
+  int64_t lead[6], als[6], bls[6], cls[6], rls[6];
+  for (int d = 0; d < nla; ++d) {
+    if (out->shape[d] != a->shape[d] || (!shared_b && b->shape[d] != a->shape[d]) || (residual && residual->shape[d] != a->shape[d])) {
+      set_error("matmul: batch dims differ");
+      return PGB_ERR_INVALID_ARG;
+    }
+    lead[d] = a->shape[d];
+    als[d] = a->stride_bytes[d] / 8;
+    bls[d] = shared_b ? 0 : b->stride_bytes[d] / 8;
+    cls[d] = out->stride_bytes[d] / 8;
+    rls[d] = residual ? residual->stride_bytes[d] / 8 : 0;
+  }
+  if (K == 0 && M > 0 && N > 0) { set_error("matmul: empty contraction dim"); return PGB_ERR_INVALID_ARG; }
+  if (!device_present()) return PGB_ERR_CUDA;
+  const int64_t strides[6] = {a->stride_bytes[nla] / 8, a->stride_bytes[nla + 1] / 8, b->stride_bytes[b->ndim - 2] / 8, b->stride_bytes[b->ndim - 1] / 8,
+                              out->stride_bytes[nla] / 8, residual ? residual->stride_bytes[nla] / 8 : 0};
+  return run_matmul_f64((const double *)a->data, (const double *)b->data, (double *)out->data, bias ? (const double *)bias->data : nullptr,
+                        residual ? (const double *)residual->data : nullptr, M, N, K, strides, nla, lead, als, bls, cls, rls, (double)alpha, act, stream);
+}
+
 }  // namespace pgb
 
 using namespace pgb;
@@ -347,6 +387,7 @@ PGB_API int pgb_matmul(const pgb_tensor *a, const pgb_tensor *b, const pgb_tenso
   if (a->dtype != b->dtype) { set_error("matmul: operand dtypes differ"); return PGB_ERR_INVALID_ARG; }
   if (act < 0 || act > 2) { set_error("matmul: unknown activation"); return PGB_ERR_INVALID_ARG; }
   if (a->dtype == PGB_F32) return matmul_f32(a, b, bias, act, alpha, residual, out, (cudaStream_t)stream);
+  if (a->dtype == PGB_F64) return matmul_f64(a, b, bias, act, alpha, residual, out, (cudaStream_t)stream);
   if (a->dtype != PGB_F16 && a->dtype != PGB_BF16) {
     // reference wording, csrc/cuda/matmul.cu:157-160
     set_error(std::string("matmul_cuda not implemented for ") + dtype_name(a->dtype));

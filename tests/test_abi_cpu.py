@@ -144,9 +144,12 @@ def test_tensor_core_entry_points_validate_their_arguments():
         assert text in lib.pgb_last_error(), lib.pgb_last_error()
 
     # matmul: dtype the reference does not have either, mismatching contraction dims, unknown activation
-    a64, o64 = _t((8, 16), dtype=L.F64, es=8), _t((8, 8), dtype=L.F64, es=8)
-    err(lib.pgb_matmul(C.byref(a64), C.byref(_t((16, 8), dtype=L.F64, es=8)), None, 0, 1.0, None, C.byref(o64), None), L.ERR_UNSUPPORTED,
-        b"matmul_cuda not implemented for float64")
+    a32i, o32i = _t((8, 16), dtype=L.I32), _t((8, 8), dtype=L.I32)
+    err(lib.pgb_matmul(C.byref(a32i), C.byref(_t((16, 8), dtype=L.I32)), None, 0, 1.0, None, C.byref(o32i), None), L.ERR_UNSUPPORTED,
+        b"matmul_cuda not implemented for int32")
+    a64 = _t((8, 16), dtype=L.F64, es=8)
+    err(lib.pgb_matmul(C.byref(a64), C.byref(_t((12, 8), dtype=L.F64, es=8)), None, 0, 1.0, None, C.byref(_t((8, 8), dtype=L.F64, es=8)), None),
+        L.ERR_INVALID_ARG, b"contraction dims differ")
     a, out = f16((8, 16)), f16((8, 24))
     err(lib.pgb_matmul(C.byref(a), C.byref(f16((24, 8), (1, 24))), None, 0, 1.0, None, C.byref(out), None), L.ERR_INVALID_ARG, b"contraction dims differ")
     err(lib.pgb_matmul(C.byref(a), C.byref(f16((16, 24), (1, 16))), None, 7, 1.0, None, C.byref(out), None), L.ERR_INVALID_ARG, b"unknown activation")

@@ -165,8 +165,8 @@ def test_linear_epilogues_and_batched_attention_shapes():
 
 
 def test_matmul_errors_follow_the_reference():
-    a = torch.zeros((8, 16), device="cuda", dtype=torch.float64)
-    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float64"):
+    a = torch.zeros((8, 16), device="cuda", dtype=torch.int32)
+    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for int32"):
         K.matmul(a, a.T)
     h = torch.zeros((16, 16), device="cuda", dtype=torch.float16)
     with pytest.raises(ValueError):
@@ -265,3 +265,21 @@ def test_half_matmul_accepts_any_view(dt):
         tol = 2e-2 * max(1.0, want.abs().max().item())
         assert got.shape == want.shape and (got - want).abs().max().item() <= tol, (tuple(a.shape), tuple(b.shape))
     assert K.device_error() == 0
+
+
+@pytest.mark.parametrize("shape_a,shape_b", [((3, 4), (4, 5)), ((5, 7), (7, 3)), ((2, 3, 4), (2, 4, 5)), ((130, 70), (70, 257)),
+                                             ((2, 3, 65, 33), (2, 3, 33, 70)), ((4, 50, 16), (16, 9))])
+def test_fp64_matmul(shape_a, shape_b):
+    """tests/test_ops.py:257-274 runs matmul in float64 too: the fp64-unit kernel, compared at the reference tests' 1e-5 (it is
+    accurate to rounding) on plain, transposed-view and batched operands, with a bias + ReLU + residual epilogue."""
+    rng = np.random.default_rng(45)
+    a = rng.uniform(0.5, 0.9, shape_a)
+    b = rng.uniform(0.5, 0.9, shape_b)
+    got = K.matmul(cu(a), cu(b)).cpu().numpy()
+    np.testing.assert_allclose(got, np.matmul(a, b), rtol=1e-12, atol=1e-12)
+    a2 = rng.standard_normal(shape_a[:-2] + (shape_a[-1], shape_a[-2]))
+    bias = rng.standard_normal(shape_b[-1])
+    res = rng.standard_normal(np.matmul(a, b).shape)
+    got2 = K.matmul(cu(a2).transpose(-2, -1), cu(b), bias=cu(bias), act=1, residual=cu(res), alpha=0.5).cpu().numpy()
+    want2 = np.maximum(np.matmul(np.swapaxes(a2, -2, -1), b) * 0.5 + bias, 0) + res
+    np.testing.assert_allclose(got2, want2, rtol=1e-11, atol=1e-11)

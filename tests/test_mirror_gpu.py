@@ -109,7 +109,7 @@ def test_composites_eager_and_jit():
     assert_close(fuser.jit(pg.gelu)(pg.Tensor(x)).numpy(), want, 1e-5)
 
 
-def test_matmul_half_float_and_reference_error_for_float64():
+def test_matmul_half_float_double_and_reference_error_for_int32():
     rng = np.random.default_rng(3)
     a = rng.standard_normal((5, 64, 128)).astype(np.float16)
     w = rng.standard_normal((128, 96)).astype(np.float16)
@@ -125,8 +125,10 @@ def test_matmul_half_float_and_reference_error_for_float64():
     got = (pg.Tensor(a32) @ pg.Tensor(w32)).numpy()
     want = a32.astype(np.float64) @ w32.astype(np.float64)
     assert np.abs(got - want).max() <= 1e-5 * float((np.abs(a32) @ np.abs(w32)).max())
-    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for float64"):
-        (pg.Tensor(a.astype(np.float64)) @ pg.Tensor(w.astype(np.float64))).eval()
+    a64, w64 = a.astype(np.float64), w.astype(np.float64)
+    np.testing.assert_allclose((pg.Tensor(a64) @ pg.Tensor(w64)).numpy(), a64 @ w64, rtol=1e-12, atol=1e-12)
+    with pytest.raises(RuntimeError, match="matmul_cuda not implemented for int32"):
+        (pg.Tensor(a.astype(np.int32)) @ pg.Tensor(w.astype(np.int32))).eval()
 
 
 def test_sdpa_composite_and_its_fused_form():
