@@ -13,12 +13,12 @@ __global__ void __launch_bounds__(256) absmax_f32_kernel(const float *__restrict
   const int64_t nvec = n >> 2, stride = (int64_t)gridDim.x * 256;
   const float4 *x4 = reinterpret_cast<const float4 *>(x);
   int64_t i = (int64_t)blockIdx.x * 256 + threadIdx.x;
-  for (; i + 3 * stride < nvec; i += 4 * stride) {  // four independent 128-bit loads in flight per thread
-    float4 v[4];
+  for (; i + 7 * stride < nvec; i += 8 * stride) {  // eight independent 128-bit loads in flight per thread
+    float4 v[8];
 #pragma unroll
-    for (int u = 0; u < 4; ++u) v[u] = __ldcs(x4 + i + u * stride);
+    for (int u = 0; u < 8; ++u) v[u] = __ldcs(x4 + i + u * stride);
 #pragma unroll
-    for (int u = 0; u < 4; ++u) m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
+    for (int u = 0; u < 8; ++u) m = fmaxf(m, fmaxf(fmaxf(fabsf(v[u].x), fabsf(v[u].y)), fmaxf(fabsf(v[u].z), fabsf(v[u].w))));
   }
   for (; i < nvec; i += stride) {
     const float4 v = __ldcs(x4 + i);
@@ -67,8 +67,8 @@ __global__ void __launch_bounds__(256) quantize_i8_kernel(const float *__restric
 int run_absmax_f32(const float *x, int64_t n, float *out, cudaStream_t stream) {
   if (cudaMemsetAsync(out, 0, sizeof(float), stream) != cudaSuccess) { set_error("absmax: memset failed"); return PGB_ERR_CUDA; }
   if (n <= 0) return PGB_OK;
-  int64_t grid = (n + 4095) / 4096;  // 4 vectors of 4 elements per thread
-  const int64_t cap = (int64_t)sm_count() * 32;
+  int64_t grid = (n + 8191) / 8192;  // 8 vectors of 4 elements per thread
+  const int64_t cap = (int64_t)sm_count() * 16;
   if (grid > cap) grid = cap;
   if (grid < 1) grid = 1;
   absmax_f32_kernel<<<(unsigned)grid, 256, 0, stream>>>(x, n, out);
