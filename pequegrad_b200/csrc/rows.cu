@@ -301,6 +301,82 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const __grid_consta
   }
 }
 
+// LayerNorm for 16-bit rows of up to 16 * 256 columns, same idea as softmax_warp16_kernel: the row stays packed
+// (4 registers per 8 elements) and is widened on the fly in each of the three passes, which leaves room for six CTAs
+// per SM; squared deviations and the affine output use fused multiply-adds (fp32 statistics, 16-bit tolerance).
+template <typename IoT, int NV>
+__global__ void __launch_bounds__(256, (NV <= 4 ? 6 : (NV <= 8 ? 4 : 2))) layernorm_warp16_kernel(const __grid_constant__ RowsParams p) {
+  constexpr bool IS_H = std::is_same<IoT, __half>::value;
+  using T2 = typename std::conditional<IS_H, __half2, __nv_bfloat162>::type;
+  auto widen = [](uint32_t w) -> float2 {
+    if constexpr (IS_H) return __half22float2(*reinterpret_cast<const T2 *>(&w));
+    else return __bfloat1622float2(*reinterpret_cast<const T2 *>(&w));
+  };
+  const int lane = threadIdx.x & 31;
+  const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
+  if (row >= p.rows) return;
+  const int C = (int)p.C;
+  const IoT *xr = (const IoT *)p.x + row * C;
+  IoT *yr = (IoT *)p.y + row * C;
+  uint32_t w[NV][4];
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int c = (u * 32 + lane) * 8;
+    uint4 r = make_uint4(0, 0, 0, 0);
+    if (c < C) r = __ldcs(reinterpret_cast<const uint4 *>(xr + c));
+    w[u][0] = r.x; w[u][1] = r.y; w[u][2] = r.z; w[u][3] = r.w;
+  }
+  float s = 0.f;
+#pragma unroll
+  for (int u = 0; u < NV; ++u)
+#pragma unroll
+    for (int j = 0; j < 4; ++j) {
+      const float2 f = widen(w[u][j]);  // columns beyond C are zeros
+      s += f.x + f.y;
+    }
+  const float n = (float)C;
+  const float mean = warp_sum(s) / n;
+  float q = 0.f;
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    if ((u * 32 + lane) * 8 < C) {
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = widen(w[u][j]);
+        const float d0 = f.x - mean, d1 = f.y - mean;
+        q = fmaf(d0, d0, q);
+        q = fmaf(d1, d1, q);
+      }
+    }
+  }
+  const float var = warp_sum(q) / n;
+  const float rsd = 1.0f / sqrtf(var + p.eps);
+  const float nmr = -mean * rsd;  // (x - mean) * rsd = x * rsd + nmr
+#pragma unroll
+  for (int u = 0; u < NV; ++u) {
+    const int c = (u * 32 + lane) * 8;
+    if (c < C) {
+      uint4 g4 = make_uint4(0, 0, 0, 0), b4 = g4;
+      if (p.gamma) g4 = __ldg(reinterpret_cast<const uint4 *>((const IoT *)p.gamma + c));
+      if (p.beta) b4 = __ldg(reinterpret_cast<const uint4 *>((const IoT *)p.beta + c));
+      const uint32_t gw[4] = {g4.x, g4.y, g4.z, g4.w}, bw[4] = {b4.x, b4.y, b4.z, b4.w};
+      uint32_t o[4];
+#pragma unroll
+      for (int j = 0; j < 4; ++j) {
+        const float2 f = widen(w[u][j]);
+        float y0 = fmaf(f.x, rsd, nmr), y1 = fmaf(f.y, rsd, nmr);
+        if (p.gamma) { const float2 g = widen(gw[j]); y0 *= g.x; y1 *= g.y; }
+        if (p.beta) { const float2 b = widen(bw[j]); y0 += b.x; y1 += b.y; }
+        T2 pk;
+        if constexpr (IS_H) pk = __floats2half2_rn(y0, y1);
+        else pk = __floats2bfloat162_rn(y0, y1);
+        o[j] = *reinterpret_cast<const uint32_t *>(&pk);
+      }
+      *reinterpret_cast<uint4 *>(yr + c) = make_uint4(o[0], o[1], o[2], o[3]);
+    }
+  }
+}
+
 template <typename IoT>
 __global__ void __launch_bounds__(256) layernorm_cta_kernel(const __grid_constant__ RowsParams p) {
   __shared__ float red[8];
@@ -349,6 +425,7 @@ static int rows_launch(const RowsParams &p, cudaStream_t stream) {
 #define PGB_ROWS_CASE(NV)                                                                   \
   if constexpr (SOFTMAX && sizeof(IoT) == 2) softmax_warp16_kernel<IoT, NV><<<wgrid, 256, 0, stream>>>(p); \
   else if constexpr (SOFTMAX) softmax_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p); \
+  else if constexpr (sizeof(IoT) == 2) layernorm_warp16_kernel<IoT, NV><<<wgrid, 256, 0, stream>>>(p); \
   else layernorm_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p)
   if (vec && per_lane_vecs <= 16) {
     if (per_lane_vecs <= 1) { PGB_ROWS_CASE(1); }
