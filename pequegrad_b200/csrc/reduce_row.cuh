@@ -66,10 +66,12 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
       uint32_t r1 = seg, cc = 0;
       if (nchunks > 1) { r1 = seg / nchunks; cc = seg - r1 * nchunks; }
       const uint32_t c_lo = cc * chunk;
-      const uint32_t c_hi = min(C, c_lo + chunk);
+      const uint32_t c_end = min(C, c_lo + chunk);
       const InT *rowp[NIN];
 #pragma unroll
       for (int k = 0; k < NIN; ++k) rowp[k] = base[k] + (int64_t)r1 * p.r1str[k];
+      // rows whose length is no multiple of the vector width: whole vectors here, the last few elements below
+      const uint32_t c_hi = (V > 1) ? c_end - (c_end % V) : c_end;  // c_lo is a multiple of V
       for (uint32_t c0 = c_lo + t * V; c0 < c_hi; c0 += G * V * U) {
         T w[NIN][B];
 #pragma unroll
@@ -114,6 +116,22 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
           }
         }
       }
+      if (V > 1 && c_hi + t < c_end) {  // the ragged end: one element per thread, through the same prologue
+        const uint32_t c = c_hi + t;
+        T w[NIN][B];
+#pragma unroll
+        for (int k = 0; k < NIN; ++k) {
+          const T b = to_compute<T, InT>(__ldg(rowp[k] + (p.cstr[k] != 0 ? c : 0u)));
+#pragma unroll
+          for (int e = 0; e < B; ++e) w[k][e] = b;
+        }
+        T run[B];
+        if (MODE == 0) run[0] = w[0][0];
+        else if (MODE == 3) run[0] = w[0][0] * aff_a + aff_b;
+        else if (MODE == 1) chain_eval_fast<T, NIN, B>(cr, w, run);
+        else chain_eval<T, NIN, B>(p.pro, w, run);
+        acc[0].add(run[0], (int)c);
+      }
     }
   }
 #pragma unroll
@@ -154,7 +172,7 @@ int launch_row_typed(ReduceJob &j, bool ident, const ChainProg<float> &chain) {
   p.C = c.rsize[ri];
   p.R1 = (c.nr == 2) ? c.rsize[0] : 1;
   p.n_out = c.n_out;
-  bool vec = (p.C % VFULL) == 0;
+  bool vec = p.C >= VFULL;  // a ragged end is read element by element
   for (int k = 0; k < NIN; ++k) {
     p.in[k] = j.in[k].data;
     p.cstr[k] = c.rin[k][ri];

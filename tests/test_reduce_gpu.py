@@ -257,3 +257,49 @@ def test_reduction_sweep_shapes_full_size():
             assert_close(got, want, 1e-5, 1e-5 * float(np.abs(want).max()), f"{name} slab ax{ax}")
             want = fused_reduce_oracle([slab.cpu().numpy()], "argmax", [ax], False, AFFINE)
             assert np.array_equal(am.narrow(0, 5, 3).narrow(1, 17, 40).cpu().numpy(), want)
+
+
+def check_ragged(inputs, op, pro, rtol, what):
+    got = K.fused_reduce([dev(i) for i in inputs], OPS[op], [1], False, pro).cpu().numpy()
+    # the kernels compute 16-bit inputs in fp32; the CPU chain has no 16-bit kernels, so it gets the upcast values
+    half = inputs[0].dtype == np.float16
+    wide = [i.astype(np.float32) for i in inputs]
+    if op == "argmax" or (op == "max" and not half):
+        assert np.array_equal(got, fused_reduce_oracle(wide, op, [1], False, pro)), what
+    elif op == "max":  # the fp32 maximum, rounded once to the 16-bit output
+        assert_close(got.astype(np.float32), fused_reduce_oracle(wide, op, [1], False, pro), rtol, rtol, what)
+    else:  # long fp32 serial sums drift: the bound is checked against the fp64-accumulating twin
+        want = fused_reduce_truth(wide, op, [1], False, pro)
+        assert_close(got.astype(np.float64), want, rtol, rtol * max(1.0, float(np.abs(want).max())), what)
+
+
+@pytest.mark.parametrize("dtype", [np.float32, np.float16])
+@pytest.mark.parametrize("cols,pitch", [(50257, 50264), (1003, 1008), (37, 40), (20483, 20488)])
+def test_ragged_rows_in_an_aligned_pitch(cols, pitch, dtype):
+    """Row length not a multiple of the vector width inside a 16-byte-aligned row pitch (the GPT-2 logits
+    layout): whole vectors plus an element-wise end. What lies in the padding must not be read as data."""
+    rng = np.random.default_rng(21)
+    rows = 48 if cols > 30000 else 131
+    base = rng.standard_normal((rows, pitch)).astype(dtype)
+    base[:, cols:] = 1e4  # larger than any element: a kernel that reads the padding fails max, argmax and sum
+    x = base[:, :cols]
+    rtol = 1e-5 if dtype == np.float32 else 2e-2
+    for op in ("sum", "max", "argmax", "mean"):
+        check_ragged([x], op, (), rtol, f"ragged {cols}/{pitch} {op}")
+    check_ragged([x], "sum", AFFINE, rtol, f"ragged {cols}/{pitch} affine")
+    check_ragged([x], "max", AFFINE, rtol, f"ragged {cols}/{pitch} affine max")
+    check_ragged([x], "sum", EXP_PRO, rtol, f"ragged {cols}/{pitch} exp")
+    y = rng.standard_normal((rows, cols)).astype(dtype)  # second operand: contiguous, so its rows are unaligned
+    two = [("LOAD", 0), ("LOAD", 1), ("MUL", 0, 1)]
+    check_ragged([x, y], "sum", two, rtol, f"ragged {cols}/{pitch} two inputs")
+    y2 = rng.standard_normal((rows, pitch)).astype(dtype)[:, :cols]  # both operands on the vector path
+    check_ragged([x, y2], "sum", two, rtol, f"ragged {cols}/{pitch} two aligned inputs")
+    check_ragged([x, y2], "argmax", two, rtol, f"ragged {cols}/{pitch} two aligned inputs argmax")
+
+
+def test_ragged_row_split_across_ctas():
+    rng = np.random.default_rng(22)
+    z = rng.standard_normal((3, 1000004)).astype(np.float32)
+    z[:, 1000001:] = 1e4
+    for op in ("argmax", "sum", "max"):
+        check_ragged([z[:, :1000001]], op, (), 1e-5, f"ragged split {op}")
