@@ -14,6 +14,7 @@
 #include <cuda_fp16.h>
 
 #include "gemm_kernel.cuh"
+#include "gemm_pair_ptx.cuh"
 
 namespace pgb {
 
@@ -59,10 +60,19 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
   const int sw = (lane >> 1) & 3;
   bool dead = false;  // a wait ran out: keep taking part in the group barriers, do nothing else
   uint32_t res_phase = 0;  // parity of this warp's residual barrier
+  // CTAs per tile: one, or a pair that shares a 256-row tile (this CTA computes rows m_off .. m_off + 127 of it, and
+  // hands its accumulator back on the barrier of the pair's leader, which issues the MMAs of both)
+  const int psh = p.pair - 1;
+  const int m_off = (int)(blockIdx.x & psh) * kBM;
+  const uint32_t leader_empty = psh ? map_to_cta(smem_u32(acc_empty), 0) : 0u;
+  auto release_acc = [&](int buf) {
+    if (psh) mbar_arrive_cluster(leader_empty + 8u * (uint32_t)buf);
+    else mbar_arrive(&acc_empty[buf]);
+  };
   int it = 0;
-  for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
+  for (int tile = blockIdx.x >> psh; tile < num_tiles; tile += gridDim.x >> psh, ++it) {
     const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
-    const int m0 = (rem / p.tiles_n) * kBM, n0 = (rem % p.tiles_n) * BN;
+    const int m0 = (rem / p.tiles_n) * (kBM << psh) + m_off, n0 = (rem % p.tiles_n) * BN;
     const int zb = bz % p.nb1, wb = bz / p.nb1;
     const int buf = it & 1;
     // Column operands of this tile, fetched while the MMAs are still running. The four warps of the group each
@@ -122,7 +132,7 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
         // every TMEM load of this tile has landed in registers: hand the buffer back to the MMA warp
         tc_fence_before();
         __syncwarp();
-        if (lane == 0) mbar_arrive(&acc_empty[buf]);
+        if (lane == 0) release_acc(buf);
         released = true;
       }
       float x[32];
@@ -237,7 +247,7 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
     if (!released) {  // none of this warp's columns exist in this tile
       tc_fence_before();
       __syncwarp();
-      if (lane == 0) mbar_arrive(&acc_empty[buf]);
+      if (lane == 0) release_acc(buf);
     }
   }
   // shared memory must outlive the reads of the last stores

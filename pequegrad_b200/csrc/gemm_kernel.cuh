@@ -47,6 +47,7 @@ struct GemmParams {
   int nb1;                      // extent of the inner batch dim
   int out_tma;  // 0: plain stores; 2 / 4: the output goes through TMA tile stores, value = its element size
   int res_vec;  // the residual rows can be read with 16-byte loads
+  int pair;     // CTAs per tile: 1, or 2 for the CTA-pair kernel (256-row tiles, tiles_m counts those)
   int *err;     // device error word: 0 = ok; else (role << 16) | block index bits
   GemmEpilogue epi;
 };
@@ -59,7 +60,7 @@ __device__ __forceinline__ void report_error(const GemmParams &p, volatile int *
 // Instruction descriptor: c format [4,6) (1 = f32, 2 = s32), a format [7,10), b format [10,13)
 // (f16 kinds: 0 f16, 1 bf16; tf32 kind: 2; i8: 1 = signed), a/b major [15],[16] (0 = K-major),
 // N >> 3 at [17,23), M >> 4 at [24,29).
-template <int KIND, int BN>
+template <int KIND, int BN, int BM = kBM>
 __device__ __forceinline__ uint32_t make_idesc() {
   uint32_t d = 0;
   const uint32_t cfmt = (KIND == GEMM_I8) ? 2u : 1u;
@@ -68,7 +69,7 @@ __device__ __forceinline__ uint32_t make_idesc() {
   d |= abfmt << 7;
   d |= abfmt << 10;
   d |= (uint32_t)(BN >> 3) << 17;
-  d |= (uint32_t)(kBM >> 4) << 24;
+  d |= (uint32_t)(BM >> 4) << 24;
   return d;
 }
 

@@ -147,6 +147,20 @@ extern template int launch_gemm_bn<GEMM_F16>(int, const CUtensorMap &, const CUt
 extern template int launch_gemm_bn<GEMM_BF16>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
 extern template int launch_gemm_bn<GEMM_TF32>(int, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, int, cudaStream_t);
 
+template <int KIND>
+int launch_gemm_pair(const CUtensorMap &ma, const CUtensorMap &mb, const CUtensorMap &mo, const CUtensorMap &mr, const GemmParams &p, cudaStream_t stream);
+extern template int launch_gemm_pair<GEMM_I8>(const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, cudaStream_t);
+extern template int launch_gemm_pair<GEMM_F16>(const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, cudaStream_t);
+extern template int launch_gemm_pair<GEMM_BF16>(const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, cudaStream_t);
+extern template int launch_gemm_pair<GEMM_TF32>(const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, cudaStream_t);
+
+// PGB_GEMM_PAIR=0 keeps every GEMM on the one-CTA kernel (a switch for A/B timing and for the tests that compare
+// the two kernels; read at every call).
+static bool pair_enabled() {
+  const char *v = getenv("PGB_GEMM_PAIR");
+  return !(v && v[0] == '0');
+}
+
 // a: [nb0, nb1, M, K], b: [nb0, nb1, N, K], both K contiguous; strides in elements.
 int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_bs1, const void *b, int64_t ldb, int64_t b_bs0, int64_t b_bs1,
                 int64_t M, int64_t N, int64_t K, int64_t nb0, int64_t nb1, const GemmEpilogue &epi, cudaStream_t stream) {
@@ -200,6 +214,26 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   }
   p.out_tma = fast ? oes : 0;
   p.res_vec = fast && epi.residual;
+  p.pair = 1;
+  // Large aligned 16-bit / tf32 problems: CTA pairs on 256 x 256 tiles (each CTA loads half of the tile's B columns,
+  // the ring is six stages deep). Measured against the one-CTA kernel on 32768-row problems: 10-17 % faster for
+  // contractions of 768 with wide outputs (qkv, lm_head), level (+-3 %) for long contractions and heavy epilogues,
+  // 40 % slower when a tile is a single K slab (attention scores, K = 64), and 6-9 % slower for the int8 layers,
+  // whose short tiles are bound by the epilogue's arithmetic and suffer from the coupling of two CTAs' epilogues.
+  if (fast && bn == 256 && M % (2 * kBM) == 0 && kind != GEMM_I8 && p.num_kb >= 4 && pair_enabled()) {
+    CUtensorMap mb_half;
+    if (make_operand_map(&mb_half, b, kind, N, K, ldb, nb0, nb1, b_bs0, b_bs1, bn / 2, "B") == PGB_OK) {
+      GemmParams pp = p;
+      pp.pair = 2;
+      pp.tiles_m = (int)(M / (2 * kBM));
+      int r;
+      if (kind == GEMM_I8) r = launch_gemm_pair<GEMM_I8>(ma, mb_half, mo, mr, pp, stream);
+      else if (kind == GEMM_F16) r = launch_gemm_pair<GEMM_F16>(ma, mb_half, mo, mr, pp, stream);
+      else if (kind == GEMM_TF32) r = launch_gemm_pair<GEMM_TF32>(ma, mb_half, mo, mr, pp, stream);
+      else r = launch_gemm_pair<GEMM_BF16>(ma, mb_half, mo, mr, pp, stream);
+      if (r != PGB_ERR_UNSUPPORTED) return r;  // else: pairs cannot be scheduled on this device
+    }
+  }
   const int64_t num_tiles = tiles_m * tiles_n * batch;
   const int grid = (int)std::min<int64_t>(num_tiles, sm_count());
   if (kind == GEMM_I8) return launch_gemm_bn<GEMM_I8>(bn, ma, mb, mo, mr, p, grid, stream);

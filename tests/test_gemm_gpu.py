@@ -283,3 +283,89 @@ def test_fp64_matmul(shape_a, shape_b):
     got2 = K.matmul(cu(a2).transpose(-2, -1), cu(b), bias=cu(bias), act=1, residual=cu(res), alpha=0.5).cpu().numpy()
     want2 = np.maximum(np.matmul(np.swapaxes(a2, -2, -1), b) * 0.5 + bias, 0) + res
     np.testing.assert_allclose(got2, want2, rtol=1e-11, atol=1e-11)
+
+
+class one_cta_kernel:
+    """Keeps the GEMMs inside the block on the one-CTA kernel (the library reads the switch at every call)."""
+
+    def __enter__(self):
+        import os
+        self.old = os.environ.get("PGB_GEMM_PAIR")
+        os.environ["PGB_GEMM_PAIR"] = "0"
+
+    def __exit__(self, *exc):
+        import os
+        if self.old is None:
+            del os.environ["PGB_GEMM_PAIR"]
+        else:
+            os.environ["PGB_GEMM_PAIR"] = self.old
+
+
+def both_kernels(fn):
+    """fn() through the CTA-pair kernel and through the one-CTA kernel: same MMAs in the same order, same epilogue,
+    so the results must be the same bits."""
+    got = fn()
+    assert K.device_error() == 0
+    with one_cta_kernel():
+        want = fn()
+    assert K.device_error() == 0
+    got = got if isinstance(got, (tuple, list)) else (got,)
+    want = want if isinstance(want, (tuple, list)) else (want,)
+    for g_, w_ in zip(got, want):
+        assert torch.equal(g_, w_)
+    return got
+
+
+@pytest.mark.parametrize("M,N,K_", [(256, 256, 128), (512, 2576, 1040), (4096, 1024, 784), (256 * 75, 768, 256)])
+def test_int8_layers_same_bits_with_and_without_the_pair_switch(M, N, K_):
+    g = torch.Generator(device="cuda").manual_seed(31)
+    a = torch.randint(-127, 128, (M, K_), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (N, K_), generator=g, device="cuda", dtype=torch.int8)
+    ws = torch.rand(N, generator=g, device="cuda") * 0.01 + 0.001
+    b = torch.randn(N, generator=g, device="cuda")
+    out, = both_kernels(lambda: K.qlinear_i8(a, w, ws, a_scale=0.02, bias=b, relu=True)[0])
+    acc = a[:300].cpu().numpy().astype(np.int32) @ w.cpu().numpy().astype(np.int32).T  # int32 accumulators on the CPU
+    want = np.maximum(acc.astype(np.float32) * (np.float32(0.02) * ws.cpu().numpy())[None, :] + b.cpu().numpy()[None, :], 0)
+    assert np.array_equal(out[:300].cpu().numpy(), want)
+    # absmax-only pass, then the int8-requantising pass
+    def two_pass():
+        am = torch.zeros(1, device="cuda")
+        K.qlinear_i8(a, w, ws, a_scale=0.02, bias=b, relu=True, want_out=False, out_absmax=am)
+        q = torch.empty((M, N), dtype=torch.int8, device="cuda")
+        K.qlinear_i8(a, w, ws, a_scale=0.02, bias=b, relu=True, out=q, out_absmax=am)
+        return am, q
+    am, q = both_kernels(two_pass)
+    assert float(am) == float(out.max())
+
+
+@pytest.mark.parametrize("dt", [torch.float16, torch.bfloat16])
+def test_cta_pair_kernel_16bit_matches_the_one_cta_kernel(dt):
+    g = torch.Generator(device="cuda").manual_seed(32)
+    x = (torch.randn((2, 1024, 768), generator=g, device="cuda") * 0.5).to(dt)
+    wt = (torch.randn((3072, 768), generator=g, device="cuda") * 0.02).to(dt)
+    b = (torch.randn(3072, generator=g, device="cuda") * 0.02).to(dt)
+    y, = both_kernels(lambda: K.matmul(x, wt.T, bias=b, act=2))
+    z = x.float() @ wt.float().T + b.float()
+    ref = 0.5 * z * (1 + torch.tanh(0.7978845608028654 * (z + 0.044715 * z ** 3)))
+    assert_close(y.float().cpu().numpy(), ref.cpu().numpy(), 2e-2, 2e-3)
+    wt2 = (torch.randn((768, 3072), generator=g, device="cuda") * 0.02).to(dt)
+    res = torch.randn((2, 1024, 768), generator=g, device="cuda").to(dt)
+    both_kernels(lambda: K.matmul(y, wt2.T, residual=res))
+    both_kernels(lambda: K.matmul(x, wt.T, out_dtype=torch.float32))
+    # ragged right edge: the peer CTA's half of the last tile lies wholly beyond N
+    wv = (torch.randn((2568, 768), generator=g, device="cuda") * 0.02).to(dt)
+    lg, = both_kernels(lambda: K.matmul(x, wv.T))
+    assert_close(lg.float().cpu().numpy(), (x.float() @ wv.float().T).cpu().numpy(), 2e-2, 2e-3)
+    # batched operands (scores of 2 x 12 heads read in place from packed buffers)
+    q = torch.randn((2, 12, 512, 64), generator=g, device="cuda").to(dt)
+    k = torch.randn((2, 12, 512, 64), generator=g, device="cuda").to(dt)
+    both_kernels(lambda: K.matmul(q, k.transpose(-2, -1), out_dtype=torch.float32))
+
+
+def test_cta_pair_kernel_fp32_split_matmul():
+    g = torch.Generator(device="cuda").manual_seed(33)
+    a = torch.randn((1024, 520), generator=g, device="cuda")
+    b = torch.randn((520, 384), generator=g, device="cuda")
+    c, = both_kernels(lambda: K.matmul(a, b))
+    bound = 1e-5 * (a.abs().double() @ b.abs().double())
+    assert bool(((c.double() - a.double() @ b.double()).abs() <= bound).all())
