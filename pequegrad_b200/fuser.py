@@ -9,6 +9,15 @@ linear program the kernels take (the counterpart of `graph_to_ir`,
 csrc/compiler/ir.cpp:839-1286). Unlike the reference there is no
 "fewer than 1024 reduced elements" refusal and shapes are runtime data, so one
 compiled kernel serves every shape.
+
+Two graph rewrites of the reference run here as well:
+  * the fused-linear pattern (`recursive_fused_linear`, csrc/compiler/compile.hpp;
+    FusedLinearBiasAct, csrc/cuda/other.cu:19-166): `act(x @ w + bias)` becomes ONE
+    tensor-core GEMM whose epilogue adds the bias and applies ReLU / tanh-GELU;
+  * `amp(f)` (pequegrad/transforms/automatic_mixed_precision.py:37-146): matmuls of
+    fp32 operands run as fp16-in / fp32-accumulate GEMMs with an fp32 result, the
+    `(xw + b).relu()` pattern rides in that GEMM's epilogue, and fp32 -> fp16 -> fp32
+    cast pairs (and the reverse) are dropped.
 """
 from __future__ import annotations
 
@@ -25,6 +34,7 @@ _ELEMENTWISE = set(T.BINARY) | set(T.UNARY) | {"where", "astype", "fill"}
 _REDUCES = {"sum", "mean", "max_reduce", "argmax"}
 _CAST = {torch.float16: "CAST_F16", torch.float32: "CAST_F32", torch.int32: "CAST_I32", torch.bfloat16: "CAST_BF16"}
 _fuse_composites = False
+EAGER, JIT, AMP = 0, 1, 2  # evaluation modes handed down the graph walk
 
 
 @contextlib.contextmanager
@@ -57,6 +67,66 @@ def _matmul(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         batch = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
         a, b = a.expand(batch + a.shape[-2:]), b.expand(batch + b.shape[-2:])
     return K.matmul(a, b)
+
+
+def _strip_broadcast(node):
+    while node.op == "broadcast_to" and node._buf is None:
+        node = node.args[0]
+    return node
+
+
+def _is_zero(node) -> bool:
+    node = _strip_broadcast(node)
+    return node.op == "fill" and node.attrs["value"] == 0.0
+
+
+def _match_linear(node, mode):
+    """(matmul node, bias node or None, act) when `node` is `act(x @ w + bias)` with a bias over the last dim and
+    act in {none, ReLU as max(., 0), the tanh-GELU composite}; None when there is nothing to fold into the GEMM."""
+    act, n = 0, node
+    if "gelu_of" in n.attrs and (mode == AMP or n.dtype in (torch.float16, torch.bfloat16)):
+        # the epilogue's GELU uses the hardware tanh approximation: good to ~1e-3, so fp32 results keep the exact chain
+        act, n = 2, n.attrs["gelu_of"]
+    elif n.op == "max" and n._buf is None and len(n.args) == 2:
+        a, b = n.args
+        if _is_zero(b):
+            act, n = 1, a
+        elif _is_zero(a):
+            act, n = 1, b
+    bias = None
+    if n.op == "add" and n._buf is None:
+        for mm, bb in (n.args, n.args[::-1]):
+            base = _strip_broadcast(bb)
+            if (mm.op == "matmul" and mm._buf is None and base.op != "fill" and base.ndim >= 1 and base.shape[-1] == mm.shape[-1]
+                    and all(d == 1 for d in base.shape[:-1])):
+                bias, n = base, mm
+                break
+        else:
+            return None
+    if n.op != "matmul" or n._buf is not None or (bias is None and act == 0):
+        return None
+    return n, bias, act
+
+
+def _half_operands(a: torch.Tensor, b: torch.Tensor):
+    """fp32 matmul operands as fp16, each cast in one pass: `a` row-major, `b` straight into the [.., N, K]
+    array whose transposed view the GEMM reads in place (no second re-layout of the weight)."""
+    (a16,) = K.fused_elementwise([a], [("LOAD", 0)], out_dtypes=[torch.float16])
+    (bt16,) = K.fused_elementwise([b.transpose(-2, -1)], [("LOAD", 0)], out_dtypes=[torch.float16])
+    return a16, bt16.transpose(-2, -1)
+
+
+def _linear(mm, bias, act, mode, out_dtype):
+    a, b = (_emit_leaf(t, mode) for t in mm.args)
+    bias_buf = None if bias is None else _emit_leaf(bias, mode).reshape(-1)
+    if mode == AMP and a.dtype == torch.float32 and b.dtype == torch.float32:
+        a, b = _half_operands(a, b)
+        if bias_buf is not None and bias_buf.dtype != torch.float32:
+            (bias_buf,) = K.fused_elementwise([bias_buf], [("LOAD", 0)], out_dtypes=[torch.float32])
+    if b.dim() > 2 and b.shape[:-2] != a.shape[:-2]:
+        batch = torch.broadcast_shapes(a.shape[:-2], b.shape[:-2])
+        a, b = a.expand(batch + a.shape[-2:]), b.expand(batch + b.shape[-2:])
+    return K.matmul(a, b, bias=bias_buf, act=act, out_dtype=out_dtype)
 
 
 def _emit_leaf(node: T.Tensor, fuse: bool) -> torch.Tensor:
@@ -92,6 +162,8 @@ class _Region:
             ix = len(self.prog) - 1
         elif node.op == "broadcast_to" and node.args[0].op == "fill":
             ix = self.emit(node.args[0], stop)  # a constant seen through a broadcast is still an immediate
+        elif _match_linear(node, self.fuse) is not None:
+            return self._as_leaf(node)  # act(x @ w + bias) inside a larger region: bias and activation stay in the GEMM
         elif (node.op in _ELEMENTWISE and node._buf is None and node.shape == self.shape and len(self.prog) < MAX_REGION_INSTRS
               and (len(self.inputs) < L.MAX_INPUTS - 1)):
             if node.op in T.BINARY:
@@ -135,10 +207,10 @@ def _find_reduce(node, shape, seen=None):
     return None
 
 
-def _eval_fused(node: T.Tensor):
+def _eval_fused(node: T.Tensor, mode: int = JIT):
     red = node if node.op in _REDUCES else _find_reduce(node, node.shape)
     if red is None:
-        reg = _Region(node.shape, True)
+        reg = _Region(node.shape, mode)
         reg.emit(node)
         if not reg.inputs:  # constants only
             (out,) = K.fused_elementwise([], reg.prog, shape=node.shape, out_dtypes=[node.dtype])
@@ -147,11 +219,11 @@ def _eval_fused(node: T.Tensor):
         node._buf = out
         return
     x = red.args[0]
-    pro = _Region(x.shape, True)
+    pro = _Region(x.shape, mode)
     pro.emit(x)
     epi_prog, epi_inputs = [], []
     if red is not node:
-        epi = _Region(node.shape, True)
+        epi = _Region(node.shape, mode)
         epi.emit(node, stop=red)
         epi_prog = epi.prog
         keep = K.reduced_shape(x.shape, red.attrs["axes"], True)
@@ -179,13 +251,24 @@ def evaluate(node: T.Tensor, fuse: bool = False):
     """Materialise `node` (and what it needs) on the device."""
     if node._buf is not None:
         return
-    fuse = fuse or getattr(node, "_jit", False)
-    if node.op in T.VIEW_OPS:
+    fuse = max(int(fuse), int(getattr(node, "_jit", 0)))
+    lin = _match_linear(node, fuse) if fuse else None
+    if lin is not None:
+        node._buf = _linear(*lin, fuse, node.dtype)
+    elif (fuse == AMP and node.op == "astype" and node.args[0].op == "astype" and node.args[0]._buf is None
+          and node.args[0].args[0].dtype == node.dtype and {node.dtype, node.args[0].dtype} == {torch.float16, torch.float32}):
+        # astype_f32_f16_f32 / astype_f16_f32_f16 (automatic_mixed_precision.py:83-113): the pair is dropped
+        node._buf = _emit_leaf(node.args[0].args[0], fuse)
+    elif node.op in T.VIEW_OPS:
         node._buf = _view(node, _emit_leaf(node.args[0], fuse))
     elif node.op == "fill":
         (node._buf,) = K.fused_elementwise([], [("IMM", 0, 0, 0, node.attrs["value"])], shape=node.shape, out_dtypes=[node.dtype])
     elif node.op == "matmul":
-        node._buf = _matmul(_emit_leaf(node.args[0], fuse), _emit_leaf(node.args[1], fuse))
+        a, b = _emit_leaf(node.args[0], fuse), _emit_leaf(node.args[1], fuse)
+        if fuse == AMP and a.dtype == torch.float32 and b.dtype == torch.float32:
+            node._buf = _linear(node, None, 0, fuse, torch.float32)  # matmul_amp: fp16 operands, fp32 accumulator and result
+        else:
+            node._buf = _matmul(a, b)
     elif node.op == "attention":
         q, k, v = (_emit_leaf(a, fuse) for a in node.args)
         node._buf = K.attention(q, k, v, scale=node.attrs["scale"], causal=node.attrs["causal"])
@@ -196,21 +279,33 @@ def evaluate(node: T.Tensor, fuse: bool = False):
         rows = x.reshape(-1, node.attrs["n"])
         node._buf = K.layernorm_rows(rows, g if g is None else g.reshape(-1), b if b is None else b.reshape(-1), node.attrs["eps"]).view(node.shape)
     elif fuse:
-        _eval_fused(node)
+        _eval_fused(node, fuse)
     else:
         _eval_eager(node)
     node.args = ()  # evaluated nodes drop their graph, as the reference frees children after eval
 
 
-def jit(f):
-    """`pg.jit`: the outputs of `f` are evaluated through the fuser (pequegrad/transforms/compile.py:84-236).
-    Tracing is just running `f` on lazy tensors; there is no per-shape compilation to cache."""
+def _traced(f, mode):
     def wrapped(*args, **kwargs):
         with fusing_composites():
             out = f(*args, **kwargs)
         outs = out if isinstance(out, (tuple, list)) else (out,)
         for o in outs:
             if isinstance(o, T.Tensor):
-                o._jit = True
+                o._jit = mode
         return out
     return wrapped
+
+
+def jit(f):
+    """`pg.jit`: the outputs of `f` are evaluated through the fuser (pequegrad/transforms/compile.py:84-236).
+    Tracing is just running `f` on lazy tensors; there is no per-shape compilation to cache."""
+    return _traced(f, JIT)
+
+
+def amp(f):
+    """`pg.amp`: automatic mixed precision (pequegrad/transforms/automatic_mixed_precision.py:145-146). Every
+    matmul of fp32 operands runs as an fp16 GEMM and returns fp32; where the reference's `cublasHgemm` accumulates
+    in fp16 (csrc/cuda/matmul.cu:140-155), the accumulator here is fp32 in tensor memory, and the bias + ReLU of
+    `bias_relu_add_amp` are applied to that fp32 accumulator in the GEMM's epilogue instead of in fp16."""
+    return _traced(f, AMP)

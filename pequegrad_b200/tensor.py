@@ -279,7 +279,9 @@ def tanh(x): return 2.0 / (1.0 + exp(-2.0 * x)) - 1.0  # pequegrad/ops.py:159-16
 
 def gelu(x: Tensor) -> Tensor:
     """tanh approximation, pequegrad/ops.py:109-118."""
-    return 0.5 * x * (1.0 + tanh(math.sqrt(2 / math.pi) * (x + 0.044715 * (x ** 3.0))))
+    y = 0.5 * x * (1.0 + tanh(math.sqrt(2 / math.pi) * (x + 0.044715 * (x ** 3.0))))
+    y.attrs = dict(y.attrs, gelu_of=x)  # lets the fuser fold gelu(x @ w + b) into the GEMM's epilogue
+    return y
 
 
 def scaled_dot_product_attention(query: Tensor, key: Tensor, value: Tensor, mask: Tensor | None = None, is_causal: bool = False) -> Tensor:

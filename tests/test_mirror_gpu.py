@@ -131,6 +131,69 @@ def test_matmul_half_float_double_and_reference_error_for_int32():
         (pg.Tensor(a.astype(np.int32)) @ pg.Tensor(w.astype(np.int32))).eval()
 
 
+def test_fused_linear_pattern_is_one_gemm():
+    """`recursive_fused_linear` (FusedLinearBiasAct, csrc/cuda/other.cu:19-166): under jit, act(x @ w + b) is ONE
+    GEMM launch with the bias and the activation in its epilogue; eager runs matmul, add and max as separate kernels."""
+    rng = np.random.default_rng(11)
+    x = (rng.standard_normal((256, 128)) * 0.5).astype(np.float16)
+    wt = (rng.standard_normal((192, 128)) * 0.1).astype(np.float16)  # the weight as [N, K]: its transposed view is read in place
+    b = rng.standard_normal(192).astype(np.float16)
+    pre = x.astype(np.float32) @ wt.astype(np.float32).T + b.astype(np.float32)
+    wt_d = pg.Tensor(wt)
+    for f, want in [(lambda t, w, c: (t @ w + c).relu(), np.maximum(pre, 0)),
+                    (lambda t, w, c: pg.gelu(t @ w + c), torch.nn.functional.gelu(torch.from_numpy(pre), approximate="tanh").numpy()),
+                    (lambda t, w, c: t @ w + c, pre)]:
+        eager = f(pg.Tensor(x), wt_d.transpose(0, 1), pg.Tensor(b)).numpy().astype(np.float32)
+        out = {}
+        n = launches(lambda: out.setdefault("v", fuser.jit(f)(pg.Tensor(x), wt_d.transpose(0, 1), pg.Tensor(b)).numpy()))
+        assert n == 1
+        assert_close(out["v"].astype(np.float32), want, 2e-2, 2e-2 * float(np.abs(want).max()))
+        assert_close(eager, want, 2e-2, 2e-2 * float(np.abs(want).max()))
+    # inside a larger region the bias and the activation still ride in the GEMM: GEMM + one elementwise kernel
+    g = lambda t, w, c: (t @ w + c).relu() * 2.0 + 1.0  # noqa: E731
+    n = launches(lambda: out.setdefault("g", fuser.jit(g)(pg.Tensor(x), wt_d.transpose(0, 1), pg.Tensor(b)).numpy()))
+    assert n == 2
+    assert_close(out["g"].astype(np.float32), np.maximum(pre, 0) * 2 + 1, 2e-2, 2e-2 * float(np.abs(pre).max()))
+    # fp32: bias + ReLU go into the tf32-split GEMM's epilogue too (the exact-chain GELU stays a kernel of its own)
+    x32, w32, b32 = x.astype(np.float32), wt.astype(np.float32).T.copy(), b.astype(np.float32)
+    got = fuser.jit(lambda t, w, c: (t @ w + c).relu())(pg.Tensor(x32), pg.Tensor(w32), pg.Tensor(b32)).numpy()
+    assert_close(got, np.maximum(x32.astype(np.float64) @ w32 + b32, 0), 1e-5, 1e-5 * float(np.abs(pre).max()))
+    got = fuser.jit(lambda t, w, c: pg.gelu(t @ w + c))(pg.Tensor(x32), pg.Tensor(w32), pg.Tensor(b32)).numpy()
+    assert_close(got, torch.nn.functional.gelu(torch.from_numpy(x32 @ w32 + b32), approximate="tanh").numpy(), 1e-5, 1e-5)
+
+
+def test_amp_runs_fp32_matmuls_as_fp16_gemms_with_fp32_results():
+    """pequegrad/transforms/automatic_mixed_precision.py:37-146 (`matmul_amp`, `bias_relu_add_amp`, the astype pairs);
+    the reference has no test of its own for amp (examples/amp_fc.py only times it), so the fp32 function is the
+    yardstick, at the 16-bit tolerance."""
+    rng = np.random.default_rng(12)
+    x = (rng.standard_normal((4, 128, 256)) * 0.5).astype(np.float32)
+    w1 = (rng.standard_normal((256, 512)) * 0.05).astype(np.float32)
+    b1 = rng.standard_normal(512).astype(np.float32)
+    w2 = (rng.standard_normal((512, 64)) * 0.05).astype(np.float32)
+
+    def mlp(t, a, c, d):
+        return (t @ a + c).relu() @ d
+
+    want = np.maximum(x @ w1 + b1, 0) @ w2
+    out = {}
+    got = fuser.amp(mlp)(*(pg.Tensor(t) for t in (x, w1, b1, w2)))
+    assert got.dtype == pg.float32  # results come back as fp32
+    n = launches(lambda: got.numpy())
+    assert n == 6  # two casts + GEMM (bias and ReLU in its epilogue), twice
+    assert_close(got.numpy(), want, 2e-2, 2e-2 * float(np.abs(want).max()))
+    # exactly the fp16-rounded operands with an fp32 accumulator: far tighter than fp16 accumulation would allow
+    h16 = np.maximum(x.astype(np.float16).astype(np.float64) @ w1.astype(np.float16).astype(np.float64) + b1, 0).astype(np.float32)
+    want16 = h16.astype(np.float16).astype(np.float64) @ w2.astype(np.float16).astype(np.float64)
+    assert_close(got.numpy(), want16, 1e-4, 1e-4 * float(np.abs(want16).max()))
+    # astype pairs vanish under amp (the value keeps its original precision): no kernel at all
+    t16 = pg.Tensor(x.astype(np.float16))
+    back = fuser.amp(lambda t: t.astype(pg.float32).astype(pg.float16))(t16)
+    assert launches(lambda: back.eval()) == 0 and np.array_equal(back.numpy(), x.astype(np.float16))
+    # non-fp32 matmuls are left alone
+    assert fuser.amp(lambda a, c: a @ c)(t16, pg.Tensor(w1.astype(np.float16))).dtype == pg.float16
+
+
 def test_sdpa_composite_and_its_fused_form():
     """pequegrad/ops.py:792-818 and tests/test_high_level_ops.py:623-639 (sdpa with a tril mask): eager = the composite
     (matmul, where, softmax, matmul), under jit without a mask tensor = the one-kernel attention."""
