@@ -9,7 +9,7 @@
 //                 S = Q K^T    128 x 64 x 64, fp32 in TMEM
 //                 O += P V     128 x 64 x 64, fp32 in TMEM; V is read as an MN-major operand, so it needs no transpose
 //   warps 2-5   softmax: thread = query row. tcgen05.ld the row of S, mask, online max / sum with exp2 on the
-//               SFU, rescale the row of O in TMEM when its max grew, write P (16-bit) to shared memory in the
+//               SFU, rescale the row of O in TMEM when its max outgrew the exponent reference by 2^8, write P (16-bit) to shared memory in the
 //               K-major 128B-swizzled operand layout for the PV MMA; at the end O / sum -> global
 // Three CTAs fit per SM (65 KB of shared memory and 128 TMEM columns each), so one CTA's MMAs and loads run
 // under the others' exponentials: the kernel is bound by its softmax warps, and three per scheduler hide the
@@ -33,11 +33,12 @@ constexpr int kQB = 128;  // query rows per CTA
 constexpr int kKB = 64;   // keys per block
 constexpr int kHD = 64;   // head dim
 constexpr int kKStages = 2, kVStages = 2;
-constexpr int kAttnThreads = 192;
+constexpr int kAttnThreads = 320;  // producer warp, MMA warp, eight softmax warps
 constexpr int kQBytes = kQB * kHD * 2, kKVBytes = kKB * kHD * 2, kPBytes = kQB * kKB * 2;
-constexpr int kAttnSmem = kQBytes + (kKStages + kVStages) * kKVBytes + kPBytes + 1024 /*alignment slack*/ + 256 /*barriers*/;
+constexpr int kAttnSmem = kQBytes + (kKStages + kVStages) * kKVBytes + kPBytes + 1024 /*alignment slack*/ + 256 /*barriers*/ + 2 * 2 * kQB * 4 /*half-row maxima, two phases*/;
 constexpr int kAttnTmemCols = 128;  // S [0,64), O [64,128)
 constexpr int kAttnCtasPerSm = 3;
+constexpr float kLazyRescale = 8.0f;  // log2 of the largest p allowed before a row's exponent reference moves
 
 struct AttnParams {
   int T, Tk, H, B, n_qblk;
@@ -99,6 +100,16 @@ __device__ __forceinline__ uint32_t pack_pair(float lo, float hi, bool is_h) {
   return *reinterpret_cast<const uint32_t *>(&b);
 }
 
+// 64-thread named barrier of the two softmax warps that share TMEM lane quadrant `quad` (ids 1..4; 0 is __syncthreads)
+__device__ __forceinline__ void pair_sync(int quad) {
+  switch (quad) {
+    case 0: asm volatile("bar.sync 1, 64;" ::: "memory"); break;
+    case 1: asm volatile("bar.sync 2, 64;" ::: "memory"); break;
+    case 2: asm volatile("bar.sync 3, 64;" ::: "memory"); break;
+    default: asm volatile("bar.sync 4, 64;" ::: "memory"); break;
+  }
+}
+
 __device__ __forceinline__ void attn_fail(const AttnParams &p, volatile int *abort_flag, int role) {
   *abort_flag = 1;
   atomicCAS(p.err, 0, ((8 + role) << 16) | (int)(blockIdx.x & 0xffff));
@@ -109,7 +120,6 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
                                                                         const __grid_constant__ CUtensorMap map_v,
                                                                         const __grid_constant__ AttnParams p) {
   extern __shared__ uint8_t smem_raw[];
-  if (*(volatile int *)p.err != 0) return;
   const uint32_t raw = smem_u32(smem_raw);
   uint8_t *smem = smem_raw + ((1024u - (raw & 1023u)) & 1023u);
   uint8_t *q_s = smem;
@@ -128,6 +138,8 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
   uint64_t *pv_done = p_full + 1;            // [1]  MMA -> softmax: P and V consumed, O updated
   uint32_t *tmem_slot = reinterpret_cast<uint32_t *>(pv_done + 1);
   volatile int *abort_flag = reinterpret_cast<volatile int *>(tmem_slot + 1);
+  int *dead = const_cast<int *>(abort_flag) + 1;
+  float *xch = reinterpret_cast<float *>(p_s + kPBytes + 256);  // [phase][column half][row]
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   // heavy query blocks (those with the most keys under a causal mask) are scheduled first
@@ -143,10 +155,11 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
     for (int s = 0; s < kKStages; ++s) { mbar_init(&k_full[s], 1); mbar_init(&k_empty[s], 1); }
     for (int s = 0; s < kVStages; ++s) { mbar_init(&v_full[s], 1); mbar_init(&v_empty[s], 1); }
     mbar_init(s_full, 1);
-    mbar_init(s_free, 4);
-    mbar_init(p_full, 4);
+    mbar_init(s_free, 8);
+    mbar_init(p_full, 8);
     mbar_init(pv_done, 1);
     *abort_flag = 0;
+    *dead = *(volatile int *)p.err != 0;  // an earlier launch failed and the host has not cleared the word: do nothing
     asm volatile("fence.mbarrier_init.release.cluster;" ::: "memory");
   }
   if (warp == 1) tmem_alloc(tmem_slot, kAttnTmemCols);
@@ -155,7 +168,10 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  if (warp == 0) {
+  if (*dead) {
+    // one decision for the whole CTA (read by one thread before the barrier): the pair barriers below need every
+    // softmax warp or none
+  } else if (warp == 0) {
     if (lane == 0) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
@@ -210,56 +226,77 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
       }
     }
   } else {
-    const int quad = warp & 3;  // TMEM lanes 32*quad .. +31
+    // Two warps share each TMEM lane quadrant (a warp reaches lanes 32 * (warp % 4) .. + 31): thread = (query row,
+    // half of the block's 64 keys). The halves exchange their maxima through shared memory once per block (a
+    // 64-thread named barrier per quadrant) so that both use the same exponent reference; the row sums stay
+    // per half until the end. Eight softmax warps per CTA, three CTAs per SM: six warps per scheduler to hide
+    // the TMEM, barrier and SFU latencies of one another.
+    const int quad = warp & 3;              // TMEM lanes 32*quad .. +31
+    const int ch = (warp - 2) >> 2;         // column half: keys [32*ch, 32*ch + 32) of the block, O columns likewise
     const int row = quad * 32 + lane, qrow = q0 + row;
     const bool is_h = p.is_half != 0;
     const float c = p.c;
     const uint32_t lane_addr = tmem_base + ((uint32_t)(quad * 32) << 16);
+    const uint32_t s_addr = lane_addr + (uint32_t)(ch * 32), o_addr = lane_addr + 64u + (uint32_t)(ch * 32);
     float m = -INFINITY, l = 0.f;
     bool ok = true;
     for (int j = 0; j < n_kb; ++j) {
-      if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag);
-      ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-      if (!ok) { if (lane == 0) attn_fail(p, abort_flag, 8); break; }
+      // A warp that gave up keeps meeting its partner at the pair barrier, once per block, so that neither is ever
+      // left waiting there: every softmax warp passes exactly n_kb + 1 pair barriers, whatever happened.
+      if (ok) {
+        if (lane == 0) ok = mbar_wait(s_full, j & 1, abort_flag);
+        ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
+        if (!ok && lane == 0) attn_fail(p, abort_flag, 8);
+      }
+      if (!ok) { pair_sync(quad); continue; }
       tc_fence_after();
-      uint32_t sa[32], sbv[32];
-      tmem_ld32_issue(lane_addr, sa);
-      tmem_ld32_issue(lane_addr + 32u, sbv);
+      uint32_t sa[32];
+      tmem_ld32_issue(s_addr, sa);
       tmem_ld_wait();
       tc_fence_before();
       __syncwarp();
       if (lane == 0) mbar_arrive(s_free);
-      float s[64];
+      float s[32];
 #pragma unroll
-      for (int i = 0; i < 32; ++i) { s[i] = __uint_as_float(sa[i]); s[32 + i] = __uint_as_float(sbv[i]); }
-      const int key0 = j * kKB;
-      if ((p.causal && key0 + kKB - 1 > q0) || key0 + kKB > p.Tk) {  // block-uniform: only edge blocks pay for the mask
+      for (int i = 0; i < 32; ++i) s[i] = __uint_as_float(sa[i]);
+      const int key0 = j * kKB + ch * 32;
+      if ((p.causal && j * kKB + kKB - 1 > q0) || j * kKB + kKB > p.Tk) {  // block-uniform: only edge blocks pay for the mask
 #pragma unroll
-        for (int i = 0; i < 64; ++i) {
+        for (int i = 0; i < 32; ++i) {
           const int key = key0 + i;
           if ((p.causal && key > qrow) || key >= p.Tk) s[i] = -INFINITY;
         }
       }
-      // three-input max, four independent chains (a single chain of 32 dependent operations left the scheduler idle)
-      float mq[4];
+      // three-input max, two independent chains
+      float mq[2];
 #pragma unroll
-      for (int g = 0; g < 4; ++g) {
+      for (int g = 0; g < 2; ++g) {
         mq[g] = max3(s[16 * g], s[16 * g + 1], s[16 * g + 2]);
 #pragma unroll
         for (int i = 3; i + 1 < 16; i += 2) mq[g] = max3(mq[g], s[16 * g + i], s[16 * g + i + 1]);
         mq[g] = fmaxf(mq[g], s[16 * g + 15]);
       }
-      const float mx = fmaxf(fmaxf(mq[0], mq[1]), fmaxf(mq[2], mq[3]));
-      const float m_new = fmaxf(m, mx);
+      float mx = fmaxf(mq[0], mq[1]);
+      float *xj = xch + (j & 1) * (2 * kQB);
+      xj[ch * kQB + row] = mx;
+      pair_sync(quad);
+      mx = fmaxf(mx, xj[(ch ^ 1) * kQB + row]);
+      // `m` is the reference point of the exponents, not the exact running max: it moves only when the row's max
+      // outgrew it by more than kLazyRescale in the log2 domain (or on the row's first finite score). Until then
+      // p <= 2^kLazyRescale, harmless in the fp32 sum, the fp32 accumulator and 16-bit P, and O / l is the same
+      // quotient whatever the reference point; the rescale of O in tensor memory becomes a rare event.
+      const float m_cand = fmaxf(m, mx);
+      const bool grow = (m_cand - m) * c > kLazyRescale;  // -inf -> finite is +inf > threshold; -inf -> -inf is NaN: false
+      const float m_new = grow ? m_cand : m;
       const float m_use = m_new == -INFINITY ? 0.f : m_new;  // a row with no key yet: every p is 0
-      const float alpha = ex2f((m - m_use) * c);
+      const float alpha = grow ? ex2f((m - m_use) * c) : 1.0f;
       const float mc = m_use * c;
       // exponent arguments and the row sum on the packed fp32 pipe (two lanes of work per instruction)
       const float2 c2 = make_float2(c, c), nmc2 = make_float2(-mc, -mc);
       float2 sq[4] = {make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f), make_float2(0.f, 0.f)};
-      uint32_t pk[32];
+      uint32_t pk[16];
 #pragma unroll
-      for (int i = 0; i < 64; i += 2) {
+      for (int i = 0; i < 32; i += 2) {
         const float2 t = fma2(make_float2(s[i], s[i + 1]), c2, nmc2);
         const float2 pp = make_float2(ex2f(t.x), ex2f(t.y));
         sq[(i >> 1) & 3] = add2(sq[(i >> 1) & 3], pp);  // four independent partial sums
@@ -273,27 +310,24 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
         // PV(j-1) must have consumed P and updated O before either is touched
         if (lane == 0) ok = mbar_wait(pv_done, (j - 1) & 1, abort_flag);
         ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
-        if (!ok) { if (lane == 0) attn_fail(p, abort_flag, 9); break; }
+        if (!ok) { if (lane == 0) attn_fail(p, abort_flag, 9); continue; }
         tc_fence_after();
         if (__any_sync(0xffffffffu, alpha != 1.0f)) {
-          // some row of this warp got a larger max: O_row *= 2^((m_old - m_new) c)
+          // some row of this warp moved its reference: O_row *= 2^((m_old - m_new) c), this warp's 32 columns
+          uint32_t o[32];
+          tmem_ld32_issue(o_addr, o);
+          tmem_ld_wait();
 #pragma unroll
-          for (int half = 0; half < 2; ++half) {
-            uint32_t o[32];
-            tmem_ld32_issue(lane_addr + 64u + (uint32_t)(half * 32), o);
-            tmem_ld_wait();
-#pragma unroll
-            for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
-            tmem_st32(lane_addr + 64u + (uint32_t)(half * 32), o);
-          }
+          for (int i = 0; i < 32; ++i) o[i] = __float_as_uint(__uint_as_float(o[i]) * alpha);
+          tmem_st32(o_addr, o);
           tmem_st_wait();
         }
       }
-      // P row -> shared memory, K-major with the 128B swizzle: 16-byte chunk i of row r sits at chunk i ^ (r & 7)
+      // P half row -> shared memory, K-major with the 128B swizzle: 16-byte chunk i of row r sits at chunk i ^ (r & 7)
       uint8_t *prow = p_s + row * 128;
 #pragma unroll
-      for (int i = 0; i < 8; ++i)
-        *reinterpret_cast<uint4 *>(prow + ((i ^ (row & 7)) << 4)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
+      for (int i = 0; i < 4; ++i)
+        *reinterpret_cast<uint4 *>(prow + (((ch * 4 + i) ^ (row & 7)) << 4)) = make_uint4(pk[4 * i], pk[4 * i + 1], pk[4 * i + 2], pk[4 * i + 3]);
       fence_proxy_async();
       tc_fence_before();
       __syncwarp();
@@ -304,29 +338,32 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
       ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
       if (!ok && lane == 0) attn_fail(p, abort_flag, 10);
     }
+    // the two halves of a row add their sums (both were kept against the same reference); failed or not, every
+    // softmax warp comes here
+    float *xl = xch + (n_kb & 1) * (2 * kQB);
+    xl[ch * kQB + row] = l;
+    pair_sync(quad);
+    l += xl[(ch ^ 1) * kQB + row];
     if (ok) {
       tc_fence_after();
       const float inv = n_kb > 0 ? 1.0f / l : 0.f;
       uint8_t *orow = reinterpret_cast<uint8_t *>(p.out) + ((int64_t)b * p.o_batch + (int64_t)h * p.o_head + (int64_t)qrow * p.o_row) * 2;
+      uint32_t o[32];
+      if (n_kb > 0) {
+        tmem_ld32_issue(o_addr, o);
+        tmem_ld_wait();
+      } else {
 #pragma unroll
-      for (int half = 0; half < 2; ++half) {
-        uint32_t o[32];
-        if (n_kb > 0) {
-          tmem_ld32_issue(lane_addr + 64u + (uint32_t)(half * 32), o);
-          tmem_ld_wait();
-        } else {
+        for (int i = 0; i < 32; ++i) o[i] = 0u;
+      }
+      if (qrow < p.T) {
 #pragma unroll
-          for (int i = 0; i < 32; ++i) o[i] = 0u;
-        }
-        if (qrow < p.T) {
+        for (int i = 0; i < 4; ++i) {
+          uint32_t w[4];
 #pragma unroll
-          for (int i = 0; i < 4; ++i) {
-            uint32_t w[4];
-#pragma unroll
-            for (int k = 0; k < 4; ++k)
-              w[k] = pack_pair(__uint_as_float(o[8 * i + 2 * k]) * inv, __uint_as_float(o[8 * i + 2 * k + 1]) * inv, is_h);
-            *reinterpret_cast<uint4 *>(orow + half * 64 + i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
-          }
+          for (int k = 0; k < 4; ++k)
+            w[k] = pack_pair(__uint_as_float(o[8 * i + 2 * k]) * inv, __uint_as_float(o[8 * i + 2 * k + 1]) * inv, is_h);
+          *reinterpret_cast<uint4 *>(orow + ch * 64 + i * 16) = make_uint4(w[0], w[1], w[2], w[3]);
         }
       }
     }
