@@ -367,6 +367,13 @@ struct Acc {
       if (x > v || (x == v && idx < i)) { v = x; i = idx; }
     }
   }
+  // For a thread's own stream, which reaches each accumulator in increasing index order: a tie can never carry a
+  // smaller index there, so argmax needs one comparison (ties across threads are settled by merge()).
+  __device__ __forceinline__ void add_stream(T x, int idx) {
+    if (ROP == ROP_ARGMAX) {
+      if (x > v) { v = x; i = idx; }
+    } else add(x, idx);
+  }
   __device__ __forceinline__ void merge(T ov, int oi) { add(ov, oi); }
 };
 

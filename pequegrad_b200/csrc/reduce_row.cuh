@@ -112,7 +112,7 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
           const uint32_t c = c0 + u * G * V;
           if (c < c_hi) {
 #pragma unroll
-            for (int e = 0; e < V; ++e) acc[(u * V + e) & 3].add(run[u * V + e], (int)(c + e));
+            for (int e = 0; e < V; ++e) acc[(u * V + e) & 3].add_stream(run[u * V + e], (int)(c + e));
           }
         }
       }
@@ -130,7 +130,7 @@ __global__ void __launch_bounds__(256) reduce_row_kernel(const __grid_constant__
         else if (MODE == 3) run[0] = w[0][0] * aff_a + aff_b;
         else if (MODE == 1) chain_eval_fast<T, NIN, B>(cr, w, run);
         else chain_eval<T, NIN, B>(p.pro, w, run);
-        acc[0].add(run[0], (int)c);
+        acc[0].add_stream(run[0], (int)c);
       }
     }
   }

@@ -24,6 +24,10 @@ def _event_us(fn, reps, flush=None):
     for a, b in evs:
         if flush is not None:
             flush()
+        # The device first spins for ~0.2 ms without touching memory, so that the launch below is already queued when
+        # the first event is reached: without this runway the interval also holds the host's time to issue the call
+        # (tens of microseconds for a ctypes call), which swamps kernels of 10-60 us.
+        torch.cuda._sleep(400_000)
         a.record()
         fn()
         b.record()
@@ -274,10 +278,17 @@ class Rows:
         self.step()
         self.host_y.copy_(self.ln_out, non_blocking=True)
 
+    def _flush_l2(self):
+        # 201 MB written, then another 201 MB read: the L2 (126 MB) ends up holding clean lines of unrelated data, as
+        # it would after the kernels that run between two LayerNorms in use. Writing alone leaves the L2 full of dirty
+        # lines, and their write-back would be charged to the timed kernel's first misses.
+        self.S[:8].zero_().add_(1)
+        self._sink = self.S[8:16].amax()
+
     def roofline(self, pk, reps):
         from . import kernels as K
         sm_us = _event_us(lambda: K.softmax_rows(self.S, causal=True), reps)
-        ln_us = _event_us(lambda: K.layernorm_rows(self.X, self.gamma, self.beta, 1e-5), reps, flush=lambda: self.S[:8].zero_().add_(1))
+        ln_us = _event_us(lambda: K.layernorm_rows(self.X, self.gamma, self.beta, 1e-5), reps, flush=self._flush_l2)
         ach = self.sm_bytes / (sm_us * 1e-6) / 1e9
         ln = self.ln_bytes / (ln_us * 1e-6) / 1e9
         return {"bound": "hbm", "kernel": "softmax_rows (causal, fp16, 1024 columns)", "achieved": round(ach, 1), "peak": pk["hbm"], "unit": "GB/s",
