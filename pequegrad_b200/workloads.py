@@ -21,13 +21,15 @@ def _event_us(fn, reps, flush=None):
     """Median device time of fn() in microseconds, CUDA events on the current stream."""
     import torch
     evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
+    runway = getattr(torch.cuda, "_sleep", None)  # a spin kernel; without it the timings below are upper bounds
     for a, b in evs:
         if flush is not None:
             flush()
         # The device first spins for ~0.2 ms without touching memory, so that the launch below is already queued when
         # the first event is reached: without this runway the interval also holds the host's time to issue the call
         # (tens of microseconds for a ctypes call), which swamps kernels of 10-60 us.
-        torch.cuda._sleep(400_000)
+        if runway is not None:
+            runway(400_000)
         a.record()
         fn()
         b.record()
