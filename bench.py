@@ -1,8 +1,8 @@
 #!/usr/bin/env python
-"""Benchmarks of the hot path: fused reduce kernels, row kernels, int8 MLP, GPT-2 forward.
+"""Benchmarks of the hot path: fused reduce kernels, row kernels, int8 MLP, GPT-2 forward, README case.
 
   python bench.py [--gpus N] [--steps K] [--warmup W] [--impl reference]
-                  [--workload sweep|mlp|gpt2|rows]
+                  [--workload sweep|mlp|gpt2|rows|readme]
 
 Default workload (`sweep`, the headline): a step = one pass over the reduction
 sweep: {sum, max, mean, argmax} x axis {0, 1, -1} x {A [8192,8192],
@@ -13,17 +13,24 @@ algorithmic bytes (inputs read once + outputs written once) / device time.
 The default run also times the other workloads briefly and reports them under
 `other_workloads` in the same JSON line.
 
-`mlp`:  int8 quantized MLP 784->1024->1024->10, 65536 rows per GPU (rows/s).
-`gpt2`: GPT-2 small forward, 32 x 1024 tokens per GPU, fp16 (tok/s).
-`rows`: causal softmax over fp16 [32,12,1024,1024] + LayerNorm over fp32 [16384,768] (GB/s).
+`mlp`:    int8 quantized MLP 784->1024->1024->10, batch 65536 (rows/s).
+`gpt2`:   GPT-2 small forward, batch 32 x 1024 tokens, fp16 (tok/s).
+`rows`:   causal softmax over fp16 [32,12,1024,1024] + LayerNorm over fp32 [16384,768] (GB/s).
+`readme`: the README fusion case, one fused kernel over 16.4 MB (microseconds per call, warm and cold L2).
 
 Every number is device time from CUDA events on the launching stream, max over
-ranks. With N > 1 GPUs every rank runs the workload on its own shard (weak
-scaling, no collective in the data path).
+ranks. With N > 1 GPUs the SAME fixed problem is partitioned over the ranks
+(strong scaling): each rank takes its slice of the same seeded global arrays
+through `pequegrad_b200.distrib.shard_tensor`, runs the kernels on it with no
+exchange, and the step ends with the final gather (NCCL all-gather), inside
+the timed region. `value` includes the gather; `compute_only` is the same
+measurement without it.
 
 `--impl reference` times the reference's CPU backend (its own templates where
 they were compiled into oracle/_ref, else the C restatement) on the host
-cores, on a bounded sample of the same workload.
+cores, on a bounded sample of the same workload. Where the reference's own CUDA
+kernels were compiled (oracle/_ref_cuda), the line also carries `reference_cuda`:
+their time on this GPU for the same case.
 """
 from __future__ import annotations
 
@@ -41,31 +48,9 @@ import numpy as np
 ROOT = Path(__file__).resolve().parent
 sys.path.insert(0, str(ROOT))
 
-AFFINE = [("LOAD", 0), ("IMM", 0, 0, 0, 1.5), ("MUL", 0, 1), ("IMM", 0, 0, 0, 0.25), ("ADD", 2, 3)]
-EXP_EPI = [("ACC",), ("EXP", 0)]
-OPS = ["sum", "max", "mean", "argmax"]
-SWEEP_DESC = ("reduction sweep: sum/max/mean/argmax x axis 0/1/-1 x A[8192,8192], B[64,4096,1024], "
-              "B.permute(0,2,1) view; prologue x*1.5+0.25, epilogue exp; one fused kernel per case")
-SHAPES = {"A": (8192, 8192), "B": (64, 4096, 1024), "Bp": (64, 1024, 4096)}
-# dram__bytes_read.sum + dram__bytes_write.sum per launch, averaged over the launches of one step of
-# each kernel family, from the ncu capture summarised in profiles/reduce_sweep_dram_traffic.md
-NCU_TRAFFIC_PER_LAUNCH = {"col": 916197568, "row": 672153568}
-
-
 def sweep_cases():
-    """(tensor name, op, axis, algorithmic bytes) in an order that alternates tensors."""
-    per = {}
-    for name, shape in SHAPES.items():
-        per[name] = []
-        for ax in (0, 1, -1):
-            for op in OPS:
-                n_in = int(np.prod(shape))
-                n_out = n_in // shape[ax]
-                per[name].append((name, op, ax, 4 * n_in + 4 * n_out))
-    out = []
-    for i in range(12):
-        out += [per["A"][i], per["B"][i], per["Bp"][i]]
-    return out
+    from pequegrad_b200.workloads import sweep_cases as sc
+    return sc()
 
 
 def peaks() -> dict:
@@ -136,128 +121,176 @@ def host_threads() -> int:
 
 
 # ---------------------------------------------------------------------------
-# Workloads. Each has: metric, unit, dtype, desc; setup(dev, rank); step(); units_per_step;
-# e2e_setup() / e2e_step() with h2d / d2h byte counts; roofline(pk, reps); cpu_sample(budget_s, threads).
-class Sweep:
-    name, metric, unit, dtype = "sweep", "fused-reduce HBM GB/s", "GB/s", "f32"
+# CPU arms: the reference's CPU backend (or the C / torch-CPU restatement where the reference has no CPU kernel
+# for the workload) on bounded samples. The only place besides tests/ and smoke() that executes oracle/.
+# Each returns (units done, seconds, sample description, kind).
+def cpu_sample_sweep(budget_s, threads):
+    """The reference CPU backend's eager chain (2 binary kernels, per-axis reduce, exp) on cases of the sweep."""
+    import oracle
+    from oracle.chain import fused_reduce_oracle
+    from pequegrad_b200.workloads import AFFINE, EXP_EPI, SHAPES
+    kind = "reference" if oracle.have_ref() else "port"
+    impl = "ref" if kind == "reference" else "port"
+    A = np.random.default_rng(2).standard_normal(SHAPES["A"], dtype=np.float32)
+    done_bytes, t_total, n = 0, 0.0, 0
+    a_cases = [c for c in sweep_cases() if c[0] == "A"]
+    while t_total < budget_s:
+        for name, op, ax, nbytes in a_cases:
+            t0 = time.perf_counter()
+            fused_reduce_oracle([A], op, [ax], False, AFFINE, () if op == "argmax" else EXP_EPI, impl=impl)
+            t_total += time.perf_counter() - t0
+            done_bytes += nbytes
+            n += 1
+            if t_total >= budget_s:
+                break
+    return done_bytes / 1e9, t_total, (f"{n} case runs cycling through the 12 cases on A[8192,8192] (eager chain: mul, add, reduce, exp), "
+                                       f"{t_total:.1f} s of CPU work, {threads} OpenMP threads"), kind
 
-    def __init__(self, only="", bare=False):
-        self.only = set(filter(None, only.split(",")))
-        self.bare = bare
-        self.desc = SWEEP_DESC + (" [diagnostic run: prologue and epilogue left out]" if bare else "")
 
-    def setup(self, dev, rank):
-        import torch
-        from pequegrad_b200 import _lib as L
-        from pequegrad_b200 import kernels as K
-        # per-rank synthetic tensors (rank-seeded; rank 0 uses the configured seed 2)
-        g = torch.Generator(device=dev).manual_seed(2 + rank)
-        only, T = self.only, {}
-        if not only or "A" in only:
-            T["A"] = torch.randn(SHAPES["A"], generator=g, device=dev)
-        if not only or only & {"B", "Bp"}:
-            T["B"] = torch.randn(SHAPES["B"], generator=g, device=dev)
-            T["Bp"] = T["B"].permute(0, 2, 1)
-        self.T = T
-        self.cases = [c for c in sweep_cases() if not only or c[0] in only]
-        opcode = {"sum": L.SUM, "max": L.MAX, "mean": L.MEAN, "argmax": L.ARGMAX}
-        self.prepared = []
-        for name, op, ax, nbytes in self.cases:
-            if self.bare:
-                pr = K.PreparedReduce([T[name]], opcode[op], [ax], False)
-            else:
-                pr = K.PreparedReduce([T[name]], opcode[op], [ax], False, AFFINE, () if op == "argmax" else EXP_EPI)
-            self.prepared.append((name, op, ax, nbytes, pr))
-        self.bytes_per_step = sum(c[3] for c in self.cases)
-        self.units_per_step = self.bytes_per_step / 1e9
-        self.stream = torch.cuda.current_stream().cuda_stream
-        self.config = {"cases": len(self.cases), "bytes_per_step": self.bytes_per_step,
-                       "l2": "inputs (268 MB and 1074 MB) are larger than the 126 MB L2; consecutive launches alternate tensors"}
+def cpu_sample_mlp(budget_s, threads):
+    """The int8 pipeline of the CPU restatement on blocks of 2048 rows."""
+    import oracle
+    from pequegrad_b200.workloads import MLP_DIMS, mlp_weights
+    Ws, bs = mlp_weights()
+    prep = [oracle.quantize_weight_per_channel(W) for W in Ws]
+    rng = np.random.default_rng(2)
+    rows, t_total = 0, 0.0
+    while t_total < budget_s:
+        h = rng.random((2048, MLP_DIMS[0]), dtype=np.float32)
+        t0 = time.perf_counter()
+        for i in range(3):
+            sx = oracle.quant_scale(oracle.absmax(h))
+            h = oracle.dequant_bias_act(oracle.gemm_i8(oracle.quantize_i8(h, sx), prep[i][0]), prep[i][1], sx, bs[i], relu=i < 2)
+        t_total += time.perf_counter() - t0
+        rows += 2048
+    return rows, t_total, f"{rows} rows in blocks of 2048 through the 3-layer int8 pipeline, {t_total:.1f} s of CPU work, {threads} threads", "port"
 
-    def step(self):
-        for *_, pr in self.prepared:
-            pr(self.stream)
 
-    def e2e_setup(self):
-        import torch
-        self.host_in = {k: torch.empty(SHAPES[k], dtype=torch.float32).pin_memory() for k in ("A", "B") if k in self.T}
-        for k in self.host_in:
-            self.host_in[k].copy_(self.T[k])
-        self.host_out = [torch.empty(pr.out.shape, dtype=pr.out.dtype).pin_memory() for *_, pr in self.prepared]
-        self.h2d = sum(v.numel() * 4 for v in self.host_in.values())
-        self.d2h = sum(o.numel() * o.element_size() for o in self.host_out)
+def cpu_sample_gpt2(budget_s, threads):
+    """The fp32 CPU restatement of the model on sequences of 256 tokens."""
+    import torch
+    from pequegrad_b200 import gpt2 as G
+    torch.set_num_threads(threads)
+    cfg = G.GPT2Config()
+    weights = _CACHE.setdefault("gpt2_w", G.init_weights(cfg, seed=5))
+    rounded = _CACHE.setdefault("gpt2_r", G.round_weights_fp16(weights))
+    rng = np.random.default_rng(2)
+    toks, t_total = 0, 0.0
+    while t_total < budget_s:
+        idx = rng.integers(0, cfg.vocab_size, (1, 256)).astype(np.int32)
+        t0 = time.perf_counter()
+        G.reference_forward(cfg, weights, idx, rounded)
+        t_total += time.perf_counter() - t0
+        toks += 256
+    return toks, t_total, f"{toks} tokens as sequences of 256 through the fp32 CPU restatement of the model, {t_total:.1f} s, {threads} threads", "port"
 
-    def e2e_step(self):
-        for k, v in self.host_in.items():
-            self.T[k].copy_(v, non_blocking=True)
-        self.step()
-        for o, (*_, pr) in zip(self.host_out, self.prepared):
-            o.copy_(pr.out, non_blocking=True)
 
-    def roofline(self, pk, reps):
-        """Per-case device time (CUDA events around each launch), grouped by kernel family."""
-        import torch
-        prepared, per_case = self.prepared, []
-        for name, op, ax, nbytes, pr in prepared:
-            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
-            for a, b in evs:
-                # touch the other big tensor first so nothing of this case's input is left in L2
-                other = prepared[0][4] if name != prepared[0][0] else prepared[min(1, len(prepared) - 1)][4]
-                other(self.stream)
-                a.record()
-                pr(self.stream)
-                b.record()
-            torch.cuda.synchronize()
-            t = statistics.median(a.elapsed_time(b) for a, b in evs)
-            per_case.append({"case": f"{name}.{op}.ax{ax}", "us": round(t * 1e3, 2), "gbs": round(nbytes / t / 1e6, 1),
-                             "kernel": pr.plan.split()[0], "bytes": nbytes})
-        self.per_case = per_case
-        fam = {}
-        for c in per_case:
-            f = fam.setdefault(c["kernel"], {"us": 0.0, "bytes": 0, "launches": 0})
-            f["us"] += c["us"]
-            f["bytes"] += c["bytes"]
-            f["launches"] += 1
-        dom = max(fam, key=lambda k: fam[k]["us"])
-        achieved = fam[dom]["bytes"] / (fam[dom]["us"] * 1e-6) / 1e9
-        return {"bound": "hbm", "kernel": f"reduce_{dom}_kernel", "achieved": round(achieved, 1), "peak": pk["hbm"], "unit": "GB/s",
-                "frac": round(achieved / pk["hbm"], 4), "peak_source": pk["source"],
-                "traffic": NCU_TRAFFIC_PER_LAUNCH.get(dom) if not self.only and not self.bare else None,
-                "algorithmic_bytes_per_launch": int(fam[dom]["bytes"] / fam[dom]["launches"]),
-                "launches_timed": fam[dom]["launches"],
-                "families": {k: {"gbs": round(v["bytes"] / (v["us"] * 1e-6) / 1e9, 1), "launches": v["launches"]} for k, v in fam.items()}}
+def cpu_sample_rows(budget_s, threads):
+    """The CPU restatement of both row kernels on slices of the same tensors."""
+    import oracle
+    rng = np.random.default_rng(2)
+    S = rng.standard_normal((2, 1024, 1024)).astype(np.float16)
+    X = rng.standard_normal((4096, 768)).astype(np.float32)
+    gm, bt = np.ones(768, np.float32), np.zeros(768, np.float32)
+    done, t_total = 0.0, 0.0
+    while t_total < budget_s:
+        t0 = time.perf_counter()
+        oracle.softmax_rows(S, causal=True)
+        oracle.layernorm_rows(X, gm, bt, 1e-5)
+        t_total += time.perf_counter() - t0
+        done += (S.size * 4 + X.size * 8) / 1e9
+    return done, t_total, f"softmax over [2,1024,1024] fp16 + LayerNorm over [4096,768] fp32, repeated for {t_total:.1f} s, {threads} threads", "port"
 
-    def cpu_sample(self, budget_s, threads):
-        """The reference CPU backend's eager chain (2 binary kernels, per-axis reduce, exp) on cases of the
-        sweep until `budget_s` is spent. Returns (units, seconds, sample description, kind)."""
-        import oracle
-        from oracle.chain import fused_reduce_oracle
-        kind = "reference" if oracle.have_ref() else "port"
-        impl = "ref" if kind == "reference" else "port"
-        A = np.random.default_rng(2).standard_normal(SHAPES["A"], dtype=np.float32)
-        done_bytes, t_total, n = 0, 0.0, 0
-        a_cases = [c for c in sweep_cases() if c[0] == "A"]
-        while t_total < budget_s:
-            for name, op, ax, nbytes in a_cases:
-                t0 = time.perf_counter()
-                fused_reduce_oracle([A], op, [ax], False, AFFINE, () if op == "argmax" else EXP_EPI, impl=impl)
-                t_total += time.perf_counter() - t0
-                done_bytes += nbytes
-                n += 1
-                if t_total >= budget_s:
-                    break
-        return done_bytes / 1e9, t_total, (f"{n} case runs cycling through the 12 cases on A[8192,8192] (eager chain: mul, add, reduce, exp), "
-                                           f"{t_total:.1f} s of CPU work, {threads} OpenMP threads"), kind
+
+def cpu_sample_readme(budget_s, threads):
+    """The README case on the reference's CPU backend, eager (what BASELINE's first config names): permute is a view,
+    two binary kernels, the axis reduce, one more binary kernel. Units = calls."""
+    import oracle
+    from oracle.chain import fused_reduce_oracle
+    from pequegrad_b200.workloads import README_EPI, README_PRO
+    kind = "reference" if oracle.have_ref() else "port"
+    rng = np.random.default_rng(1)
+    x = rng.random((1000, 20, 100), dtype=np.float32).transpose(0, 2, 1)
+    y = rng.random((1000, 100, 20), dtype=np.float32)
+    calls, t_total = 0, 0.0
+    while t_total < budget_s:
+        t0 = time.perf_counter()
+        fused_reduce_oracle([x, y], "sum", [2], False, README_PRO, README_EPI, impl="ref" if kind == "reference" else "port")
+        t_total += time.perf_counter() - t0
+        calls += 1
+    return calls, t_total, f"{calls} calls of the eager chain on the full-size case, {t_total:.1f} s, {threads} OpenMP threads", kind
+
+
+_CACHE: dict = {}
+CPU_SAMPLES = {"sweep": cpu_sample_sweep, "mlp": cpu_sample_mlp, "gpt2": cpu_sample_gpt2, "rows": cpu_sample_rows, "readme": cpu_sample_readme}
+
+
+def cpu_value(name, units, seconds):
+    """The workload's metric from a CPU sample (the README case reports microseconds per call, the others a rate)."""
+    return seconds / units * 1e6 if name == "readme" else units / seconds
+
+
+def reference_cuda_leg(wl, reps=10):
+    """Times of the reference's own CUDA kernels on this GPU for the same case (the comparator named in the baseline
+    notes): the eager chain mul -> add -> reduce -> exp on A for the sweep, the generated kernel for the README
+    case. None where that library was not built (it needs the reference checkout at build time)."""
+    from oracle import ref_cuda
+    if not ref_cuda.available() or wl.world != 1:
+        return None
+    import torch
+    from pequegrad_b200.workloads import SHAPES, _event_us, _L2Flush
+    dev = wl.dev
+    if wl.name == "readme":
+        x, y = wl.pairs[0]
+        out = torch.empty((1000, 100), dtype=torch.float32, device=dev)
+        ring = [lambda p=p: ref_cuda.readme_kernel(p[0], p[1], out) for p in wl.pairs]
+        state = {"i": 0}
+
+        def cold():
+            state["i"] = (state["i"] + 1) % len(ring)
+            ring[state["i"]]()
+        warm_us = _event_us(ring[0], 20)
+        cold_us = _event_us(cold, 20)
+        ok = bool(torch.allclose(ref_cuda.readme_kernel(x, y), wl.calls[0](), rtol=1e-5, atol=1e-4))
+        return {"kernel": "the generated reduce_kernel printed in the reference's README, recompiled for sm_100a, its launch geometry",
+                "warm_us": round(warm_us, 2), "cold_us": round(cold_us, 2), "matches_pgb": ok, "published_us_on_the_authors_gpu": 272.85}
+    if wl.name != "sweep" or "A0" not in wl.S:
+        return None
+    A = wl.S["A0"]
+    flush = _L2Flush(dev)
+    res = {}
+    total_ref = total_pgb = 0.0
+    by_case = {(n, o, a): pr for n, o, a, _, pr in wl.prepared}
+    for ax in (0, 1):
+        for op in ("sum", "max", "mean"):
+            chain = ref_cuda.EagerReduceChain(A, op, [ax])
+            chain()
+            us = _event_us(chain, reps, flush)
+            pgb = by_case[("A", op, ax)]
+            pus = _event_us(lambda: pgb(wl.stream), reps, flush)
+            got, want = pgb(wl.stream), chain()
+            both_inf = torch.isinf(got) & torch.isinf(want)
+            ok = bool(torch.allclose(torch.where(both_inf, 0, got), torch.where(both_inf, 0, want), rtol=1e-4 if op != "max" else 0, atol=0))
+            res[f"A.{op}.ax{ax}"] = {"reference_cuda_us": round(us, 1), "pgb_us": round(pus, 1), "speedup": round(us / pus, 1), "matches_pgb": ok}
+            total_ref += us
+            total_pgb += pus
+            del chain
+    del flush
+    return {"kernels": "the reference's eager chain on A[8192,8192]: mult_kernel, add_kernel, sum/max/mean_kernel, exp_kernel_dense "
+                       "(csrc/cuda), its launch geometry, metadata uploaded once", "cases": res,
+            "total_reference_cuda_us": round(total_ref, 1), "total_pgb_us": round(total_pgb, 1), "speedup": round(total_ref / total_pgb, 1)}
 
 
 def make_workload(args):
     from pequegrad_b200 import workloads as W
     if args.workload == "sweep":
-        return Sweep(args.only, args.bare)
+        return W.Sweep(args.only, args.bare)
     if args.workload == "mlp":
         return W.Mlp(args.rows or W.MLP_ROWS)
     if args.workload == "gpt2":
         return W.Gpt2(args.batch or W.GPT2_BATCH, args.seq or W.GPT2_T)
+    if args.workload == "readme":
+        return W.Readme()
     return W.Rows()
 
 
@@ -267,16 +300,17 @@ def run_reference(args, rank: int):
         return
     threads = host_threads()
     wl = make_workload(args)
-    wl.cpu_sample(0.5, threads)
+    sample_fn = CPU_SAMPLES[wl.name]
+    sample_fn(0.5, threads)
     vals, ms, sample, kind = [], [], "", "port"
     for _ in range(max(1, min(args.steps, 3))):
-        u, t, sample, kind = wl.cpu_sample(6.0, threads)
-        vals.append(u / t)
+        u, t, sample, kind = sample_fn(6.0, threads)
+        vals.append(cpu_value(wl.name, u, t))
         ms.append(t * 1e3)
     v = statistics.median(vals)
     print(json.dumps({
         "impl": "reference", "metric": wl.metric, "value": v, "unit": wl.unit, "n_gpus": args.gpus, "steps": len(vals),
-        "warmup": 1, "ms_per_step": statistics.median(ms), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "warmup": 1, "ms_per_step": statistics.median(ms), "higher_is_better": wl.name != "readme", "scaling": "strong", "vs_baseline": None,
         "dtype": wl.dtype, "data": "synthetic", "config": {"workload": wl.desc, "sample": sample},
         "cpu_baseline": {"value": v, "unit": wl.unit, "cores": threads, "kind": kind, "sample": sample},
         "e2e": {"value": v, "unit": wl.unit, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
@@ -298,22 +332,40 @@ def timed_steps(fn, n, barrier, nvtx="pgb_other"):
     return e0.elapsed_time(e1)
 
 
-def quick_other(name, dev, rank, pk, barrier):
-    """A short measurement of one of the non-headline workloads for the `other_workloads` report."""
+def max_over_ranks(vals, dev, world):
+    import torch
+    import torch.distributed as dist
+    t = torch.tensor(vals, device=dev, dtype=torch.float64)
+    if world > 1:
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+    return [float(v) for v in t]
+
+
+def quick_other(name, dev, rank, world, pk, barrier):
+    """A short measurement of one of the non-headline workloads for the `other_workloads` report: the same fixed
+    problem split over the ranks, device time as the max over ranks, with and without the final gather."""
     import torch
     from pequegrad_b200 import workloads as W
-    wl = {"mlp": W.Mlp, "gpt2": W.Gpt2, "rows": W.Rows}[name]()
-    wl.setup(dev, rank)
+    wl = {"mlp": W.Mlp, "gpt2": W.Gpt2, "rows": W.Rows, "readme": W.Readme}[name]()
+    wl.setup(dev, rank, world)
     for _ in range(3):
         wl.step()
     n = 5
     ms = timed_steps(wl.step, n, barrier) / n
-    rf = wl.roofline(pk, 5)
-    out = {"metric": wl.metric, "per_gpu_value": round(wl.units_per_step / (ms * 1e-3), 1), "unit": wl.unit, "ms_per_step": round(ms, 4), "roofline": rf}
+    ms_c = timed_steps(wl.step_compute, n, barrier) / n
+    ms, ms_c = max_over_ranks([ms, ms_c], dev, world)
+    rf = wl.roofline(pk, 5) if rank == 0 else None
+    barrier()
+    if name == "readme":
+        out = {"metric": wl.metric, "value": round(ms * 1e3, 2), "unit": wl.unit, "ms_per_step": round(ms, 5), "roofline": rf}
+    else:
+        out = {"metric": wl.metric, "value": round(wl.units_per_step / (ms * 1e-3), 1), "unit": wl.unit, "ms_per_step": round(ms, 4),
+               "compute_only": {"value": round(wl.units_per_step / (ms_c * 1e-3), 1), "ms_per_step": round(ms_c, 4)},
+               "n_gpus": world, "scaling": "strong", "timing": "max over ranks", "roofline": rf}
     if name == "gpt2":
-        out["model_tflops"] = round(wl.flops_per_token * wl.units_per_step / (ms * 1e-3) / 1e12, 1)
+        out["model_tflops_per_gpu"] = round(wl.flops_per_token * wl.units_per_step / world / (ms * 1e-3) / 1e12, 1)
     if name == "mlp":
-        out["model_tops"] = round(wl.ops_per_row * wl.units_per_step / (ms * 1e-3) / 1e12, 1)
+        out["model_tops_per_gpu"] = round(wl.ops_per_row * wl.units_per_step / world / (ms * 1e-3) / 1e12, 1)
     del wl
     torch.cuda.empty_cache()
     return out
@@ -325,13 +377,13 @@ def main():
     ap.add_argument("--steps", type=int, default=10)
     ap.add_argument("--warmup", type=int, default=3)
     ap.add_argument("--impl", default="pgb200", choices=["pgb200", "reference"])
-    ap.add_argument("--workload", default="sweep", choices=["sweep", "mlp", "gpt2", "rows"])
+    ap.add_argument("--workload", default="sweep", choices=["sweep", "mlp", "gpt2", "rows", "readme"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-others", action="store_true", help="sweep only: skip the short runs of the other workloads")
     ap.add_argument("--only", default="", help="sweep: comma-separated tensor names (A,B,Bp) to restrict the sweep, for profiling")
     ap.add_argument("--bare", action="store_true", help="sweep diagnostic: no prologue / epilogue (not the benchmark workload)")
-    ap.add_argument("--rows", type=int, default=0, help="mlp: rows per GPU (default 65536; smaller for profiling)")
-    ap.add_argument("--batch", type=int, default=0, help="gpt2: sequences per GPU (default 32; smaller for profiling)")
+    ap.add_argument("--rows", type=int, default=0, help="mlp: rows in total (default 65536; smaller for profiling)")
+    ap.add_argument("--batch", type=int, default=0, help="gpt2: sequences in total (default 32; smaller for profiling)")
     ap.add_argument("--seq", type=int, default=0, help="gpt2: tokens per sequence (default 1024)")
     ap.add_argument("--cases-out", default="", help="sweep: write the per-case timings to this JSON file")
     args = ap.parse_args()
@@ -346,6 +398,7 @@ def main():
     import torch
     import torch.distributed as dist
     from pequegrad_b200 import _lib as L
+    from pequegrad_b200 import distrib as D
     from pequegrad_b200 import kernels as K
 
     if not torch.cuda.is_available():
@@ -353,7 +406,7 @@ def main():
     torch.cuda.set_device(local_rank)
     dev = torch.device("cuda", local_rank)
     if world > 1:
-        dist.init_process_group("nccl", device_id=dev)
+        D.init("nccl")
 
     def barrier():
         if world > 1:
@@ -362,7 +415,7 @@ def main():
 
     pk = peaks()
     wl = make_workload(args)
-    wl.setup(dev, rank)
+    wl.setup(dev, rank, world)
     for _ in range(args.warmup):
         wl.step()
     barrier()
@@ -372,7 +425,9 @@ def main():
     launches0 = L.lib().pgb_launch_count()
     ms_total = timed_steps(wl.step, args.steps, barrier, nvtx="pgb_timed")
     launches = L.lib().pgb_launch_count() - launches0
-    roofline = wl.roofline(pk, max(5, min(args.steps, 20)))  # per-kernel device times, still under the clock sampler
+    ms_compute = timed_steps(wl.step_compute, args.steps, barrier)
+    roofline = wl.roofline(pk, max(5, min(args.steps, 20))) if rank == 0 else None  # per-kernel device times, still under the clock sampler
+    barrier()
     clocks = sampler.stop()
 
     # end to end through the public call: pinned host inputs -> device, the step, results -> host
@@ -384,50 +439,63 @@ def main():
     if err:
         raise SystemExit(f"a GEMM kernel reported device error {err} (a bounded wait ran out)")
 
-    ms = torch.tensor([ms_total, e2e_ms], device=dev, dtype=torch.float64)
-    if world > 1:
-        dist.all_reduce(ms, op=dist.ReduceOp.MAX)
-    ms_total, e2e_ms = float(ms[0]), float(ms[1])
+    ms_total, ms_compute, e2e_ms, h2d = max_over_ranks([ms_total, ms_compute, e2e_ms, float(wl.h2d)], dev, world)
     ms_per_step = ms_total / args.steps
-    value = world * wl.units_per_step / (ms_per_step * 1e-3)
-    e2e_value = world * wl.units_per_step / (e2e_ms * 1e-3)
+    ms_compute /= args.steps
+    latency = wl.name == "readme"  # a time per call, not a rate
+    value = ms_per_step * 1e3 if latency else wl.units_per_step / (ms_per_step * 1e-3)
+    e2e_value = e2e_ms * 1e3 if latency else wl.units_per_step / (e2e_ms * 1e-3)
+
+    ref_cuda = None
+    if rank == 0 and world == 1 and wl.name in ("sweep", "readme") and not args.only and not args.bare:
+        ref_cuda = reference_cuda_leg(wl)
 
     others = None
     if args.workload == "sweep" and not args.no_others and not args.only and not args.bare:
-        del wl.T, wl.prepared
+        per_case = getattr(wl, "per_case", None)
+        del wl.S, wl.prepared, wl.buckets, wl.copies, wl.slots
         torch.cuda.empty_cache()
-        others = {n: quick_other(n, dev, rank, pk, barrier) for n in ("rows", "mlp", "gpt2")}
+        others = {n: quick_other(n, dev, rank, world, pk, barrier) for n in ("rows", "mlp", "gpt2") + (("readme",) if world == 1 else ())}
+        wl.per_case = per_case
 
     if rank == 0:
         cpu = None
         if not args.no_cpu_baseline:
             threads = host_threads()
-            u, t, sample, kind = wl.cpu_sample(10.0, threads)
-            cpu = {"value": round(u / t, 3), "unit": wl.unit, "cores": threads, "kind": kind, "sample": sample}
+            u, t, sample, kind = CPU_SAMPLES[wl.name](10.0, threads)
+            cpu = {"value": round(cpu_value(wl.name, u, t), 3), "unit": wl.unit, "cores": threads, "kind": kind, "sample": sample}
         line = {
-            "metric": wl.metric, "value": round(value, 1), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
-            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 4), "higher_is_better": True, "scaling": "weak",
-            "vs_baseline": None, "dtype": wl.dtype, "data": "synthetic",
-            "config": dict({"workload": wl.desc}, **wl.config),
+            "metric": wl.metric, "value": round(value, 2 if latency else 1), "unit": wl.unit, "n_gpus": world, "steps": args.steps,
+            "warmup": args.warmup, "ms_per_step": round(ms_per_step, 5), "higher_is_better": not latency, "scaling": "strong",
+            "vs_baseline": round(value / 272.85, 4) if latency else None, "dtype": wl.dtype, "data": "synthetic",
+            "config": dict({"workload": wl.desc, "parallelism": f"dp{world}: one fixed problem split over the GPUs, final all-gather inside the timed region"},
+                           **wl.config),
             "clocks": clocks,
-            "e2e": {"value": round(e2e_value, 2), "unit": wl.unit, "h2d_bytes_per_step": wl.h2d, "d2h_bytes_per_step": wl.d2h,
-                    "ms_per_step": round(e2e_ms, 3)},
+            "compute_only": {"value": round(ms_compute * 1e3 if latency else wl.units_per_step / (ms_compute * 1e-3), 2 if latency else 1),
+                             "unit": wl.unit, "ms_per_step": round(ms_compute, 5), "what": "the same steps without the final gather"},
+            "e2e": {"value": round(e2e_value, 2), "unit": wl.unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": wl.d2h,
+                    "ms_per_step": round(e2e_ms, 4),
+                    "what": "pinned host inputs copied to every rank's shards, the step with its gather, the result read back by rank 0; "
+                            "h2d bytes are the sum over ranks"},
             "gpu_launches": int(launches),
             "roofline": roofline,
             "cpu_baseline": cpu,
         }
+        if ref_cuda is not None:
+            line["reference_cuda"] = ref_cuda
         if args.workload == "sweep":
-            line["frac_of_peak"] = round(value / world / pk["hbm"], 4)
+            line["frac_of_peak_per_gpu"] = round(value / world / pk["hbm"], 4)
         if args.workload == "gpt2":
-            line["model_tflops_per_gpu"] = round(wl.flops_per_token * wl.units_per_step / (ms_per_step * 1e-3) / 1e12, 1)
+            line["model_tflops_per_gpu"] = round(wl.flops_per_token * wl.units_per_step / world / (ms_per_step * 1e-3) / 1e12, 1)
         if args.workload == "mlp":
-            line["model_tops_per_gpu"] = round(wl.ops_per_row * wl.units_per_step / (ms_per_step * 1e-3) / 1e12, 1)
+            line["model_tops_per_gpu"] = round(wl.ops_per_row * wl.units_per_step / world / (ms_per_step * 1e-3) / 1e12, 1)
         if others is not None:
             line["other_workloads"] = others
         print(json.dumps(line))
         if args.cases_out and args.workload == "sweep":
             Path(args.cases_out).write_text(json.dumps(wl.per_case, indent=1))
     if world > 1:
+        barrier()
         dist.destroy_process_group()
 
 

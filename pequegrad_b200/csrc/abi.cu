@@ -105,6 +105,22 @@ static int plan_and_launch(ReduceJob &j) {
   return r == 1 ? PGB_OK : (r == 0 ? PGB_ERR_UNSUPPORTED : r);
 }
 
+int fused_reduce_run(const pgb_tensor *in, int n_in, const pgb_tensor *out, int reduce_op, const int32_t *axes, int n_axes,
+                     const pgb_instr *prologue, int n_pro, const pgb_tensor *epi_in, int n_epi_in, const pgb_instr *epilogue, int n_epi,
+                     void *workspace, size_t workspace_bytes, void *stream, bool no_alloc) {
+  g_last_error.clear();
+  ReduceJob j;
+  int st = build_reduce_job(j, in, n_in, out, reduce_op, axes, n_axes, prologue, n_pro, epi_in, n_epi_in, epilogue, n_epi);
+  if (st != PGB_OK) return st;
+  if (!device_ok()) return PGB_ERR_CUDA;
+  j.workspace = workspace;
+  j.workspace_bytes = workspace_bytes;
+  j.stream = (cudaStream_t)stream;
+  j.dry_run = false;
+  j.no_alloc = no_alloc;
+  return plan_and_launch(j);
+}
+
 }  // namespace pgb
 
 using namespace pgb;
@@ -151,16 +167,8 @@ int pgb_fused_elementwise(const pgb_tensor *in, int n_in, const pgb_tensor *out,
 int pgb_fused_reduce(const pgb_tensor *in, int n_in, const pgb_tensor *out, int reduce_op, const int32_t *axes, int n_axes,
                      const pgb_instr *prologue, int n_pro, const pgb_tensor *epi_in, int n_epi_in, const pgb_instr *epilogue, int n_epi,
                      void *workspace, size_t workspace_bytes, void *stream) {
-  g_last_error.clear();
-  ReduceJob j;
-  int st = build_reduce_job(j, in, n_in, out, reduce_op, axes, n_axes, prologue, n_pro, epi_in, n_epi_in, epilogue, n_epi);
-  if (st != PGB_OK) return st;
-  if (!device_ok()) return PGB_ERR_CUDA;
-  j.workspace = workspace;
-  j.workspace_bytes = workspace_bytes;
-  j.stream = (cudaStream_t)stream;
-  j.dry_run = false;
-  return plan_and_launch(j);
+  return fused_reduce_run(in, n_in, out, reduce_op, axes, n_axes, prologue, n_pro, epi_in, n_epi_in, epilogue, n_epi, workspace,
+                          workspace_bytes, stream, false);
 }
 
 int pgb_fused_reduce_workspace(const pgb_tensor *in, int n_in, const pgb_tensor *out, int reduce_op, const int32_t *axes, int n_axes,

@@ -22,6 +22,7 @@ struct ReduceJob {
   void *workspace; size_t workspace_bytes;
   cudaStream_t stream;
   bool dry_run;        // plan only: fill `desc` / `ws_needed`, launch nothing
+  bool no_alloc = false;  // a split reduction without a caller workspace is refused instead of allocating one
   std::string desc;
   size_t ws_needed = 0;
 };
@@ -83,6 +84,10 @@ template <typename T>
 std::string make_epi(const ReduceJob &j, EpiParams<T> &e);
 
 // Each returns: 1 launched (or planned), 0 not applicable, <0 pgb_status error.
+// The body of pgb_fused_reduce; `no_alloc` makes a split reduction without a workspace fail instead of allocating.
+int fused_reduce_run(const pgb_tensor *in, int n_in, const pgb_tensor *out, int reduce_op, const int32_t *axes, int n_axes,
+                     const pgb_instr *prologue, int n_pro, const pgb_tensor *epi_in, int n_epi_in, const pgb_instr *epilogue, int n_epi,
+                     void *workspace, size_t workspace_bytes, void *stream, bool no_alloc);
 int launch_reduce_row(ReduceJob &j);
 int launch_reduce_col(ReduceJob &j);
 int launch_reduce_generic(ReduceJob &j);

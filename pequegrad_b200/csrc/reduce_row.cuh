@@ -235,6 +235,9 @@ int launch_row_typed(ReduceJob &j, bool ident, const ChainProg<float> &chain) {
     if (j.workspace) {
       if (j.workspace_bytes < ws) { set_error("fused_reduce: workspace too small"); return PGB_ERR_WORKSPACE; }
       ws_ptr = j.workspace;
+    } else if (j.no_alloc) {
+      set_error("fused_reduce: this call may not allocate and was given no workspace for its partial results");
+      return PGB_ERR_WORKSPACE;
     } else {
       if (cudaMallocAsync(&ws_ptr, ws, j.stream) != cudaSuccess) { set_error("fused_reduce: workspace allocation failed"); return PGB_ERR_CUDA; }
       own_ws = true;

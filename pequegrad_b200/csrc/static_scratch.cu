@@ -72,6 +72,9 @@ extern "C" PGB_API int pgb_fused_reduce_noalloc(const pgb_tensor *in, int n_in, 
   }
   // Nothing in the scratch has to start at zero: the first kernel writes every
   // partial result before the second one reads it.
-  return pgb_fused_reduce(in, n_in, out, reduce_op, axes, n_axes, prologue, n_pro, epi_in, n_epi_in, epilogue, n_epi, scratch,
-                          need > 0 ? (size_t)PGB_NOALLOC_SCRATCH_BYTES : 0, stream);
+  // `need` was planned without the prologue. That is the size the launch uses: how a reduction is split depends on
+  // shapes and strides alone, and a prologue the fast kernels cannot take moves the call to the generic kernel, which
+  // needs no scratch. Should the two ever disagree, the launch below is told not to allocate and refuses instead.
+  return pgb::fused_reduce_run(in, n_in, out, reduce_op, axes, n_axes, prologue, n_pro, epi_in, n_epi_in, epilogue, n_epi, scratch,
+                               need > 0 ? (size_t)PGB_NOALLOC_SCRATCH_BYTES : 0, stream, /*no_alloc=*/true);
 }

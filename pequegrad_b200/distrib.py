@@ -1,19 +1,31 @@
-"""Batch / row sharding over the GPUs of one box: one process per GPU.
+"""Batch / row sharding over the GPUs of one box.
 
-Keeps the API shape of the reference's `pequegrad/distrib`
-(`shard_tensor`, `unshard_tensor`, `ShardedTensor`, `all_reduce`,
-pequegrad/distrib/sharded_tensor.py:7-95, distrib/__init__.py:4-62) and of
-`pmap` (pequegrad/transforms/distrib.py:31-163). The reference emulates its
-devices on one GPU and moves data with Python loops; here every rank owns a
-real device, computes on its shard with no exchange, and the only collective
-on the data path is the final gather (NCCL over NVLink on GPUs, gloo in the
-CPU tests). Shards may be uneven: rank r owns rows [r*n//W, (r+1)*n//W).
+The API is the reference's `pequegrad/distrib` and `pmap`
+(pequegrad/distrib/sharded_tensor.py:7-95, distrib/__init__.py:4-62,
+pequegrad/transforms/distrib.py:31-163):
+
+    shard_tensor(x, num_shards, dim, devices) -> ShardedTensor
+    unshard_tensor(x, dim, dev)                -> tensor
+    pmap(f, devices, argnum_opts)              -> callable
+    all_reduce(tensors, op)                    -> tensor
+
+The reference emulates its devices on one GPU and runs them one after another
+in Python. Here the shards are spread over processes, one process per GPU
+(`torchrun`, `torch.distributed`): with W processes and S shards (S a multiple
+of W) process r owns shards [r*S/W, (r+1)*S/W). W == S is the production
+layout (one shard per GPU); W == 1 holds every shard on the one device, which
+is what the reference's emulated devices do and what lets the same code run
+and be tested on a single GPU. Every rank computes on its own shards with no
+exchange; the only collective on the data path is the final gather
+(`unshard_tensor`, an NCCL all-gather over NVLink; gloo in the CPU tests),
+plus `all_reduce` for callers that shard a reduced quantity (the int8 MLP's
+per-tensor activation absmax).
 """
 from __future__ import annotations
 
 import datetime
 import os
-from typing import Callable, Sequence
+from typing import Callable, List, Sequence
 
 import torch
 import torch.distributed as dist
@@ -24,9 +36,12 @@ def init(backend: str | None = None, timeout_s: float = 600.0) -> tuple[int, int
     if not dist.is_initialized():
         if backend is None:
             backend = "nccl" if torch.cuda.is_available() else "gloo"
+        kw = {}
         if backend == "nccl":
-            torch.cuda.set_device(int(os.environ.get("LOCAL_RANK", "0")))
-        dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_s))
+            local = int(os.environ.get("LOCAL_RANK", "0"))
+            torch.cuda.set_device(local)
+            kw["device_id"] = torch.device("cuda", local)
+        dist.init_process_group(backend, timeout=datetime.timedelta(seconds=timeout_s), **kw)
     return dist.get_rank(), dist.get_world_size()
 
 
@@ -36,90 +51,307 @@ def rank_world() -> tuple[int, int]:
     return 0, 1
 
 
-def shard_range(n: int, rank: int, world: int) -> tuple[int, int]:
-    """Half-open row range of `rank` when n rows are split over `world` ranks."""
-    return rank * n // world, (rank + 1) * n // world
+def default_devices(num_shards: int | None = None) -> List[str]:
+    """One name per shard. Every process computes on its current CUDA device (or the CPU in the gloo tests);
+    the names only say how many shards there are, as the reference's emulated `cuda:i` aliases do."""
+    _, world = rank_world()
+    n = world if num_shards is None else num_shards
+    kind = "cuda" if torch.cuda.is_available() else "cpu"
+    return [f"{kind}:{i}" for i in range(n)]
+
+
+def shard_range(n: int, index: int, num_shards: int) -> tuple[int, int]:
+    """Half-open range of shard `index` when n rows are split into `num_shards` (uneven splits allowed)."""
+    return index * n // num_shards, (index + 1) * n // num_shards
+
+
+def local_shards(num_shards: int) -> range:
+    """Indices of the shards this process owns."""
+    rank, world = rank_world()
+    if num_shards % world:
+        raise ValueError(f"{num_shards} shards cannot be spread evenly over {world} processes")
+    per = num_shards // world
+    return range(rank * per, (rank + 1) * per)
 
 
 class ShardedTensor:
-    """This rank's shard of a tensor split along `dim` (None = replicated)."""
+    """A tensor split along `dim` (a one-element list, as in the reference; None = replicated).
+    `shards` holds the shards this process owns, in shard order."""
 
-    def __init__(self, local: torch.Tensor, dim: int | None, global_shape: Sequence[int]):
-        self.local, self.dim, self.global_shape = local, dim, tuple(global_shape)
+    def __init__(self, shards: List[torch.Tensor], dim: List[int] | None = None, num_shards: int | None = None,
+                 shape: Sequence[int] | None = None):
+        self.shards = list(shards)
+        self.dim = dim
+        self.num_shards = num_shards if num_shards is not None else len(self.shards) * rank_world()[1]
+        if shape is not None:
+            self.shape = list(shape)
+        elif dim is None:
+            self.shape = list(self.shards[0].shape)
+        else:
+            # what the reference computes (sharded_tensor.py:12-21), valid when every shard is held locally
+            self.shape = [sum(s.shape[i] for s in self.shards) if i in dim else self.shards[0].shape[i]
+                          for i in range(self.shards[0].dim())]
 
-    @property
-    def shape(self):
-        return self.global_shape
+    def is_replicated(self) -> bool:
+        return self.dim is None
+
+    def _zip(self, other, fn):
+        if len(self.shards) != len(other.shards):
+            raise ValueError("operands are sharded differently")
+        return ShardedTensor([fn(a, b) for a, b in zip(self.shards, other.shards)], self.dim or other.dim, self.num_shards)
+
+    def __add__(self, o): return self._zip(o, lambda a, b: a + b)
+    def __sub__(self, o): return self._zip(o, lambda a, b: a - b)
+    def __mul__(self, o): return self._zip(o, lambda a, b: a * b)
+    def __truediv__(self, o): return self._zip(o, lambda a, b: a / b)
+    def __neg__(self): return ShardedTensor([-a for a in self.shards], self.dim, self.num_shards, self.shape)
 
     def __matmul__(self, other: "ShardedTensor") -> "ShardedTensor":
-        # 1-D sharded matmul as in the reference (sharded_tensor.py:49-67): one side replicated, the other split
-        # by rows (dim 0 of the left operand) or by columns (last dim of the right operand); no communication.
-        if self.dim == 0 and other.dim is None:
-            out = self.local @ other.local
-            return ShardedTensor(out, 0, (self.global_shape[0], other.global_shape[-1]))
-        if self.dim is None and other.dim == other.local.dim() - 1:
-            out = self.local @ other.local
-            return ShardedTensor(out, out.dim() - 1, tuple(self.global_shape[:-1]) + (other.global_shape[-1],))
-        raise ValueError("sharded matmul needs one replicated operand and one split by rows (left) or columns (right)")
+        # 1-D sharded matmul as in the reference (sharded_tensor.py:49-67): both 2-D, one side replicated; the
+        # result is split the way the non-replicated operand is. No communication.
+        if len(self.shape) != 2 or len(other.shape) != 2 or self.shape[1] != other.shape[0]:
+            raise ValueError(f"sharded matmul needs 2-D operands with matching inner sizes, got {self.shape} and {other.shape}")
+        if not (self.is_replicated() or other.is_replicated()):
+            raise ValueError("one of the tensors must be replicated")
+        dim = other.dim if self.is_replicated() else self.dim
+        if dim is not None and ((self.is_replicated() and dim != [1]) or (other.is_replicated() and dim != [0])):
+            raise ValueError("the left operand may be split by rows or the right operand by columns, nothing else")
+        res = [a @ b for a, b in zip(self.shards, other.shards)]
+        return ShardedTensor(res, dim, self.num_shards, [self.shape[0], other.shape[1]])
+
+    def numpy(self):
+        if self.dim is None:
+            return self.shards[0].cpu().numpy()
+        if len(self.dim) != 1:
+            raise ValueError("only works for 1D sharded tensors")
+        return unshard_tensor(self, self.dim[0]).cpu().numpy()
+
+    def __repr__(self):
+        return f"ShardedTensor(shape={self.shape}, dim={self.dim}, num_shards={self.num_shards}, local={len(self.shards)})"
 
 
-def shard_tensor(x: torch.Tensor, dim: int | None = 0) -> ShardedTensor:
-    """Keep this rank's slice of a tensor every rank holds in full (`dim=None` keeps it replicated)."""
-    rank, world = rank_world()
+def shard_tensor(x: torch.Tensor, num_shards: int, dim: int | None = 0, devices: Sequence | None = None) -> ShardedTensor:
+    """Split a tensor that every process holds in full; each process keeps contiguous copies of its own
+    shards (`dim=None`: every shard is the whole tensor). Signature of sharded_tensor.py:74-88."""
+    if devices is not None and num_shards != len(devices):
+        raise ValueError("num_shards must match the number of devices")
+    mine = local_shards(num_shards)
     if dim is None:
-        return ShardedTensor(x, None, x.shape)
+        return ShardedTensor([x for _ in mine], None, num_shards, x.shape)
     dim = dim + x.dim() if dim < 0 else dim
-    lo, hi = shard_range(x.shape[dim], rank, world)
-    return ShardedTensor(x.narrow(dim, lo, hi - lo), dim, x.shape)
+    if not 0 <= dim < x.dim():
+        raise ValueError(f"cannot shard a {x.dim()}-d tensor along dim {dim}")
+    shards = []
+    for i in mine:
+        lo, hi = shard_range(x.shape[dim], i, num_shards)
+        shards.append(x.narrow(dim, lo, hi - lo).contiguous())
+    return ShardedTensor(shards, [dim], num_shards, x.shape)
 
 
-def unshard_tensor(st: ShardedTensor) -> torch.Tensor:
-    """The final gather: every rank receives the whole tensor (one all-gather; uneven shards are padded)."""
-    rank, world = rank_world()
-    if st.dim is None or world == 1:
-        return st.local
-    n = st.global_shape[st.dim]
-    sizes = [shard_range(n, r, world)[1] - shard_range(n, r, world)[0] for r in range(world)]
-    biggest = max(sizes)
-    loc = st.local.movedim(st.dim, 0).contiguous()
-    if loc.shape[0] < biggest:
-        pad = torch.zeros((biggest - loc.shape[0],) + tuple(loc.shape[1:]), dtype=loc.dtype, device=loc.device)
-        loc = torch.cat([loc, pad], 0)
-    bufs = [torch.empty_like(loc) for _ in range(world)]
-    dist.all_gather(bufs, loc)
-    full = torch.cat([b[:s] for b, s in zip(bufs, sizes)], 0)
-    return full.movedim(0, st.dim).contiguous()
-
-
-def all_reduce(t: torch.Tensor, op: str = "sum") -> torch.Tensor:
-    """In-place all-reduce ("sum", "avg", "max"); needed only when a REDUCED axis is what was sharded."""
+def _gather_rows(local: torch.Tensor, rows_per_rank: List[int]) -> torch.Tensor:
+    """All-gather of per-process row blocks (dim 0) into one contiguous tensor on every process."""
     rank, world = rank_world()
     if world == 1:
-        return t
-    if op == "max":
-        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        return local
+    local = local.contiguous()
+    if len(set(rows_per_rank)) == 1:
+        out = torch.empty((sum(rows_per_rank),) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+        dist.all_gather_into_tensor(out, local)
+        return out
+    # uneven blocks: pad to the largest, gather, drop the padding
+    biggest = max(rows_per_rank)
+    padded = torch.zeros((biggest,) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    padded[:local.shape[0]] = local
+    recv = torch.empty((world, biggest) + tuple(local.shape[1:]), dtype=local.dtype, device=local.device)
+    dist.all_gather_into_tensor(recv.view((world * biggest,) + tuple(local.shape[1:])), padded)
+    return torch.cat([recv[r, :n] for r, n in enumerate(rows_per_rank)], 0)
+
+
+def unshard_tensor(x: ShardedTensor, dim: int | None = 0, dev=None) -> torch.Tensor:
+    """The final gather (sharded_tensor.py:91-97): every process receives the whole tensor, shards
+    concatenated along `dim` (None: the dim it was sharded along). One all-gather; a `dim` other
+    than 0 costs one extra copy on the device, because the gather delivers whole row blocks."""
+    if x.dim is None:
+        return x.shards[0]
+    if dim is None:
+        dim = x.dim[0]
+    nd = x.shards[0].dim()
+    dim = dim + nd if dim < 0 else dim
+    rank, world = rank_world()
+    local = x.shards[0] if len(x.shards) == 1 else torch.cat(x.shards, dim)
+    if world == 1:
+        return local
+    per = x.num_shards // world
+    n = x.shape[dim]
+    sizes = [shard_range(n, (r + 1) * per - 1, x.num_shards)[1] - shard_range(n, r * per, x.num_shards)[0] for r in range(world)]
+    if dim == 0:
+        return _gather_rows(local, sizes)
+    full = _gather_rows(local.movedim(dim, 0).contiguous(), sizes)
+    return full.movedim(0, dim).contiguous()
+
+
+class GatherBucket:
+    """Several sharded outputs gathered by ONE collective. Kernels write their output slabs into views of
+    one flat buffer (`local_view`); `gather()` all-gathers that buffer; `full(i)` is output i assembled
+    from every process. An output whose slabs are concatenated along dim 0 is returned as a view of the
+    receive buffer (strided across processes, no copy); other dims take one permuting copy."""
+
+    ALIGN = 256
+
+    def __init__(self, device, async_op: bool = False):
+        self.device, self.async_op = device, async_op
+        self.specs, self.nbytes = [], 0
+        self.local = self.recv = self.work = None
+
+    def add(self, local_shape: Sequence[int], dtype: torch.dtype, dim: int = 0) -> int:
+        if self.local is not None:
+            raise RuntimeError("GatherBucket: add() after the buffers were allocated")
+        n = 1
+        for s in local_shape:
+            n *= int(s)
+        es = torch.empty((), dtype=dtype).element_size()
+        self.specs.append((self.nbytes, tuple(int(s) for s in local_shape), dtype, dim))
+        self.nbytes += (n * es + self.ALIGN - 1) // self.ALIGN * self.ALIGN
+        return len(self.specs) - 1
+
+    def _alloc(self):
+        if self.local is None:
+            _, world = rank_world()
+            self.local = torch.empty(max(self.nbytes, self.ALIGN), dtype=torch.uint8, device=self.device)
+            self.recv = self.local if world == 1 else torch.empty(world * self.local.numel(), dtype=torch.uint8, device=self.device)
+
+    def local_view(self, i: int) -> torch.Tensor:
+        self._alloc()
+        off, shape, dtype, _ = self.specs[i]
+        n = 1
+        for s in shape:
+            n *= s
+        es = torch.empty((), dtype=dtype).element_size()
+        return self.local[off:off + n * es].view(dtype).view(shape)
+
+    def gather(self):
+        """Enqueue the all-gather of everything written to the local views so far (stream-ordered)."""
+        self._alloc()
+        _, world = rank_world()
+        if world > 1:
+            self.work = dist.all_gather_into_tensor(self.recv, self.local, async_op=self.async_op)
+
+    def wait(self):
+        """Make the current stream wait for an asynchronous gather (no host synchronisation)."""
+        if self.work is not None:
+            self.work.wait()
+            self.work = None
+
+    def full(self, i: int, copy_out: torch.Tensor | None = None, copy_fn: Callable | None = None) -> torch.Tensor:
+        """Output i of every process, concatenated along its dim. `copy_fn(dst_view, src_view)` replaces
+        the torch copy for the outputs that need one (e.g. by a kernel of this library)."""
+        _, world = rank_world()
+        off, shape, dtype, dim = self.specs[i]
+        if world == 1:
+            return self.local_view(i)
+        es = torch.empty((), dtype=dtype).element_size()
+        n = 1
+        for s in shape:
+            n *= s
+        stride0 = self.local.numel() // es
+        base = self.recv.view(dtype)
+        # [world, *shape] view of the receive buffer: process r's slab starts r * (bytes per process) further on
+        inner, acc = [], 1
+        for s in reversed(shape):
+            inner.append(acc)
+            acc *= s
+        v = base.as_strided((world,) + shape, (stride0,) + tuple(reversed(inner)), off // es)
+        if not shape:
+            return v
+        if dim == 0:
+            return v  # [world, rows/world, ...]: the gathered tensor, split in two along dim 0
+        moved = v.movedim(0, dim)  # [.., world, shape[dim], ..]
+        tgt = list(shape)
+        tgt[dim] *= world
+        if copy_out is None:
+            copy_out = torch.empty(tgt, dtype=dtype, device=self.device)
+        dst = copy_out.view(moved.shape)
+        if copy_fn is None:
+            dst.copy_(moved)
+        else:
+            copy_fn(dst, moved)
+        return copy_out
+
+
+def all_reduce(tensors, op: str = "sum") -> torch.Tensor:
+    """All-reduce over every shard (distrib/__init__.py:4-29): `tensors` is this process's list of per-shard
+    tensors (or a single tensor); each of them ends up holding the result, which is also returned.
+    "sum" and "avg" as in the reference; "max" is added for the per-tensor activation absmax."""
+    if op not in ("sum", "avg", "max"):
+        raise ValueError(f"Unknown op {op}")
+    ts = [tensors] if isinstance(tensors, torch.Tensor) else list(tensors)
+    if op == "avg" and not ts[0].is_floating_point():
+        raise ValueError("all_reduce('avg') needs floating-point tensors")
+    _, world = rank_world()
+    if len(ts) == 1:
+        total = ts[0]  # reduced in place
     else:
-        dist.all_reduce(t, op=dist.ReduceOp.SUM)
-        if op == "avg":
-            t /= world
-    return t
+        total = ts[0].clone()
+        for t in ts[1:]:
+            if op == "max":
+                torch.maximum(total, t, out=total)
+            else:
+                total.add_(t)
+    if world > 1:
+        dist.all_reduce(total, op=dist.ReduceOp.MAX if op == "max" else dist.ReduceOp.SUM)
+    n = len(ts) * world
+    if op == "avg" and n > 1:
+        total.div_(n)
+    for t in ts:
+        if t is not total:
+            t.copy_(total)
+    return total
 
 
-def pmap(f: Callable, argnum_opts: Sequence[int | None], gather: bool = True) -> Callable:
-    """Data-parallel map: argument i is split along `argnum_opts[i]` (None = replicated), `f` runs on this
-    rank's shards, the outputs are taken as split along dim 0 and, with `gather`, gathered on every rank."""
+def pmap(f: Callable, devices: Sequence | None, argnum_opts: Sequence[int | None], out_opts="avg") -> Callable:
+    """Data-parallel map with the reference's calling convention (transforms/distrib.py:31-67,
+    examples/data_parallel_mlp.py:38-57): argument i with `argnum_opts[i] = d` must have
+    `shape[d] == len(devices)` and shard k receives `arg.select(d, k)`; `None` replicates the argument.
+
+    Outputs: `out_opts="avg"` averages each output over the shards, which is what the reference does with
+    its per-device losses and gradients (transforms/distrib.py:150-157). An int d (or one entry per
+    output) instead stacks the per-shard outputs along a new dim d on every process — the final gather of
+    an inference workload. "sharded" returns this process's per-shard outputs untouched (no collective).
+    `f` must not call collectives itself."""
+    num = len(devices) if devices is not None else rank_world()[1]
+
     def wrapped(*args):
         if len(args) != len(argnum_opts):
-            raise ValueError("pmap: one sharding option per argument is required")
-        local = [a if d is None else shard_tensor(a, d).local for a, d in zip(args, argnum_opts)]
-        out = f(*local)
-        outs = out if isinstance(out, (tuple, list)) else (out,)
-        rank, world = rank_world()
-        n_batch = next((a.shape[d] for a, d in zip(args, argnum_opts) if d is not None), None)
+            raise ValueError(f"Number of args must match argnum_opts: {len(args)} != {len(argnum_opts)}")
+        mine = local_shards(num)
+        for a, d in zip(args, argnum_opts):
+            if d is not None:
+                if not isinstance(a, torch.Tensor):
+                    raise ValueError("Only tensors can be split")
+                if a.shape[d] != num:
+                    raise ValueError(f"Splitting dimension must be equal to the number of devices: {a.shape[d]} != {num}")
+        per_shard = [f(*[a if d is None else a.select(d, k) for a, d in zip(args, argnum_opts)]) for k in mine]
+        is_seq = isinstance(per_shard[0], (tuple, list))
+        n_out = len(per_shard[0]) if is_seq else 1
+        outs = [[(p[j] if is_seq else p) for p in per_shard] for j in range(n_out)]
+        opts = list(out_opts) if isinstance(out_opts, (tuple, list)) else [out_opts] * n_out
+        if len(opts) != n_out:
+            raise ValueError("pmap: one out_opts entry per output is required")
         res = []
-        for o in outs:
-            gshape = (n_batch,) + tuple(o.shape[1:]) if n_batch is not None else tuple(o.shape)
-            st = ShardedTensor(o, 0 if n_batch is not None else None, gshape)
-            res.append(unshard_tensor(st) if gather else st)
-        return res[0] if not isinstance(out, (tuple, list)) else tuple(res)
+        for shards, opt in zip(outs, opts):
+            if opt == "sharded":
+                res.append(shards)
+            elif opt == "avg":
+                res.append(all_reduce([s.clone() for s in shards], "avg"))
+            elif isinstance(opt, int):
+                nd = shards[0].dim() + 1
+                d = opt + nd if opt < 0 else opt
+                if not 0 <= d < nd:
+                    raise ValueError(f"pmap: cannot stack {nd - 1}-d outputs along dim {opt}")
+                stacked = torch.stack(shards, 0)  # [local shards, ...]
+                st = ShardedTensor([stacked], [0], rank_world()[1], [num] + list(shards[0].shape))
+                res.append(unshard_tensor(st, 0).movedim(0, d))
+            else:
+                raise ValueError(f"pmap: unknown out_opts entry {opt!r}")
+        return tuple(res) if is_seq else res[0]
     return wrapped

@@ -120,17 +120,18 @@ def describe_reduce(in_descs: Sequence[L.PgbTensor], out_desc: L.PgbTensor, op: 
     return buf.value.decode()
 
 
-def fused_elementwise(inputs: Sequence[torch.Tensor], prog, shape=None, out_dtypes=None, out_vals=None) -> list:
-    """Evaluate `prog` per element; inputs must already be views of `shape`."""
+def fused_elementwise(inputs: Sequence[torch.Tensor], prog, shape=None, out_dtypes=None, out_vals=None, outs=None) -> list:
+    """Evaluate `prog` per element; inputs must already be views of `shape`. `outs`: caller-allocated outputs."""
     if shape is None:
-        shape = tuple(inputs[0].shape)
+        shape = tuple(outs[0].shape) if outs else tuple(inputs[0].shape)
     n = len(prog)
     if out_vals is None:
         out_vals = [n - 1]
-    if out_dtypes is None:
-        out_dtypes = [inputs[0].dtype] * len(out_vals)
     dev = inputs[0].device if inputs else torch.device("cuda")
-    outs = [torch.empty(shape, dtype=dt, device=dev) for dt in out_dtypes]
+    if outs is None:
+        if out_dtypes is None:
+            out_dtypes = [inputs[0].dtype] * len(out_vals)
+        outs = [torch.empty(shape, dtype=dt, device=dev) for dt in out_dtypes]
     p, n = L.make_program(list(prog))
     ov = (C.c_int16 * len(out_vals))(*out_vals)
     with torch.cuda.device(dev):

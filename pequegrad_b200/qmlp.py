@@ -43,8 +43,8 @@ class QuantizedMLP:
                                 torch.from_numpy(np.ascontiguousarray(b, np.float32)).to(device)))
         self._bufs = {}
 
-    def _buffers(self, rows: int, device):
-        key = (rows, str(device))
+    def _buffers(self, rows: int, device, slot: int = 0):
+        key = (rows, str(device), slot)
         if key not in self._bufs:
             dims = [self.layers[0][0].shape[1]] + [l[0].shape[0] for l in self.layers]
             self._bufs[key] = dict(
@@ -56,24 +56,53 @@ class QuantizedMLP:
 
     def forward(self, x: torch.Tensor, keep: bool = False):
         """x: [rows, 784] fp32 on the device. Returns logits [rows, 10] fp32 (and, with keep, the per-layer tensors)."""
-        b = self._buffers(x.shape[0], x.device)
-        amax = b["amax"]
-        amax[1:].zero_()  # slot i holds max|input of layer i|; the GEMM epilogues fold into slots 1..
-        K.absmax(x, out=amax[0:1])
-        xq = K.quantize_i8(x, absmax_dev=amax[0:1], out=b["q"][0])
-        kept = []
+        out = self.forward_sharded([x], keep)[0]
+        return out
+
+    def forward_sharded(self, xs, keep: bool = False):
+        """The same forward over row shards of ONE batch: `xs` is this process's list of shards (or a
+        `distrib.ShardedTensor` split along dim 0). "Per tensor" keeps meaning the whole batch: after every
+        absmax the shards' maxima are combined (`distrib.all_reduce(.., "max")`: one float per layer, across the
+        shards held here and across processes), so the int8 activations and the outputs have the same bits
+        however the rows are split. Returns one output per local shard."""
+        from . import distrib as D
+        xs = xs.shards if isinstance(xs, D.ShardedTensor) else list(xs)
+        S = len(xs)
+        lone = S == 1 and D.rank_world()[1] == 1
+        bufs = [self._buffers(x.shape[0], x.device, j) for j, x in enumerate(xs)]
+        for b in bufs:
+            b["amax"][1:].zero_()  # slot i holds max|input of layer i|; the GEMM epilogues fold into slots 1..
+
+        def combine(i):
+            if not lone:
+                D.all_reduce([b["amax"][i:i + 1] for b in bufs], "max")
+
+        for x, b in zip(xs, bufs):
+            K.absmax(x, out=b["amax"][0:1])
+        combine(0)
+        xq = [K.quantize_i8(x, absmax_dev=b["amax"][0:1], out=b["q"][0]) for x, b in zip(xs, bufs)]
+        kept = [[] for _ in xs]
+        hs = [None] * S
         n = len(self.layers)
         for i, (wq, ws, bias) in enumerate(self.layers):
             last = i == n - 1
-            fused = not keep and not last and self.layers[i][0].shape[0] > 128 and self.layers[i][0].shape[0] % 16 == 0
+            fused = not keep and not last and wq.shape[0] > 128 and wq.shape[0] % 16 == 0
             if fused:
-                K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=True, want_out=False, out_absmax=amax[i + 1:i + 2])
-                xq, _ = K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=True, out=b["q"][i + 1], out_absmax=amax[i + 1:i + 2])
+                for j, b in enumerate(bufs):
+                    K.qlinear_i8(xq[j], wq, ws, a_absmax=b["amax"][i:i + 1], bias=bias, relu=True, want_out=False, out_absmax=b["amax"][i + 1:i + 2])
+                combine(i + 1)
+                for j, b in enumerate(bufs):
+                    # with an int8 output the absmax slot is an input: the scale the epilogue quantises with
+                    xq[j], _ = K.qlinear_i8(xq[j], wq, ws, a_absmax=b["amax"][i:i + 1], bias=bias, relu=True, out=b["q"][i + 1],
+                                            out_absmax=b["amax"][i + 1:i + 2])
                 continue
-            h, _ = K.qlinear_i8(xq, wq, ws, a_absmax=amax[i:i + 1], bias=bias, relu=not last, out=b["h"][i],
-                                out_absmax=amax[i + 1:i + 2] if not last else None)
-            if keep:
-                kept.append((xq, h))
+            for j, b in enumerate(bufs):
+                hs[j], _ = K.qlinear_i8(xq[j], wq, ws, a_absmax=b["amax"][i:i + 1], bias=bias, relu=not last, out=b["h"][i],
+                                        out_absmax=b["amax"][i + 1:i + 2] if not last else None)
+                if keep:
+                    kept[j].append((xq[j], hs[j]))
             if not last:
-                xq = K.quantize_i8(h, absmax_dev=amax[i + 1:i + 2], out=b["q"][i + 1])
-        return (h, kept) if keep else h
+                combine(i + 1)
+                for j, b in enumerate(bufs):
+                    xq[j] = K.quantize_i8(hs[j], absmax_dev=b["amax"][i + 1:i + 2], out=b["q"][i + 1])
+        return [(h, k) for h, k in zip(hs, kept)] if keep else hs

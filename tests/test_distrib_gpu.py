@@ -1,0 +1,138 @@
+"""The sharding layer over the kernels of this library on real devices.
+
+One GPU: a process that holds every shard (what the reference's emulated devices do,
+examples/data_parallel_mlp.py:28-31) runs `pmap` / `shard_tensor` over pgb kernels and must give the
+unsharded results. Two GPUs (skipped below that): two processes over NCCL run the same checks and the
+benchmark's partitioned workloads, whose gathered results must equal the single-GPU ones."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+from pequegrad_b200 import _lib as L
+from pequegrad_b200 import distrib as D
+from pequegrad_b200 import kernels as K
+from pequegrad_b200.workloads import AFFINE, EXP_EPI
+
+pytestmark = pytest.mark.gpu
+
+
+def _reduce(op, ax, epi=()):
+    return lambda t: K.fused_reduce([t], op, [ax], False, AFFINE, epi)
+
+
+def _check_pmap_over_reduces(x3, devs):
+    """x3: [P, rows / P, cols] on the device. Row-sharded fused reduces through pmap == the reduce over all rows."""
+    P, r, c = x3.shape
+    flat = x3.reshape(P * r, c)
+    got = D.pmap(_reduce(L.MAX, 1), devs, [0], out_opts=0)(x3).reshape(-1)
+    assert torch.equal(got, _reduce(L.MAX, 1)(flat))
+    got = D.pmap(_reduce(L.ARGMAX, 1), devs, [0], out_opts=0)(x3).reshape(-1)
+    assert torch.equal(got, _reduce(L.ARGMAX, 1)(flat))
+    got = D.pmap(_reduce(L.SUM, 1, EXP_EPI), devs, [0], out_opts=0)(x3).reshape(-1)
+    want = _reduce(L.SUM, 1, EXP_EPI)(flat)
+    assert torch.allclose(got, want, rtol=1e-5, atol=0)  # the row kernel may split rows differently: not the same bits
+    # column reduce with the columns split: shards arrive as [rows, cols / P] slabs and come back side by side
+    xt = x3.permute(1, 0, 2)  # [r, P, c]: P column blocks of an [r, P * c] matrix
+    got = D.pmap(_reduce(L.MAX, 0), devs, [1], out_opts=0)(xt).reshape(-1)
+    assert torch.equal(got, _reduce(L.MAX, 0)(xt.reshape(r, P * c)))
+    # the reference's default: outputs averaged over the devices
+    got = D.pmap(lambda t: _reduce(L.MEAN, 0)(t), devs, [0])(x3)
+    assert torch.allclose(got, flat.mul(1.5).add(0.25).mean(0), rtol=1e-4, atol=1e-5)
+
+
+def test_one_process_holding_every_shard():
+    g = torch.Generator(device="cuda").manual_seed(21)
+    for P in (2, 4):
+        x3 = torch.randn((P, 96, 1500), generator=g, device="cuda")
+        _check_pmap_over_reduces(x3, D.default_devices(P))
+    # shard_tensor -> kernels on every shard -> unshard_tensor
+    x = torch.randn((1000, 777), generator=g, device="cuda")
+    st = D.shard_tensor(x, 4, 0, D.default_devices(4))
+    outs = D.ShardedTensor([_reduce(L.MAX, 1)(s) for s in st.shards], [0], 4, [1000])
+    assert torch.equal(D.unshard_tensor(outs, 0), _reduce(L.MAX, 1)(x))
+    st = D.shard_tensor(x, 3, 1)  # uneven column slabs
+    outs = D.ShardedTensor([_reduce(L.ARGMAX, 0)(s) for s in st.shards], [0], 3, [777])
+    assert torch.equal(D.unshard_tensor(outs, 0), _reduce(L.ARGMAX, 0)(x))
+
+
+def _free_port():
+    s = socket.socket()
+    s.bind(("127.0.0.1", 0))
+    p = s.getsockname()[1]
+    s.close()
+    return p
+
+
+def _worker(rank, world, port, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), RANK=str(rank), WORLD_SIZE=str(world), LOCAL_RANK=str(rank),
+                      NCCL_NVLS_ENABLE="0")
+    try:
+        D.init("nccl", timeout_s=120.0)
+        dev = torch.device("cuda", rank)
+        g = torch.Generator(device=dev).manual_seed(21)
+        x3 = torch.randn((world, 96, 1500), generator=g, device=dev)
+        _check_pmap_over_reduces(x3, D.default_devices(world))
+
+        # the benchmark's partitioned sweep: gathered results == the unsharded kernels on the global arrays
+        from pequegrad_b200 import workloads as W
+        wl = W.Sweep()
+        wl.setup(dev, rank, world)
+        wl.step()
+        wl.step()
+        torch.cuda.synchronize()
+        got = dict(wl.results())
+        g2 = torch.Generator(device=dev).manual_seed(2)
+        T = {"A": torch.randn(W.SHAPES["A"], generator=g2, device=dev)}
+        T["B"] = torch.randn(W.SHAPES["B"], generator=g2, device=dev)
+        T["Bp"] = T["B"].permute(0, 2, 1)
+        opcode = {"sum": L.SUM, "max": L.MAX, "mean": L.MEAN, "argmax": L.ARGMAX}
+        for name, op, ax, _ in wl.cases:
+            want = K.fused_reduce([T[name]], opcode[op], [ax], False, AFFINE, () if op == "argmax" else EXP_EPI)
+            have = got[f"{name}.{op}.ax{ax}"]
+            assert have.shape == want.shape, (name, op, ax, have.shape, want.shape)
+            if op in ("max", "argmax"):
+                assert torch.equal(have, want), (name, op, ax)
+            else:
+                both_inf = torch.isinf(have) & torch.isinf(want)
+                assert torch.allclose(torch.where(both_inf, 0, have), torch.where(both_inf, 0, want), rtol=2e-5, atol=0), (name, op, ax)
+        del wl, T, got
+        torch.cuda.empty_cache()
+
+        # the int8 MLP split by rows: the bits of the single-GPU forward over the whole batch
+        m = W.Mlp(rows=16384)
+        m.setup(dev, rank, world)
+        m.step()
+        g3 = torch.Generator(device=dev).manual_seed(3)
+        X = torch.rand((16384, 784), generator=g3, device=dev)
+        whole = m.mlp.forward_sharded([X])[0]  # one shard per process holding ALL rows: both ranks compute the same thing
+        assert torch.equal(m.out_full, whole)
+        assert K.device_error() == 0
+        q.put((rank, "ok"))
+    except Exception as e:  # noqa: BLE001
+        import traceback
+        q.put((rank, "FAILED " + repr(e) + traceback.format_exc()[-1500:]))
+    finally:
+        import torch.distributed as dist
+        if dist.is_initialized():
+            dist.destroy_process_group()
+
+
+@pytest.mark.skipif(torch.cuda.device_count() < 2, reason="needs two GPUs")
+def test_two_processes_over_nccl():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    res = dict(q.get(timeout=600) for _ in range(world))
+    for p in procs:
+        p.join(timeout=120)
+        if p.is_alive():
+            p.kill()
+    assert res == {0: "ok", 1: "ok"}, res

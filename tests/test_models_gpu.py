@@ -42,6 +42,39 @@ def test_quantized_mlp_class_matches_the_oracle_pipeline():
     assert K.device_error() == 0
 
 
+def test_quantized_mlp_at_the_configured_batch_of_65536_rows():
+    """The benchmark's batch: 65536 x 784 uniform[0,1). Rows are independent given the per-tensor scales, so slabs of
+    the full-size run (first, middle, last 256 rows) are compared with the oracle pipeline fed the run's own
+    absmax values; the absmax values themselves are checked against the whole tensors."""
+    from pequegrad_b200.workloads import mlp_weights
+    Ws, bs = mlp_weights()
+    g = torch.Generator(device="cuda").manual_seed(3)
+    X = torch.rand((65536, 784), generator=g, device="cuda")
+    mlp = QuantizedMLP(Ws, bs)
+    out, kept = mlp.forward(X, keep=True)
+    out = out.clone()
+    amax = mlp._buffers(65536, X.device)["amax"].cpu().numpy()
+    assert amax[0] == float(X.abs().max())
+    for i in range(2):  # max |relu output| of the whole batch, folded in by the GEMM epilogues
+        assert amax[i + 1] == float(kept[i][1].abs().max()), f"absmax of layer {i}'s output"
+    prep = [oracle.quantize_weight_per_channel(W) for W in Ws]
+    for lo in (0, 32768 - 128, 65536 - 256):
+        h = X[lo:lo + 256].cpu().numpy()
+        for i in range(3):
+            sx = oracle.quant_scale(amax[i])
+            xq = oracle.quantize_i8(h, sx)
+            assert np.array_equal(kept[i][0][lo:lo + 256].cpu().numpy(), xq), f"rows {lo}: layer {i} int8 activations"
+            h = oracle.dequant_bias_act(oracle.gemm_i8(xq, prep[i][0]), prep[i][1], sx, bs[i], relu=i < 2)
+            assert_close(kept[i][1][lo:lo + 256].cpu().numpy(), h, 1e-5, 1e-6, f"rows {lo}: layer {i} output")
+    # the route the benchmark runs (hidden fp32 activations never written) gives the same logits, bit for bit
+    assert torch.equal(mlp.forward(X), out)
+    # and so does any split of the rows, because the absmax is combined over the shards
+    for parts in (2, 8):
+        outs = mlp.forward_sharded(list(X.chunk(parts, 0)))
+        assert torch.equal(torch.cat(outs, 0), out), f"{parts} row shards"
+    assert K.device_error() == 0
+
+
 @pytest.mark.parametrize("cfg,B,T", [(G.GPT2Config(n_layer=2, n_head=2, n_embd=128, vocab_size=1000, block_size=64), 3, 64),
                                      (G.GPT2Config(n_layer=3, n_head=4, n_embd=256, vocab_size=517, block_size=128), 2, 100),
                                      (G.GPT2Config(n_layer=2, n_head=4, n_embd=128, vocab_size=300, block_size=64), 2, 48)])
@@ -67,13 +100,13 @@ def test_gpt2_small_configs_match_fp32_reference(cfg, B, T):
         assert_close(got, want, 2e-2, 2e-2 * float(np.abs(want).max()), f"logits (fused attention: {model.fused_attention})")
 
 
-def test_gpt2_small_full_architecture_one_sequence():
-    # the configured model (12 layers, 768, 12 heads, vocab 50257, context 1024) on one sequence; the CPU
-    # reference at fp32 takes a few seconds
+def test_gpt2_small_full_architecture_two_sequences():
+    # the configured model (12 layers, 768, 12 heads, vocab 50257, context 1024) on a 2 x 1024 slice of the batch;
+    # the CPU reference at fp32 takes some seconds
     cfg = G.GPT2Config()
     w = G.init_weights(cfg, seed=5)
     rng = np.random.default_rng(5)
-    idx = rng.integers(0, cfg.vocab_size, (1, 1024)).astype(np.int32)
+    idx = rng.integers(0, cfg.vocab_size, (2, 1024)).astype(np.int32)
     model = G.GPT2(cfg, w)
     got = model.forward(torch.from_numpy(idx).cuda()).float().cpu().numpy()
     assert K.device_error() == 0
@@ -81,3 +114,36 @@ def test_gpt2_small_full_architecture_one_sequence():
     assert_close(got, want, 2e-2, 2e-2 * float(np.abs(want).max()), "logits")
     # and the argmax token agrees almost everywhere (ties aside)
     assert (got.argmax(-1) == want.argmax(-1)).mean() > 0.98
+
+
+@pytest.mark.parametrize("dtype", [torch.float16, torch.float32])
+def test_embedding_rows_is_an_exact_gather(dtype):
+    """out[r] = wte[ids[r]] + wpe[r % T] (pequegrad/modules.py:329-337 over csrc/cuda/select.cuh:27-79): index work, so
+    the gathered rows are compared bit for bit; the positional row wraps at T; an id outside the table gives a zero row."""
+    g = torch.Generator(device="cuda").manual_seed(9)
+    V, C, T = 1000, 96, 7
+    wte = torch.randn((V, C), generator=g, device="cuda").to(dtype)
+    wpe = torch.randn((T, C), generator=g, device="cuda").to(dtype)
+    ids = torch.randint(0, V, (5, T), generator=g, device="cuda", dtype=torch.int32)
+    # without positions: a pure gather
+    got = K.embedding_rows(ids, wte, None, T)
+    assert got.shape == (5, T, C) and torch.equal(got, wte[ids.long()])
+    # with positions: one add per element, in the table's dtype arithmetic (fp32 add, rounded once for fp16)
+    got = K.embedding_rows(ids, wte, wpe, T)
+    want = (wte[ids.long()].float() + wpe[None].float()).to(dtype)
+    assert torch.equal(got, want)
+    # a flat id list longer than T: row r uses position r % T
+    flat = ids.reshape(-1)
+    got = K.embedding_rows(flat, wte, wpe, T)
+    pos = torch.arange(flat.numel(), device="cuda") % T
+    assert torch.equal(got, (wte[flat.long()].float() + wpe[pos].float()).to(dtype))
+    # ids outside [0, V) read nothing: the whole output row is zero, with or without positions
+    bad = ids.clone()
+    bad[0, 0], bad[2, 3] = V, -1
+    got = K.embedding_rows(bad, wte, wpe, T)
+    assert (got[0, 0] == 0).all() and (got[2, 3] == 0).all()
+    got = K.embedding_rows(bad, wte, None, T)
+    assert (got[0, 0] == 0).all() and (got[2, 3] == 0).all()
+    ok = torch.ones((5, T), dtype=torch.bool, device="cuda")
+    ok[0, 0] = ok[2, 3] = False
+    assert torch.equal(got[ok], wte[bad.long().clamp(0, V - 1)][ok])

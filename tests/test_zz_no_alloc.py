@@ -12,6 +12,8 @@ problem whose partials do not fit is refused cleanly.
 The file sorts last on purpose: a run that stops at the first failure has
 already been through every other test by the time it gets here.
 """
+import ctypes as C
+
 import pytest
 import torch
 
@@ -67,3 +69,71 @@ def test_refuses_what_does_not_fit():
     assert (idx == -3).all()  # refused before anything was launched
     # the regular entry point still handles it, with a workspace of the caller's or its own
     assert torch.equal(K.fused_reduce([big], L.ARGMAX, [0]).long(), big.argmax(0))
+
+
+@pytest.mark.parametrize("dtype", [torch.float32, torch.float16])
+def test_two_inputs_half_precision_and_programs_the_fast_kernels_refuse(dtype):
+    """More shapes of call through the built-in array: two inputs, fp16 inputs, and a prologue that is not a chain
+    (it runs on the generic kernel, which needs no scratch although the planner, asked without the prologue, reserved some)."""
+    g = torch.Generator(device="cuda").manual_seed(6)
+    a = torch.randn((6, 1 << 18), generator=g, device="cuda").to(dtype)
+    b = torch.randn((6, 1 << 18), generator=g, device="cuda").to(dtype)
+    two = [("LOAD", 0), ("LOAD", 1), ("MUL", 0, 1)]
+    tree = [("LOAD", 0), ("IMM", 0, 0, 0, 1.0), ("ADD", 0, 1), ("IMM", 0, 0, 0, 2.0), ("SUB", 0, 3), ("MUL", 2, 4)]
+    for ins, pro in (([a, b], two), ([a], tree), ([a], AFFINE)):
+        for op in (L.SUM, L.MAX, L.ARGMAX):
+            for _ in range(2):
+                want = K.fused_reduce(ins, op, [1], False, pro)
+                got = K.fused_reduce_noalloc(ins, op, [1], _out_like(want), pro)
+                assert torch.equal(got, want), (dtype, op, len(ins))
+
+
+class _DefaultPool:
+    """The device's default stream-ordered memory pool, read through the CUDA runtime: every cudaMallocAsync of this
+    library draws from it, so its high-water mark shows whether a call allocated."""
+    USED_CURRENT, USED_HIGH = 7, 8  # cudaMemPoolAttrUsedMemCurrent, cudaMemPoolAttrUsedMemHigh
+
+    def __init__(self):
+        self.rt = C.CDLL("libcudart.so.12")
+        self.pool = C.c_void_p()
+        assert self.rt.cudaDeviceGetDefaultMemPool(C.byref(self.pool), torch.cuda.current_device()) == 0
+
+    def get(self, attr):
+        v = C.c_uint64(0)
+        assert self.rt.cudaMemPoolGetAttribute(self.pool, attr, C.byref(v)) == 0
+        return v.value
+
+    def reset_high(self):
+        v = C.c_uint64(0)
+        assert self.rt.cudaMemPoolSetAttribute(self.pool, self.USED_HIGH, C.byref(v)) == 0
+
+    def free_bytes(self):
+        f, t = C.c_size_t(0), C.c_size_t(0)
+        assert self.rt.cudaMemGetInfo(C.byref(f), C.byref(t)) == 0
+        return f.value
+
+
+def test_the_call_allocates_nothing_on_the_device():
+    x = torch.randn((4, 1 << 20), device="cuda")
+    need = K.reduce_workspace_bytes(x, [4], L.SUM, [1])
+    assert need > 0
+    want = K.fused_reduce([x], L.SUM, [1], False, AFFINE, EXP_EPI)
+    out = _out_like(want)
+    K.fused_reduce_noalloc([x], L.SUM, [1], out, AFFINE, EXP_EPI)  # first call on the device: looks up the array's address
+    torch.cuda.synchronize()
+    pool = _DefaultPool()
+    # control: the regular entry point without a caller workspace takes its partials from the pool, and the probe sees it
+    pool.reset_high()
+    base = pool.get(pool.USED_CURRENT)
+    K.fused_reduce([x], L.SUM, [1], False, AFFINE, EXP_EPI, out=out)
+    torch.cuda.synchronize()
+    assert pool.get(pool.USED_HIGH) >= base + need
+    # the variant: no stream-ordered allocation (the pool's high-water mark does not move) and no plain one either
+    pool.reset_high()
+    base, free0 = pool.get(pool.USED_CURRENT), pool.free_bytes()
+    for _ in range(3):
+        K.fused_reduce_noalloc([x], L.SUM, [1], out, AFFINE, EXP_EPI)
+    torch.cuda.synchronize()
+    assert pool.get(pool.USED_HIGH) == base and pool.get(pool.USED_CURRENT) == base
+    assert pool.free_bytes() == free0
+    assert torch.equal(out, want)
