@@ -89,10 +89,14 @@ REF_API int refcuda_where_f32(const long *d_s0, const long *d_s1, const long *d_
 // The README case: x is the [1000,20,100] buffer (read through its permuted strides inside the kernel),
 // y [1000,100,20], out [1000,100]. The shapes are baked into the generated source.
 REF_API int refcuda_readme_kernel(const float *x, const float *y, float *out, void *stream) {
-  cudaDeviceProp prop;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || cudaGetDeviceProperties(&prop, dev) != cudaSuccess) return -3;
-  const int threads = prop.maxThreadsPerBlock / 2, n_out = 100000;
+  // the reference queries the device once, when it first compiles the kernel (csrc/compiler/ir.cpp:1577-1579)
+  static int threads = 0;
+  if (threads == 0) {
+    int dev = 0, max_threads = 0;
+    if (cudaGetDevice(&dev) != cudaSuccess || cudaDeviceGetAttribute(&max_threads, cudaDevAttrMaxThreadsPerBlock, dev) != cudaSuccess) return -3;
+    threads = max_threads / 2;
+  }
+  const int n_out = 100000;
   reduce_kernel<<<(n_out + threads - 1) / threads, threads, 0, (cudaStream_t)stream>>>(x, y, out);
   return last_error();
 }

@@ -135,5 +135,5 @@ def test_the_call_allocates_nothing_on_the_device():
         K.fused_reduce_noalloc([x], L.SUM, [1], out, AFFINE, EXP_EPI)
     torch.cuda.synchronize()
     assert pool.get(pool.USED_HIGH) == base and pool.get(pool.USED_CURRENT) == base
-    assert pool.free_bytes() == free0
+    assert pool.free_bytes() >= free0  # nothing was taken from the device by cudaMalloc either
     assert torch.equal(out, want)
