@@ -318,9 +318,24 @@ PGB_API int pgb_absmax_f32(const pgb_tensor *x, float *absmax_dev, void *stream)
 PGB_API int pgb_quantize_i8(const pgb_tensor *x, const float *absmax_dev, float scale, const pgb_tensor *q,
                             void *stream);
 
-/* Error word of the tensor-core kernels' bounded waits: 0 = none. Synchronises with the device.
- * Nonzero = (role << 16) | block: 1 producer, 2 MMA issuer, 3 epilogue gave up waiting. */
+/* Error word of the kernels' bounded device-side waits (every mbarrier wait of the tensor-core GEMMs, the fused
+ * attention and the streaming LayerNorm gives up after a fixed number of polls instead of hanging). Synchronises
+ * with the device. *code = 0 and PGB_OK when no wait ran out; else *code = (role << 16) | block (roles: 1 producer,
+ * 2 MMA issuer, 3 epilogue, 4-7 other roles of the GEMM / attention kernels, 8-9 streaming LayerNorm) and the
+ * return value is PGB_ERR_TIMEOUT. While the word is set, later launches of those kernels return at once without
+ * computing; `reset` clears it. Replaces nothing in the reference, whose kernels never wait on one another. */
 PGB_API int pgb_device_error(int *code, int reset);
+
+/* Which GEMMs run on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles): 0 = none, 1 = the measured default
+ * (large aligned f16 / bf16 / tf32 problems), negative = only query. Returns the previous mode. A tuning switch in
+ * the manner of cublasSetMathMode; the reference has no counterpart. */
+PGB_API int pgb_gemm_pair_mode(int mode);
+
+/* Failure-detection drill: the NEXT tensor-core GEMM launched from this host thread polls each of its waits at most
+ * `polls` times and, with skip_loads != 0, its producer issues no loads, so the wait of its MMA warp runs out: the
+ * kernel records the error word above, frees its tensor memory and returns; nothing faults or hangs. Used by the
+ * tests to exercise the timeout path; no counterpart in the reference. */
+PGB_API int pgb_gemm_wait_drill(unsigned int polls, int skip_loads);
 
 #ifdef __cplusplus
 }

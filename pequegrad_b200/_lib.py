@@ -58,6 +58,7 @@ EXPORTS = [
     "pgb_fused_elementwise", "pgb_fused_reduce", "pgb_fused_reduce_workspace", "pgb_fused_reduce_describe",
     "pgb_softmax_rows", "pgb_layernorm_rows", "pgb_fused_reduce_noalloc",
     "pgb_embedding_rows", "pgb_matmul", "pgb_attention", "pgb_qlinear_i8", "pgb_absmax_f32", "pgb_quantize_i8", "pgb_device_error",
+    "pgb_gemm_pair_mode", "pgb_gemm_wait_drill",
 ]
 NOALLOC_SCRATCH_BYTES = 4 << 20  # PGB_NOALLOC_SCRATCH_BYTES
 
@@ -95,6 +96,8 @@ def lib() -> C.CDLL:
     L.pgb_absmax_f32.argtypes = [TP, C.c_void_p, C.c_void_p]
     L.pgb_quantize_i8.argtypes = [TP, C.c_void_p, C.c_float, TP, C.c_void_p]
     L.pgb_device_error.argtypes = [C.POINTER(C.c_int), C.c_int]
+    L.pgb_gemm_pair_mode.argtypes = [C.c_int]
+    L.pgb_gemm_wait_drill.argtypes = [C.c_uint, C.c_int]
     L.pgb_softmax_rows.argtypes = [TP, TP, C.c_int, C.c_void_p]
     L.pgb_layernorm_rows.argtypes = [TP, TP, TP, C.c_float, TP, C.c_void_p]
     for name in EXPORTS:

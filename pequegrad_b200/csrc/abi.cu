@@ -101,6 +101,7 @@ static int plan_and_launch(ReduceJob &j) {
   if (j.c.n_out == 0) { j.desc = "empty"; return PGB_OK; }
   int r = launch_reduce_row(j);
   if (r == 0) r = launch_reduce_col(j);
+  if (r == 0) r = launch_reduce_plane(j);
   if (r == 0) r = launch_reduce_generic(j);
   return r == 1 ? PGB_OK : (r == 0 ? PGB_ERR_UNSUPPORTED : r);
 }

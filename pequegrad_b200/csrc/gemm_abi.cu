@@ -250,7 +250,21 @@ extern "C" {
 
 PGB_API int pgb_device_error(int *code, int reset) {
   if (!code) return PGB_ERR_INVALID_ARG;
-  return read_gemm_error(code, reset != 0);
+  const int st = read_gemm_error(code, reset != 0);
+  if (st != PGB_OK) return st;
+  if (*code != 0) {
+    set_error("a bounded device-side wait ran out: role " + std::to_string(*code >> 16) + ", block " + std::to_string(*code & 0xffff));
+    return PGB_ERR_TIMEOUT;
+  }
+  return PGB_OK;
+}
+
+PGB_API int pgb_gemm_pair_mode(int mode) { return set_gemm_pair_mode(mode); }
+
+PGB_API int pgb_gemm_wait_drill(unsigned int polls, int skip_loads) {
+  if (polls == 0) { set_error("gemm_wait_drill: the poll limit must be positive"); return PGB_ERR_INVALID_ARG; }
+  set_next_gemm_wait_test(polls, skip_loads != 0);
+  return PGB_OK;
 }
 
 PGB_API int pgb_absmax_f32(const pgb_tensor *x, float *absmax_dev, void *stream) {

@@ -129,7 +129,7 @@ __device__ __noinline__ void gemm_epilogue_tiles(const GemmParams &p, uint32_t t
     }
     __syncwarp();
     bool ok = true;
-    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
+    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag, p.spin_limit);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) {
       if (lane == 0) report_error(p, abort_flag, 3);

@@ -94,7 +94,7 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
       for (int c = cbeg; c < lim; c += 64 / OES) tma_prefetch_4d(rmap, n0 + c, row0, zb, wb);
     }
     bool ok = true;
-    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
+    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag, p.spin_limit);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) {
       if (lane == 0) report_error(p, abort_flag, 3);
@@ -120,7 +120,7 @@ __device__ __noinline__ void gemm_epilogue_tma(const GemmParams &p, const CUtens
       };
       auto res_arrived = [&]() -> bool {
         bool got = true;
-        if (lane == 0) got = mbar_wait(res_bar, res_phase, abort_flag);
+        if (lane == 0) got = mbar_wait(res_bar, res_phase, abort_flag, p.spin_limit);
         got = __shfl_sync(0xffffffffu, got ? 1 : 0, 0) != 0;
         res_phase ^= 1u;
         return got;
@@ -267,7 +267,7 @@ static __device__ __noinline__ void gemm_epilogue_idle(const GemmParams &p, uint
   for (int tile = blockIdx.x; tile < num_tiles; tile += gridDim.x, ++it) {
     const int buf = it & 1;
     bool ok = true;
-    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag);
+    if (lane == 0) ok = mbar_wait(&acc_full[buf], (it >> 1) & 1, abort_flag, p.spin_limit);
     ok = __shfl_sync(0xffffffffu, ok ? 1 : 0, 0) != 0;
     if (!ok) {
       if (lane == 0) report_error(p, abort_flag, 3);

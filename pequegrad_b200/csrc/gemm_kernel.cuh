@@ -48,6 +48,9 @@ struct GemmParams {
   int out_tma;  // 0: plain stores; 2 / 4: the output goes through TMA tile stores, value = its element size
   int res_vec;  // the residual rows can be read with 16-byte loads
   int pair;     // CTAs per tile: 1, or 2 for the CTA-pair kernel (256-row tiles, tiles_m counts those)
+  int last_mmas;        // MMAs the last K slab needs (1..4): K need not fill it
+  uint32_t spin_limit;  // polls per bounded wait
+  int skip_loads;       // test hook: the producer issues no loads, so the first wait of the MMA warp runs out
   int *err;     // device error word: 0 = ok; else (role << 16) | block index bits
   GemmEpilogue epi;
 };

@@ -67,7 +67,8 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
         const int bz = tile / tiles_per_batch, rem = tile - bz * tiles_per_batch;
         const int m0 = (rem / p.tiles_n) * kBM, n0 = (rem % p.tiles_n) * BN;
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(&empty[s], phase ^ 1, abort_flag)) {
+          if (p.skip_loads) { ok = false; break; }  // test hook: nothing is loaded, the MMA warp's wait runs out
+          if (!mbar_wait(&empty[s], phase ^ 1, abort_flag, p.spin_limit)) {
             report_error(p, abort_flag, 1);
             ok = false;
             break;
@@ -89,14 +90,14 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
       for (int tile = blockIdx.x; tile < num_tiles && ok; tile += gridDim.x, ++it) {
         const int buf = it & 1;
         // the epilogue must have drained this accumulator (its use two tiles ago)
-        if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag)) {
+        if (!mbar_wait(&acc_empty[buf], ((it >> 1) & 1) ^ 1, abort_flag, p.spin_limit)) {
           report_error(p, abort_flag, 4);
           break;
         }
         tc_fence_after();
         const uint32_t tmem_d = tmem_base + (uint32_t)(buf * BN);
         for (int kb = 0; kb < p.num_kb; ++kb) {
-          if (!mbar_wait(&full[s], phase, abort_flag)) {
+          if (!mbar_wait(&full[s], phase, abort_flag, p.spin_limit)) {
             report_error(p, abort_flag, 2);
             ok = false;
             break;
@@ -104,9 +105,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1) gemm_tc_kernel(const __grid_c
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + s * Cfg::kStageBytes);
           const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kTileABytes);
+          const int n_mma = kb == p.num_kb - 1 ? p.last_mmas : kSlabBytes / 32;
 #pragma unroll
           for (int kk = 0; kk < kSlabBytes / 32; ++kk)  // one MMA consumes 32 bytes of K: +2 in 16-byte units
-            tc_mma<KIND>(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
+            if (kk < n_mma) tc_mma<KIND>(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
           tc_commit(&empty[s]);  // frees the stage when these MMAs have read it
           if (++s == STAGES) { s = 0; phase ^= 1; }
         }

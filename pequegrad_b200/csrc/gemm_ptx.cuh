@@ -32,8 +32,8 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t *bar, uint32_t parity) {
 }
 // Bounded wait. Returns false if the barrier did not flip within the limit or
 // another role already gave up.
-__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
-  for (uint32_t i = 0; i < kSpinLimit; ++i) {
+__device__ __forceinline__ bool mbar_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t limit = kSpinLimit) {
+  for (uint32_t i = 0; i < limit; ++i) {
     if (mbar_try_wait(bar, parity)) return true;
     if ((i & 1023) == 1023 && *abort_flag) return false;
   }

@@ -24,6 +24,7 @@
 // Every wait is bounded: on a timeout the kernel records an error word that
 // pgb_device_error() reads, skips the rest of its work and frees its TMEM.
 #include <algorithm>
+#include <atomic>
 #include <cstdlib>
 #include <mutex>
 #include <string>
@@ -49,6 +50,52 @@ static EncodeTiledFn encode_fn() {
   return fn;
 }
 
+// Encoding a tensor map costs a microsecond or two of host time, four of them per launch; a map depends only on the
+// address, the extents, the pitches and the box, so the last encodings are kept and reused (what matters when a
+// launch is tens of microseconds: the 8192-row MLP shards of an 8-GPU run, decode-sized GEMMs).
+struct MapKey {
+  const void *ptr;
+  int dt, swizzle, promo;
+  uint64_t dims[4], strides[3];
+  uint32_t box[4];
+  bool operator==(const MapKey &o) const {
+    if (ptr != o.ptr || dt != o.dt || swizzle != o.swizzle || promo != o.promo) return false;
+    for (int i = 0; i < 4; ++i) if (dims[i] != o.dims[i] || box[i] != o.box[i]) return false;
+    for (int i = 0; i < 3; ++i) if (strides[i] != o.strides[i]) return false;
+    return true;
+  }
+};
+
+static CUresult encode_cached(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, const cuuint64_t dims[4], const cuuint64_t strides[3],
+                              const cuuint32_t box[4], CUtensorMapSwizzle swizzle, CUtensorMapL2promotion promo) {
+  constexpr int kSlots = 128;
+  static std::mutex mu;
+  static MapKey keys[kSlots];
+  static CUtensorMap maps[kSlots];
+  static int used = 0, next = 0;
+  MapKey k{};
+  k.ptr = ptr; k.dt = (int)dt; k.swizzle = (int)swizzle; k.promo = (int)promo;
+  for (int i = 0; i < 4; ++i) { k.dims[i] = dims[i]; k.box[i] = box[i]; }
+  for (int i = 0; i < 3; ++i) k.strides[i] = strides[i];
+  {
+    std::lock_guard<std::mutex> lock(mu);
+    for (int i = 0; i < used; ++i)
+      if (keys[i] == k) { *map = maps[i]; return CUDA_SUCCESS; }
+  }
+  EncodeTiledFn fn = encode_fn();
+  if (!fn) return CUDA_ERROR_NOT_SUPPORTED;
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  const CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, swizzle, promo,
+                        CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  if (r == CUDA_SUCCESS) {
+    std::lock_guard<std::mutex> lock(mu);
+    const int slot = used < kSlots ? used++ : (next = (next + 1) % kSlots);
+    keys[slot] = k;
+    maps[slot] = *map;
+  }
+  return r;
+}
+
 // [nb0, nb1, rows, K] K-major operand -> 4-D tensor map with a {128 bytes of K, box_rows, 1, 1} box, 128B swizzle
 static int make_operand_map(CUtensorMap *map, const void *ptr, int kind, int64_t rows, int64_t K, int64_t ld_elems, int64_t nb0, int64_t nb1,
                             int64_t bs0, int64_t bs1, int box_rows, const char *what) {
@@ -69,9 +116,7 @@ static int make_operand_map(CUtensorMap *map, const void *ptr, int kind, int64_t
   const cuuint64_t dims[4] = {(cuuint64_t)K, (cuuint64_t)rows, (cuuint64_t)std::max<int64_t>(nb1, 1), (cuuint64_t)std::max<int64_t>(nb0, 1)};
   const cuuint64_t strides[3] = {(cuuint64_t)(ld_elems * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
   const cuuint32_t box[4] = {(cuuint32_t)(kSlabBytes / es), (cuuint32_t)box_rows, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  const CUresult r = fn(map, dt, 4, const_cast<void *>(ptr), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
-                        CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE);
+  const CUresult r = encode_cached(map, dt, ptr, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B);
   if (r != CUDA_SUCCESS) {
     set_error(std::string("matmul: cuTensorMapEncodeTiled failed for operand ") + what + " (code " + std::to_string((int)r) + ")");
     return PGB_ERR_CUDA;
@@ -86,9 +131,7 @@ bool encode_map_4d(CUtensorMap *map, CUtensorMapDataType dt, const void *ptr, co
   const cuuint64_t d[4] = {dims[0], dims[1], dims[2], dims[3]};
   const cuuint64_t s[3] = {strides[0], strides[1], strides[2]};
   const cuuint32_t b[4] = {box[0], box[1], box[2], box[3]};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(map, dt, 4, const_cast<void *>(ptr), d, s, b, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B,
-            CU_TENSOR_MAP_L2_PROMOTION_L2_128B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_cached(map, dt, ptr, d, s, b, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B) == CUDA_SUCCESS;
 }
 
 // The output as a 4-D tensor map for TMA tile stores: {N, M, nb1, nb0} with a {128 bytes, 32 rows, 1, 1} box, 128B swizzle.
@@ -116,9 +159,7 @@ static bool make_box_map(CUtensorMap *map, void *ptr, int dtype, int64_t ld, int
   const cuuint64_t strides[3] = {(cuuint64_t)(e.ldc * es), (cuuint64_t)(bs1 * es), (cuuint64_t)(bs0 * es)};
   // the epilogue's box: 32 rows x 64 bytes, 64B swizzle (gemm_epilogue_tma.cuh)
   const cuuint32_t box[4] = {(cuuint32_t)(64 / es), 32, 1, 1};
-  const cuuint32_t estr[4] = {1, 1, 1, 1};
-  return fn(map, dt, 4, e.out, dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_64B,
-            CU_TENSOR_MAP_L2_PROMOTION_NONE, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+  return encode_cached(map, dt, e.out, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_64B, CU_TENSOR_MAP_L2_PROMOTION_NONE) == CUDA_SUCCESS;
 }
 
 // The device error word that a kernel sets when one of its bounded waits runs out (one per device).
@@ -154,11 +195,23 @@ extern template int launch_gemm_pair<GEMM_F16>(const CUtensorMap &, const CUtens
 extern template int launch_gemm_pair<GEMM_BF16>(const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, cudaStream_t);
 extern template int launch_gemm_pair<GEMM_TF32>(const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const CUtensorMap &, const GemmParams &, cudaStream_t);
 
-// PGB_GEMM_PAIR=0 keeps every GEMM on the one-CTA kernel (a switch for A/B timing and for the tests that compare
-// the two kernels; read at every call).
-static bool pair_enabled() {
-  const char *v = getenv("PGB_GEMM_PAIR");
-  return !(v && v[0] == '0');
+// Which problems go to the CTA-pair kernel: 0 none (every GEMM on the one-CTA kernel), 1 the measured default below.
+// Set through pgb_gemm_pair_mode() (A/B timing, and the tests that compare the two kernels).
+static std::atomic<int> g_pair_mode{1};
+int set_gemm_pair_mode(int mode) {
+  if (mode < 0) return g_pair_mode.load();
+  return g_pair_mode.exchange(mode > 0 ? 1 : 0);
+}
+static bool pair_enabled() { return g_pair_mode.load(std::memory_order_relaxed) != 0; }
+
+// A test hook: the next launch of the one-CTA kernel on this thread uses this many polls per wait instead of the
+// default and, if `skip_loads`, its producer issues no loads, so that the first wait runs out (nothing faults, nothing
+// hangs: the kernel records the error word and returns). Cleared by that launch.
+static thread_local uint32_t t_next_spin_limit = 0;
+static thread_local int t_next_skip_loads = 0;
+void set_next_gemm_wait_test(uint32_t spin_limit, int skip_loads) {
+  t_next_spin_limit = spin_limit;
+  t_next_skip_loads = skip_loads;
 }
 
 // a: [nb0, nb1, M, K], b: [nb0, nb1, N, K], both K contiguous; strides in elements.
@@ -184,6 +237,12 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   p.K = (int)K;
   const int es = gemm_elem_size(kind);
   p.num_kb = (int)((K * es + kSlabBytes - 1) / kSlabBytes);
+  // MMAs (32 bytes of K each) that the last slab needs: the zero fill beyond K is not worth multiplying
+  p.last_mmas = (int)((K * es - (int64_t)(p.num_kb - 1) * kSlabBytes + 31) / 32);
+  p.spin_limit = t_next_spin_limit ? t_next_spin_limit : kSpinLimit;
+  p.skip_loads = t_next_skip_loads;
+  t_next_spin_limit = 0;
+  t_next_skip_loads = 0;
   p.tiles_m = (int)tiles_m;
   p.tiles_n = (int)tiles_n;
   p.batch = (int)batch;
@@ -220,7 +279,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   // contractions of 768 with wide outputs (qkv, lm_head), level (+-3 %) for long contractions and heavy epilogues,
   // 40 % slower when a tile is a single K slab (attention scores, K = 64), and 6-9 % slower for the int8 layers,
   // whose short tiles are bound by the epilogue's arithmetic and suffer from the coupling of two CTAs' epilogues.
-  if (fast && bn == 256 && M % (2 * kBM) == 0 && kind != GEMM_I8 && p.num_kb >= 4 && pair_enabled()) {
+  if (fast && bn == 256 && M % (2 * kBM) == 0 && kind != GEMM_I8 && p.num_kb >= 4 && pair_enabled() && !p.skip_loads) {
     CUtensorMap mb_half;
     if (make_operand_map(&mb_half, b, kind, N, K, ldb, nb0, nb1, b_bs0, b_bs1, bn / 2, "B") == PGB_OK) {
       GemmParams pp = p;

@@ -1,8 +1,38 @@
 // Dispatcher of the col reduce family; the kernels are instantiated in reduce_col_*.cu
 // (one translation unit per input type and input count, so they compile in parallel).
+#include <mutex>
+
 #include "reduce_col.cuh"
 
 namespace pgb {
+
+// Ticket counters of the single-launch split reductions. They live in the library image (zero when the module is
+// loaded, and every launch leaves them at zero), one bank per stream so that launches which may overlap never share
+// a counter. A kernel that is killed mid-flight would leave a bank dirty, but by then the context is lost anyway.
+constexpr int kTicketBanks = 16;
+constexpr int kTicketsPerBank = 4096;
+static __device__ unsigned int g_split_tickets[kTicketBanks][kTicketsPerBank];
+
+unsigned int *split_tickets(cudaStream_t stream, int64_t count) {
+  static std::mutex mu;
+  static unsigned int *base[64] = {};
+  static cudaStream_t owner[64][kTicketBanks] = {};
+  static int used[64] = {};
+  if (count > kTicketsPerBank) return nullptr;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) { cudaGetLastError(); return nullptr; }
+  std::lock_guard<std::mutex> lock(mu);
+  if (!base[dev]) {
+    void *p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_split_tickets) != cudaSuccess || !p) { cudaGetLastError(); return nullptr; }
+    base[dev] = static_cast<unsigned int *>(p);
+  }
+  for (int b = 0; b < used[dev]; ++b)
+    if (owner[dev][b] == stream) return base[dev] + (size_t)b * kTicketsPerBank;
+  if (used[dev] == kTicketBanks) return nullptr;
+  owner[dev][used[dev]] = stream;
+  return base[dev] + (size_t)(used[dev]++) * kTicketsPerBank;
+}
 
 extern template int launch_col_typed<float, 1>(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain);
 extern template int launch_col_typed<float, 2>(ReduceJob &j, int jd, bool ident, const ChainProg<float> &chain);

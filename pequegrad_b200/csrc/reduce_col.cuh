@@ -138,6 +138,26 @@ __global__ void __launch_bounds__(256, NIN == 1 ? (((MODE == 0 || MODE == 3) && 
       if (ROP == ROP_ARGMAX) p.part_i[(int64_t)s * p.n_out + o] = a.i;
     }
   }
+  if (p.S == 1 || p.tickets == nullptr) return;  // a finish kernel combines the partials
+  // Split reduction without a second launch: every CTA of a column tile takes a ticket once its partials are
+  // visible; whoever draws the last one combines the S partials of the tile, in split order (the same order, hence
+  // the same bits, as the finish kernel). Nobody waits. atomicInc wraps the counter back to zero for the next launch.
+  __shared__ bool is_last;
+  __threadfence();
+  __syncthreads();
+  if (threadIdx.x == 0) is_last = atomicInc(p.tickets + (batch * ntiles + tile), S - 1) == S - 1;
+  __syncthreads();
+  if (!is_last) return;
+  __threadfence();
+  for (int col = threadIdx.x; col < TILE; col += 256) {
+    const uint32_t jj = tile * TILE + col;
+    if (jj >= J) break;
+    const int64_t o = (int64_t)b0 * p.bout[0] + (int64_t)b1 * p.bout[1] + (int64_t)jj * p.jout;
+    Acc<T, ROP> a;
+    a.init();
+    for (uint32_t ss = 0; ss < S; ++ss) a.merge(__ldcg(p.part_v + (int64_t)ss * p.n_out + o), ROP == ROP_ARGMAX ? __ldcg(p.part_i + (int64_t)ss * p.n_out + o) : 0);
+    finish_output<T>(p.epi, o, a.v, a.i);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -227,6 +247,7 @@ int launch_col_typed(ReduceJob &j, int jd, bool ident, const ChainProg<float> &c
     p.part_i = (int *)((char *)ws_ptr + (size_t)(S * p.n_out) * sizeof(T));
   }
   p.pro = chain;
+  p.tickets = (S > 1) ? split_tickets(j.stream, ctas) : nullptr;
   std::string err = make_epi<T>(j, p.epi);
   if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
 
@@ -253,7 +274,7 @@ int launch_col_typed(ReduceJob &j, int jd, bool ident, const ChainProg<float> &c
   else by_ident(std::integral_constant<int, ROP_ARGMAX>{});
   count_launch();
   int st = check_launch("reduce_col_kernel");
-  if (st == PGB_OK && S > 1) st = launch_reduce_finish(j, p.part_v, p.part_i, S);
+  if (st == PGB_OK && S > 1 && !p.tickets) st = launch_reduce_finish(j, p.part_v, p.part_i, S);
   if (own_ws) cudaFreeAsync(ws_ptr, j.stream);
   return st == PGB_OK ? 1 : st;
 }

@@ -61,6 +61,7 @@ struct ColParams {
   int64_t n_out;
   T *part_v;
   int *part_i;
+  unsigned int *tickets;  // one counter per (batch, column tile) of a split reduction, or null: a finish kernel combines
   ChainProg<T> pro;
   EpiParams<T> epi;
 };
@@ -90,7 +91,12 @@ int fused_reduce_run(const pgb_tensor *in, int n_in, const pgb_tensor *out, int 
                      void *workspace, size_t workspace_bytes, void *stream, bool no_alloc);
 int launch_reduce_row(ReduceJob &j);
 int launch_reduce_col(ReduceJob &j);
+int launch_reduce_plane(ReduceJob &j);
 int launch_reduce_generic(ReduceJob &j);
+// Ticket counters for the single-launch split reduction: `count` zeroed counters that only launches on `stream`
+// use (launches on one stream run one after another, and the last CTA of each tile leaves its counter at zero).
+// Null when `count` is too large or too many streams are in use: the caller then runs the finish kernel.
+unsigned int *split_tickets(cudaStream_t stream, int64_t count);
 // Second stage of split reductions: combines S partials per output.
 int launch_reduce_finish(ReduceJob &j, const void *part_v, const int *part_i, int64_t S);
 

@@ -14,6 +14,9 @@
 
 namespace pgb {
 
+int launch_layernorm_stream_f32(const float *x, float *y, const float *gamma, const float *beta, int64_t rows, int64_t C, float eps,
+                                cudaStream_t stream);
+
 struct RowsParams {
   const void *x;
   void *y;
@@ -494,7 +497,12 @@ int run_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma, const pgb_t
   p.beta = beta ? beta->data : nullptr;
   p.eps = eps;
   if (p.rows == 0 || p.C == 0) return PGB_OK;
-  if (x->dtype == PGB_F32) return rows_launch<float, false>(p, stream);
+  if (x->dtype == PGB_F32) {
+    // many rows: the persistent kernel that streams row blocks through shared memory (rows_stream.cu)
+    const int r = launch_layernorm_stream_f32((const float *)p.x, (float *)p.y, (const float *)p.gamma, (const float *)p.beta, p.rows, p.C, eps, stream);
+    if (r != 0) return r == 1 ? PGB_OK : r;
+    return rows_launch<float, false>(p, stream);
+  }
   if (x->dtype == PGB_F16) return rows_launch<__half, false>(p, stream);
   return rows_launch<__nv_bfloat16, false>(p, stream);
 }

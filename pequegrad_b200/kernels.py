@@ -248,9 +248,23 @@ def qlinear_i8(a: torch.Tensor, w: torch.Tensor, w_scale: torch.Tensor, a_scale:
 
 
 def device_error(reset: bool = True) -> int:
+    """The error word of the kernels' bounded waits: 0, or (role << 16) | block of the first wait that ran out."""
     code = C.c_int(0)
-    L.check(L.lib().pgb_device_error(C.byref(code), 1 if reset else 0))
+    st = L.lib().pgb_device_error(C.byref(code), 1 if reset else 0)
+    if st not in (L.OK, L.ERR_TIMEOUT):
+        L.check(st)
     return code.value
+
+
+def gemm_pair_mode(mode: int) -> int:
+    """0: every GEMM on the one-CTA kernel; 1: CTA pairs where they measured faster (the default). Returns the previous mode."""
+    return L.lib().pgb_gemm_pair_mode(mode)
+
+
+def gemm_wait_drill(polls: int, skip_loads: bool = True) -> None:
+    """The next tensor-core GEMM of this thread polls each wait at most `polls` times; with `skip_loads` its producer
+    loads nothing, so a wait runs out and the kernel reports it through `device_error` (nothing faults or hangs)."""
+    L.check(L.lib().pgb_gemm_wait_drill(polls, 1 if skip_loads else 0))
 
 
 class PreparedReduce:

@@ -5,12 +5,15 @@ dequant + bias + ReLU epilogue and the dynamic activation quantiser bit-exact
 too (same fp32 operations in the same order). f16 / bf16 matmul: fp32
 accumulation, compared with an fp32 reference at 2e-2 (the bound north_star
 states for half precision)."""
+import ctypes as C
+
 import numpy as np
 import pytest
 import torch
 
 import oracle
 from helpers import assert_close
+from pequegrad_b200 import _lib as L
 from pequegrad_b200 import kernels as K
 
 pytestmark = pytest.mark.gpu
@@ -286,19 +289,13 @@ def test_fp64_matmul(shape_a, shape_b):
 
 
 class one_cta_kernel:
-    """Keeps the GEMMs inside the block on the one-CTA kernel (the library reads the switch at every call)."""
+    """Keeps the GEMMs inside the block on the one-CTA kernel (pgb_gemm_pair_mode)."""
 
     def __enter__(self):
-        import os
-        self.old = os.environ.get("PGB_GEMM_PAIR")
-        os.environ["PGB_GEMM_PAIR"] = "0"
+        self.old = K.gemm_pair_mode(0)
 
     def __exit__(self, *exc):
-        import os
-        if self.old is None:
-            del os.environ["PGB_GEMM_PAIR"]
-        else:
-            os.environ["PGB_GEMM_PAIR"] = self.old
+        K.gemm_pair_mode(self.old)
 
 
 def both_kernels(fn):
@@ -369,3 +366,36 @@ def test_cta_pair_kernel_fp32_split_matmul():
     c, = both_kernels(lambda: K.matmul(a, b))
     bound = 1e-5 * (a.abs().double() @ b.abs().double())
     assert bool(((c.double() - a.double() @ b.double()).abs() <= bound).all())
+
+
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """Failure detection without a fault: the next GEMM's producer is told to load nothing and every wait to give up
+    after 1024 polls. The kernel must record who gave up, free its tensor memory and return; while the error word is
+    set further launches do nothing; once the host has read and cleared it the same GEMM is bit-exact again."""
+    g = torch.Generator(device="cuda").manual_seed(41)
+    a = torch.randint(-127, 128, (128, 256), generator=g, device="cuda", dtype=torch.int8)
+    w = torch.randint(-127, 128, (128, 256), generator=g, device="cuda", dtype=torch.int8)
+    ws = torch.rand(128, generator=g, device="cuda") * 0.01 + 0.001
+    want = a.cpu().numpy().astype(np.int32) @ w.cpu().numpy().astype(np.int32).T
+    _, acc = K.qlinear_i8(a, w, ws, a_scale=0.02, want_acc=True, want_out=False)
+    assert np.array_equal(acc.cpu().numpy(), want) and K.device_error() == 0
+    K.gemm_wait_drill(1024, skip_loads=True)
+    _, acc = K.qlinear_i8(a, w, ws, a_scale=0.02, want_acc=True, want_out=False)  # one 128 x 128 tile, block 0
+    torch.cuda.synchronize()  # returns: nothing hangs
+    code = C.c_int(0)
+    st = L.lib().pgb_device_error(C.byref(code), 0)
+    assert st == L.ERR_TIMEOUT and "wait ran out" in L.lib().pgb_last_error().decode()
+    assert (code.value >> 16) in (2, 3) and (code.value & 0xffff) == 0  # the MMA issuer (or the epilogue behind it) of block 0
+    # the word is still set: the next launch returns at once and leaves its output alone
+    sentinel = torch.full((128, 128), 7.0, device="cuda")
+    K.qlinear_i8(a, w, ws, a_scale=0.02, out=sentinel)
+    torch.cuda.synchronize()
+    assert (sentinel == 7).all()
+    assert K.device_error(reset=True) == code.value
+    assert K.device_error() == 0
+    # the drill applied to one launch only, and the device is as good as before
+    _, acc = K.qlinear_i8(a, w, ws, a_scale=0.02, want_acc=True, want_out=False)
+    assert np.array_equal(acc.cpu().numpy(), want) and K.device_error() == 0
+    x = torch.randn((256, 512), generator=g, device="cuda").half()
+    y = torch.randn((384, 512), generator=g, device="cuda").half()
+    assert_close(K.matmul(x, y.T).float().cpu().numpy(), (x.float() @ y.float().T).cpu().numpy(), 2e-2, 2e-2)

@@ -313,3 +313,26 @@ def test_ragged_row_split_across_ctas():
     z[:, 1000001:] = 1e4
     for op in ("argmax", "sum", "max"):
         check_ragged([z[:, :1000001]], op, (), 1e-5, f"ragged split {op}")
+
+
+@pytest.mark.parametrize("shape", [(7, 100, 20), (3, 5, 33, 6), (40, 9, 128), (2, 300, 7), (1000, 12, 3)])
+def test_short_reduced_axis_with_operands_of_opposite_orientation(shape):
+    """x read through a permute of its last two dims against a plain y (the README case's shape of problem): the
+    (kept, reduced) plane of each operand is contiguous, one as [k][j], the other as [j][k]; every op, a chain
+    prologue and an epilogue, odd sizes and planes that 128-bit loads cannot fetch."""
+    rng = np.random.default_rng(31)
+    *lead, J, Kr = shape
+    xbuf = rng.standard_normal(tuple(lead) + (Kr, J)).astype(np.float32)
+    x = np.swapaxes(xbuf, -1, -2)  # logical [.., J, K], stored [.., K, J]
+    y = rng.standard_normal(shape).astype(np.float32)
+    ax = len(shape) - 1
+    pro = [("LOAD", 0), ("IMM", 0, 0, 0, 2.0), ("ADD", 0, 1), ("LOAD", 1), ("MUL", 2, 3)]
+    epi = [("ACC",), ("IMM", 0, 0, 0, 3.0), ("MUL", 0, 1)]
+    xd, yd = dev(x), dev(y)
+    out_shape = K.reduced_shape(shape, [ax], False)
+    od = torch.empty(out_shape, device="cuda")
+    assert K.describe_reduce([K.desc(xd), K.desc(yd)], K.desc(od), L.SUM, [ax], pro).startswith("plane")
+    for op in ("sum", "max", "mean"):
+        run_case([x, y], op, [ax], False, pro, epi, what=f"plane {shape} {op}")
+        run_case([y, x], op, [ax], True, pro, (), what=f"plane swapped {shape} {op}")
+    run_case([x, y], "argmax", [ax], False, pro, (), what=f"plane {shape} argmax")
