@@ -1,14 +1,18 @@
-// Plane reduce: a SHORT reduced axis k next to the innermost kept axis j, where the (j, k) plane of every input is
-// one contiguous block of memory but the inputs disagree on its orientation: [k][j] for one (j contiguous), [j][k]
-// for another (k contiguous). The README fusion case of the reference is exactly this, x read through
-// permute(0, 2, 1) against a plain y (README.md:59-63): no single thread mapping reads both operands coalesced, so
-// the row and column kernels refuse it, and the generated kernel of the reference reads y with an 80-byte stride
-// between threads (README.md:110-111).
+// Short-axis reduce, one thread per output: a SHORT reduced axis k (at most 128 elements) over operands that disagree
+// on which axis is contiguous. The README fusion case of the reference is exactly this: x read through
+// permute(0, 2, 1), so that the innermost KEPT axis j is its contiguous one, against a plain y whose contiguous axis
+// is k (README.md:59-63). No single thread mapping reads both with 128-byte requests, so the row and column kernels
+// refuse it, and the generic kernel pays 64-bit div / mod and the interpreter per element.
 //
-// Here a CTA takes G whole planes of every input (all other kept dims are a batch), copies them to shared memory
-// with coalesced 128-bit loads in memory order (the [j][k] orientation with an odd row pitch, so that the strided
-// reads below hit distinct banks), and then thread (g, j) walks k: prologue chain, accumulate, epilogue, one
-// coalesced store. Each input is read once, in full lines.
+// Here thread (plane, j) walks k with every address precomputed: 32-bit offsets, four k steps in flight (eight
+// loads for two inputs), 128-bit loads for an operand whose k axis is contiguous, the prologue as a decoded chain.
+// Consecutive threads read consecutive j of the j-contiguous operand (full requests) and neighbouring short rows of
+// the k-contiguous one, whose sectors the L1 serves on the following steps; every byte is fetched from L2 once.
+// A shared-memory staging of whole (j, k) planes was tried first and took 26 us on the README case, three times
+// the reference's own generated kernel on the same GPU (8 us, thread per output like this one): the problem fits
+// the L2, so the staging's barrier and serialised copy loop cost more than the uncoalesced requests they avoid.
+#include <type_traits>
+
 #include "reduce_common.cuh"
 #include "vec.cuh"
 
@@ -16,171 +20,124 @@ namespace pgb {
 
 namespace {
 
-constexpr int kPlaneThreads = 256;
-constexpr int kPlaneSmem = 48 * 1024;
+constexpr int kShortThreads = 256;
 
 template <int NIN>
-struct PlaneParams {
+struct ShortParams {
   const float *in[NIN];
-  int kj[NIN];             // 1: plane stored [k][j] (j contiguous); 0: stored [j][k] (k contiguous)
-  int vec[NIN];            // planes can be fetched with 128-bit loads
-  int64_t bstr[NIN][2];    // element strides of the two outer kept dims
-  int64_t bsize1;          // extent of the inner one of them
-  int64_t nplanes;
-  int J, K, G, pitch;      // pitch: shared-memory row pitch of a [j][k] plane (odd)
+  int64_t bstr[NIN][2];  // element strides of the two outer kept dims
+  int32_t jstr[NIN], kstr[NIN];
+  int vec4[NIN];         // k contiguous and every row 16-byte aligned: four k steps per load
+  int64_t bsize1;        // extent of the inner outer dim
+  int64_t n_out;
+  int J, K;
   ChainProg<float> pro;
   EpiParams<float> epi;
 };
 
-template <int NIN, int ROP>
-__global__ void __launch_bounds__(kPlaneThreads) reduce_plane_kernel(const __grid_constant__ PlaneParams<NIN> p) {
-  extern __shared__ __align__(16) float sm[];
-  const int J = p.J, K = p.K, G = p.G, JK = J * K;
-  const int plane_words[2] = {J * p.pitch, JK};  // by orientation: [j][k] padded, [k][j] as in memory
-  const int64_t plane0 = (int64_t)blockIdx.x * G;
-  const int g_here = (int)min((int64_t)G, p.nplanes - plane0);
-  float *base_sm[NIN];
-  {
-    float *cur = sm;
+template <int NIN, int ROP, bool LITE>
+__global__ void __launch_bounds__(kShortThreads, 4) reduce_short_kernel(const __grid_constant__ ShortParams<NIN> p) {
+  const int64_t o = (int64_t)blockIdx.x * kShortThreads + threadIdx.x;
+  if (o >= p.n_out) return;
+  const int J = p.J, K = p.K;
+  const int64_t plane = o / J;
+  const int j = (int)(o - plane * J);
+  const int64_t b1 = plane % p.bsize1, b0 = plane / p.bsize1;
+  const float *base[NIN];
+#pragma unroll
+  for (int k = 0; k < NIN; ++k) base[k] = p.in[k] + b0 * p.bstr[k][0] + b1 * p.bstr[k][1] + (int64_t)j * p.jstr[k];
+  ChainRegs<float> cr;
+  if (LITE) chain_decode<float>(p.pro, cr);
+  Acc<float, ROP> acc;
+  acc.init();
+#pragma unroll 1
+  for (int k0 = 0; k0 < K; k0 += 4) {
+    float w[NIN][4], run[4];
 #pragma unroll
     for (int k = 0; k < NIN; ++k) {
-      base_sm[k] = cur;
-      cur += (size_t)G * ((plane_words[p.kj[k]] + 3) & ~3);
-    }
-  }
-  // stage the planes
-#pragma unroll
-  for (int k = 0; k < NIN; ++k) {
-    const int pw = (plane_words[p.kj[k]] + 3) & ~3;
-    for (int g = 0; g < g_here; ++g) {
-      const int64_t pl = plane0 + g;
-      const int64_t b1 = pl % p.bsize1, b0 = pl / p.bsize1;
-      const float *src = p.in[k] + b0 * p.bstr[k][0] + b1 * p.bstr[k][1];
-      float *dst = base_sm[k] + (size_t)g * pw;
-      if (p.vec[k]) {
-        for (int v = threadIdx.x; v < JK / 4; v += kPlaneThreads) {
-          const float4 t = __ldg(reinterpret_cast<const float4 *>(src) + v);
-          if (p.kj[k]) {
-            reinterpret_cast<float4 *>(dst)[v] = t;
-          } else {
-            const float e[4] = {t.x, t.y, t.z, t.w};
-            const int m = v * 4;
-            int jj = m / K, kk = m - jj * K;
-#pragma unroll
-            for (int i = 0; i < 4; ++i) {
-              dst[jj * p.pitch + kk] = e[i];
-              if (++kk == K) { kk = 0; ++jj; }
-            }
-          }
-        }
+      if (p.vec4[k]) {
+        const float4 t = __ldg(reinterpret_cast<const float4 *>(base[k] + k0));  // K % 4 == 0 here: never past the row
+        w[k][0] = t.x; w[k][1] = t.y; w[k][2] = t.z; w[k][3] = t.w;
       } else {
-        for (int m = threadIdx.x; m < JK; m += kPlaneThreads) {
-          const float t = __ldg(src + m);
-          if (p.kj[k]) dst[m] = t;
-          else { const int jj = m / K; dst[jj * p.pitch + (m - jj * K)] = t; }
-        }
+#pragma unroll
+        for (int e = 0; e < 4; ++e) w[k][e] = __ldg(base[k] + (int64_t)min(k0 + e, K - 1) * p.kstr[k]);
       }
     }
+    if (LITE) chain_eval_fast<float, NIN, 4>(cr, w, run);
+    else chain_eval<float, NIN, 4>(p.pro, w, run);
+#pragma unroll
+    for (int e = 0; e < 4; ++e)
+      if (k0 + e < K) acc.add_stream(run[e], k0 + e);
   }
-  __syncthreads();
-  // thread -> (plane of the group, j); J > 256 loops over j
-  const int per = G > 1 ? J : kPlaneThreads;
-  for (int j0 = 0; j0 < J; j0 += per) {
-    const int g = G > 1 ? (int)threadIdx.x / J : 0;
-    const int j = G > 1 ? (int)threadIdx.x - g * J : j0 + (int)threadIdx.x;
-    if (g >= g_here || j >= J) continue;
-    Acc<float, ROP> acc;
-    acc.init();
-    const float *pl[NIN];
-#pragma unroll
-    for (int k = 0; k < NIN; ++k) pl[k] = base_sm[k] + (size_t)g * ((plane_words[p.kj[k]] + 3) & ~3);
-    for (int k0 = 0; k0 < K; k0 += 4) {
-      float w[NIN][4], run[4];
-#pragma unroll
-      for (int k = 0; k < NIN; ++k) {
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          const int kk = min(k0 + e, K - 1);
-          w[k][e] = p.kj[k] ? pl[k][kk * J + j] : pl[k][j * p.pitch + kk];
-        }
-      }
-      chain_eval<float, NIN, 4>(p.pro, w, run);
-#pragma unroll
-      for (int e = 0; e < 4; ++e)
-        if (k0 + e < K) acc.add_stream(run[e], k0 + e);
-    }
-    finish_output<float>(p.epi, (plane0 + g) * J + j, acc.v, acc.i);
-  }
+  finish_output<float>(p.epi, o, acc.v, acc.i);
 }
 
 template <int NIN>
-int launch_plane(ReduceJob &j, const ChainProg<float> &chain) {
+int launch_short(ReduceJob &j, const ChainProg<float> &chain) {
   const CanonReduce &c = j.c;
-  PlaneParams<NIN> p{};
+  ShortParams<NIN> p{};
   const int jd = c.nk - 1;
   const int64_t J = c.ksize[jd], K = c.rsize[0];
   p.J = (int)J;
   p.K = (int)K;
-  p.pitch = (int)(K | 1);
-  size_t per_group = 0;
-  bool mixed = false;
+  p.n_out = c.n_out;
+  p.bsize1 = jd >= 1 ? c.ksize[jd - 1] : 1;
   for (int k = 0; k < NIN; ++k) {
     const int64_t sj = c.kin[k][jd], sk = c.rin[k][0];
-    if (sj == 1 && sk == J) p.kj[k] = 1;
-    else if (sj == K && sk == 1) p.kj[k] = 0;
-    else return 0;
-    if (p.kj[k] != p.kj[0]) mixed = true;
+    if (sj > 2147483647LL / 4 || sk > 2147483647LL / 256) return 0;
     p.in[k] = (const float *)j.in[k].data;
-    bool vec = (J * K) % 4 == 0 && (reinterpret_cast<uintptr_t>(p.in[k]) & 15) == 0;
+    p.jstr[k] = (int32_t)sj;
+    p.kstr[k] = (int32_t)sk;
+    bool v4 = sk == 1 && K % 4 == 0 && sj % 4 == 0 && (reinterpret_cast<uintptr_t>(p.in[k]) & 15) == 0;
     for (int q = 0; q < 2; ++q) {
       const int d = jd - 2 + q;
       p.bstr[k][q] = d >= 0 ? c.kin[k][d] : 0;
-      if (d >= 0 && c.kin[k][d] % 4) vec = false;
+      if (d >= 0 && c.kin[k][d] % 4) v4 = false;
     }
-    p.vec[k] = vec ? 1 : 0;
-    per_group += (size_t)(((p.kj[k] ? J * K : J * p.pitch) + 3) & ~3) * sizeof(float);
+    p.vec4[k] = v4 ? 1 : 0;
   }
-  // one orientation for all inputs is the row or the column kernel's case
-  if (!mixed) return 0;
-  p.bsize1 = jd >= 1 ? c.ksize[jd - 1] : 1;
-  p.nplanes = c.n_out / J;
-  int G = J >= kPlaneThreads ? 1 : (int)(kPlaneThreads / J);
-  while (G > 1 && per_group * G > (size_t)kPlaneSmem) --G;
-  if (per_group * G > (size_t)kPlaneSmem) return 0;
-  p.G = G;
-  const int64_t grid = (p.nplanes + G - 1) / G;
+  const int64_t grid = (c.n_out + kShortThreads - 1) / kShortThreads;
   if (grid > 2147483647LL) return 0;
   char buf[160];
-  snprintf(buf, sizeof buf, "plane nin=%d J=%lld K=%lld planes=%lld per_cta=%d grid=%lld", NIN, (long long)J, (long long)K, (long long)p.nplanes, G,
-           (long long)grid);
+  snprintf(buf, sizeof buf, "short nin=%d J=%lld K=%lld outputs=%lld grid=%lld %s", NIN, (long long)J, (long long)K, (long long)c.n_out, (long long)grid,
+           chain.lite ? "chain" : "chain-full");
   j.desc = buf;
   j.ws_needed = 0;
   if (j.dry_run) return 1;
   p.pro = chain;
   std::string err = make_epi<float>(j, p.epi);
   if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
-  const size_t smem = per_group * G;
-  if (j.rop == ROP_SUM) reduce_plane_kernel<NIN, ROP_SUM><<<(unsigned)grid, kPlaneThreads, smem, j.stream>>>(p);
-  else if (j.rop == ROP_MAX) reduce_plane_kernel<NIN, ROP_MAX><<<(unsigned)grid, kPlaneThreads, smem, j.stream>>>(p);
-  else reduce_plane_kernel<NIN, ROP_ARGMAX><<<(unsigned)grid, kPlaneThreads, smem, j.stream>>>(p);
+  auto go = [&](auto rop_c) {
+    constexpr int ROP = decltype(rop_c)::value;
+    if (chain.lite) reduce_short_kernel<NIN, ROP, true><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    else reduce_short_kernel<NIN, ROP, false><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+  };
+  if (j.rop == ROP_SUM) go(std::integral_constant<int, ROP_SUM>{});
+  else if (j.rop == ROP_MAX) go(std::integral_constant<int, ROP_MAX>{});
+  else go(std::integral_constant<int, ROP_ARGMAX>{});
   count_launch();
-  const int st = check_launch("reduce_plane_kernel");
+  const int st = check_launch("reduce_short_kernel");
   return st == PGB_OK ? 1 : st;
 }
 
 }  // namespace
 
-// 1 launched (or planned), 0 not this kernel's case, < 0 error.
+// 1 launched (or planned), 0 not this kernel's case, < 0 error. Takes what the row and column kernels refused: two
+// fp32 operands, one short reduced axis, a chain prologue, at most three kept dims; and only when one operand's
+// innermost kept axis is its contiguous one (so that the requests of a warp are whole lines for at least that one).
 int launch_reduce_plane(ReduceJob &j) {
   const CanonReduce &c = j.c;
   if (j.cdtype != PGB_F32 || c.n_in != 2 || c.nr != 1 || c.nk < 1 || c.nk > 3) return 0;
-  for (int k = 0; k < c.n_in; ++k)
+  bool any_j1 = false;
+  for (int k = 0; k < c.n_in; ++k) {
     if (j.in[k].dtype != PGB_F32) return 0;
+    if (c.kin[k][c.nk - 1] == 1) any_j1 = true;
+  }
   const int64_t J = c.ksize[c.nk - 1], K = c.rsize[0];
-  if (K < 2 || K > 128 || J < 8 || J * K > 8192) return 0;
+  if (!any_j1 || K < 2 || K > 128 || J < 8) return 0;
   ChainProg<float> chain;
   if (!to_chain<float>(j.pro, j.n_pro, chain)) return 0;
-  return launch_plane<2>(j, chain);
+  return launch_short<2>(j, chain);
 }
 
 }  // namespace pgb

@@ -9,6 +9,8 @@
 // come are in flight while the current one is computed and stored, so the DRAM queue never drains.
 // The arithmetic is that of layernorm_warp_kernel (and of the composite, pequegrad/ops.py:515-551): mean,
 // biased variance of the deviations, eps before the square root.
+#include <cstdlib>
+
 #include "gemm_ptx.cuh"
 #include "reduce_common.cuh"
 
@@ -163,7 +165,12 @@ __global__ void __launch_bounds__(kStreamThreads, 2) layernorm_stream_kernel(con
 
 template <int NV>
 int launch_stream(const StreamParams &p, int grid, size_t smem, cudaStream_t stream) {
-  static cudaError_t attr_err = cudaFuncSetAttribute(layernorm_stream_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 110 * 1024);
+  static cudaError_t attr_err = [] {
+    cudaError_t e = cudaFuncSetAttribute(layernorm_stream_kernel<NV>, cudaFuncAttributeMaxDynamicSharedMemorySize, 220 * 1024);
+    // two CTAs of ~100 KB per SM only fit when the L1 / shared split leans fully to shared memory
+    if (e == cudaSuccess) e = cudaFuncSetAttribute(layernorm_stream_kernel<NV>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    return e;
+  }();
   if (attr_err != cudaSuccess) return 0;
   layernorm_stream_kernel<NV><<<grid, kStreamThreads, smem, stream>>>(p);
   count_launch();
@@ -180,13 +187,17 @@ int launch_layernorm_stream_f32(const float *x, float *y, const float *gamma, co
   if (C % 4 != 0 || C < 128 || C > 1024 || rows < 2048) return 0;
   if (!a16(x) || !a16(y) || (gamma && !a16(gamma)) || (beta && !a16(beta))) return 0;
   const size_t blk = (size_t)C * 4 * kRowsPerBlock;
-  int stages = (int)((100 * 1024) / blk);  // two CTAs per SM: about 100 KB of ring each
+  const char *var = getenv("PGB_LN_VARIANT");
+  const int variant = var ? atoi(var) : 1;
+  if (variant == 0 || variant >= 3) return 0;
+  const int per_sm = variant == 2 ? 1 : 2;
+  int stages = (int)(((variant == 2 ? 200 : 100) * 1024) / blk);  // two CTAs per SM: about 100 KB of ring each
   if (stages > 6) stages = 6;
   if (stages < 2) return 0;
   StreamParams p{x, y, gamma, beta, rows, (int)C, stages, eps, gemm_error_word()};
   if (!p.err) return 0;
   const int64_t nblk = (rows + kRowsPerBlock - 1) / kRowsPerBlock;
-  int64_t grid = (int64_t)sm_count() * 2;
+  int64_t grid = (int64_t)sm_count() * per_sm;
   if (grid > nblk) grid = nblk;
   const size_t smem = 128 + (size_t)stages * blk;
   const int nv = (int)((C + 127) / 128);

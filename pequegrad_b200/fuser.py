@@ -8,7 +8,12 @@ immediates (csrc/compiler/ir.cpp:235-255), and the region is lowered to the
 linear program the kernels take (the counterpart of `graph_to_ir`,
 csrc/compiler/ir.cpp:839-1286). Unlike the reference there is no
 "fewer than 1024 reduced elements" refusal and shapes are runtime data, so one
-compiled kernel serves every shape.
+compiled kernel serves every shape. The "one reduce per kernel" rule is lifted
+for the two multi-reduce chains that matter on this path: a softmax or a
+LayerNorm written from primitives is recognised in the graph and runs as ONE
+row kernel. Outputs of one traced call that are elementwise results of the same
+shape come out of one multi-output kernel (the reference's sibling outputs,
+csrc/compiler/scheduler.cpp:229-256).
 
 Two graph rewrites of the reference run here as well:
   * the fused-linear pattern (`recursive_fused_linear`, csrc/compiler/compile.hpp;
@@ -21,6 +26,7 @@ Two graph rewrites of the reference run here as well:
 """
 from __future__ import annotations
 
+import builtins
 import contextlib
 
 import torch
@@ -129,17 +135,155 @@ def _linear(mm, bias, act, mode, out_dtype):
     return K.matmul(a, b, bias=bias_buf, act=act, out_dtype=out_dtype)
 
 
+def _const(node):
+    """The value of a constant seen through broadcasts, else None."""
+    node = _strip_broadcast(node)
+    return node.attrs["value"] if node.op == "fill" else None
+
+
+def _last_dims(axes, nd) -> bool:
+    return len(axes) >= 1 and tuple(sorted(axes)) == tuple(range(nd - len(axes), nd))
+
+
+def _match_softmax(node):
+    """x when `node` is the softmax composite over the last axis written from primitives,
+    exp(x - max(x)) / sum(exp(x - max(x))) (pequegrad/ops.py:259-267): two reduces and three elementwise passes that
+    the reference's scheduler can only split (one reduce per kernel, csrc/compiler/scheduler.cpp:62-66) and that the
+    row kernel computes in one read and one write of the tensor."""
+    if node.op != "div" or node._buf is not None:
+        return None
+    e, den = node.args
+    s = _strip_broadcast(den)
+    if s.op != "sum" or s._buf is not None or s.args[0] is not e or not s.attrs["keepdims"] or tuple(s.attrs["axes"]) != (e.ndim - 1,):
+        return None
+    if e.op != "exp" or e._buf is not None or e.args[0].op != "sub" or e.args[0]._buf is not None:
+        return None
+    x, mb = e.args[0].args
+    m = _strip_broadcast(mb)
+    if m.op != "max_reduce" or m._buf is not None or m.args[0] is not x or not m.attrs["keepdims"] or tuple(m.attrs["axes"]) != (x.ndim - 1,):
+        return None
+    if x.dtype not in (torch.float32, torch.float16, torch.bfloat16) or x.ndim < 1:
+        return None
+    return x
+
+
+def _match_centered(node):
+    """(x, mean node) when `node` is x - mean(x, last dims, keepdim)."""
+    if node.op != "sub" or node._buf is not None:
+        return None
+    x, mb = node.args
+    mu = _strip_broadcast(mb)
+    if mu.op != "mean" or mu._buf is not None or mu.args[0] is not x or not mu.attrs["keepdims"] or not _last_dims(mu.attrs["axes"], x.ndim):
+        return None
+    return x, mu
+
+
+def _match_layernorm(node):
+    """(x, weight, bias, eps, n) when `node` is the LayerNorm composite written from primitives,
+    (x - mean) / (var + eps) ** 0.5 [* weight] [+ bias] with var = sum((x - mean) ** 2) / n over the last dims
+    (pequegrad/ops.py:515-551, 480-501): three reduces in the reference's terms, one row kernel here."""
+    weight = bias = None
+    n0 = node
+    if n0.op == "add" and n0._buf is None:
+        for a, b in (n0.args, n0.args[::-1]):
+            base = _strip_broadcast(b)
+            if base.op not in _ELEMENTWISE and base.op not in _REDUCES and a.op in ("mul", "div") and a._buf is None:
+                cand = (a, base)
+                break
+        else:
+            return None
+        n0, bias = cand
+    if n0.op == "mul" and n0._buf is None:
+        for a, b in (n0.args, n0.args[::-1]):
+            base = _strip_broadcast(b)
+            if base.op not in _ELEMENTWISE and base.op not in _REDUCES and a.op == "div" and a._buf is None:
+                cand = (a, base)
+                break
+        else:
+            return None
+        n0, weight = cand
+    if n0.op != "div" or n0._buf is not None:
+        return None
+    num, den = n0.args
+    c = _match_centered(num)
+    if c is None:
+        return None
+    x, mu = c
+    sd = _strip_broadcast(den)
+    if sd.op != "pow" or sd._buf is not None or _const(sd.args[1]) != 0.5:
+        return None
+    ve = sd.args[0]
+    if ve.op != "add" or ve._buf is not None or _const(ve.args[1]) is None:
+        return None
+    eps, var = _const(ve.args[1]), ve.args[0]
+    if var.op != "div" or var._buf is not None or _const(var.args[1]) is None:
+        return None
+    n, ss = _const(var.args[1]), var.args[0]
+    if ss.op != "sum" or ss._buf is not None or not ss.attrs["keepdims"] or tuple(sorted(ss.attrs["axes"])) != tuple(sorted(mu.attrs["axes"])):
+        return None
+    sq = ss.args[0]
+    if sq.op != "pow" or sq._buf is not None or _const(sq.args[1]) != 2.0:
+        return None
+    c2 = _match_centered(sq.args[0])
+    if c2 is None or c2[0] is not x:
+        return None
+    k = len(mu.attrs["axes"])
+    count = 1
+    for d in x.shape[x.ndim - k:]:
+        count *= d
+    if float(n) != float(count) or x.dtype not in (torch.float32, torch.float16, torch.bfloat16):
+        return None
+    for t in (weight, bias):
+        if t is not None and (tuple(t.shape[-k:]) != tuple(x.shape[-k:]) or any(d != 1 for d in t.shape[:-k]) or t.dtype != x.dtype):
+            return None
+    return x, weight, bias, float(eps), count
+
+
+def _rows_of(buf: torch.Tensor, n: int) -> torch.Tensor:
+    """`buf` as contiguous rows of n (a copy through the elementwise kernel only when the view is not contiguous)."""
+    if not buf.is_contiguous():
+        (buf,) = K.fused_elementwise([buf], [("LOAD", 0)])
+    return buf.reshape(-1, n)
+
+
 def _emit_leaf(node: T.Tensor, fuse: bool) -> torch.Tensor:
     evaluate(node, fuse)
     return node._buf
 
 
-class _Region:
-    """Collects the program and the leaf tensors of one fused region."""
+def _subtree_size(node, shape, memo=None) -> int:
+    """Instructions the fusable subtree under `node` would add to a region (shared nodes counted once)."""
+    memo = {} if memo is None else memo
+    if id(node) in memo:
+        return 0
+    memo[id(node)] = True
+    if node._buf is not None or node.op not in _ELEMENTWISE or node.shape != shape or node.op == "fill":
+        return 1
+    return 1 + builtins.sum(_subtree_size(a, shape, memo) for a in node.args)
 
-    def __init__(self, shape, fuse):
+
+class _Region:
+    """Collects the program and the leaf tensors of one fused region. The C ABI takes at most `max_instrs`
+    instructions and `max_inputs` operands per region: a node is fused only if, with everything under it, the
+    region still fits; otherwise its largest operand subtrees are cut off into leaves of their own (which are
+    evaluated as separate regions), largest first, until it does."""
+
+    def __init__(self, shape, fuse, max_instrs=MAX_REGION_INSTRS, max_inputs=L.MAX_INPUTS):
         self.shape, self.fuse = tuple(shape), fuse
+        self.max_instrs, self.max_inputs = max_instrs, max_inputs
         self.prog, self.inputs, self.memo, self.leaf_ix = [], [], {}, {}
+
+    def _snapshot(self):
+        return len(self.prog), len(self.inputs), dict(self.memo), dict(self.leaf_ix)
+
+    def _restore(self, snap):
+        n_prog, n_in, memo, leaf_ix = snap
+        del self.prog[n_prog:]
+        del self.inputs[n_in:]
+        self.memo, self.leaf_ix = memo, leaf_ix
+
+    def fits(self) -> bool:
+        return len(self.prog) <= self.max_instrs and len(self.inputs) <= self.max_inputs
 
     def leaf(self, node):
         buf = _emit_leaf(node, self.fuse)
@@ -150,7 +294,12 @@ class _Region:
         self.prog.append(("LOAD", self.leaf_ix[key]))
         return len(self.prog) - 1
 
-    def emit(self, node, stop=None):
+    def _fusable(self, node) -> bool:
+        if node._buf is not None or node.op not in _ELEMENTWISE or node.shape != self.shape:
+            return False
+        return node.op != "astype" or node.attrs["dtype"] in _CAST
+
+    def emit(self, node, stop=None, forced_leaves=frozenset()):
         """Value index of `node`; `stop` is the reduce node whose result reads as ACC."""
         if id(node) in self.memo:
             return self.memo[id(node)]
@@ -162,28 +311,39 @@ class _Region:
             ix = len(self.prog) - 1
         elif node.op == "broadcast_to" and node.args[0].op == "fill":
             ix = self.emit(node.args[0], stop)  # a constant seen through a broadcast is still an immediate
-        elif _match_linear(node, self.fuse) is not None:
-            return self._as_leaf(node)  # act(x @ w + bias) inside a larger region: bias and activation stay in the GEMM
-        elif (node.op in _ELEMENTWISE and node._buf is None and node.shape == self.shape and len(self.prog) < MAX_REGION_INSTRS
-              and (len(self.inputs) < L.MAX_INPUTS - 1)):
-            if node.op in T.BINARY:
-                a, b = self.emit(node.args[0], stop), self.emit(node.args[1], stop)
-                self.prog.append((T.BINARY[node.op], a, b))
-            elif node.op in T.UNARY:
-                self.prog.append((T.UNARY[node.op], self.emit(node.args[0], stop)))
-            elif node.op == "where":
-                c, a, b = (self.emit(t, stop) for t in node.args)
-                self.prog.append(("WHERE", c, a, b))
-            else:  # astype
-                if node.attrs["dtype"] not in _CAST:
-                    return self._as_leaf(node)
-                a = self.emit(node.args[0], stop)
-                self.prog.append((_CAST[node.attrs["dtype"]], a))
-            ix = len(self.prog) - 1
-        else:
+        elif id(node) in forced_leaves or not self._fusable(node) or _match_linear(node, self.fuse) is not None:
+            # (act(x @ w + bias) inside a larger region: bias and activation stay in the GEMM)
             return self._as_leaf(node)
+        else:
+            return self._emit_op(node, stop)
         self.memo[id(node)] = ix
         return ix
+
+    def _emit_op(self, node, stop):
+        forced = set()
+        while True:
+            snap = self._snapshot()
+            ops = [self.emit(a, stop, frozenset(forced)) for a in node.args]
+            if node.op in T.BINARY:
+                self.prog.append((T.BINARY[node.op], ops[0], ops[1]))
+            elif node.op in T.UNARY:
+                self.prog.append((T.UNARY[node.op], ops[0]))
+            elif node.op == "where":
+                self.prog.append(("WHERE", ops[0], ops[1], ops[2]))
+            else:  # astype
+                self.prog.append((_CAST[node.attrs["dtype"]], ops[0]))
+            if self.fits():
+                ix = len(self.prog) - 1
+                self.memo[id(node)] = ix
+                return ix
+            # too large: cut the biggest operand subtree that is still fused off into a leaf and try again
+            self._restore(snap)
+            cands = [a for a in node.args if id(a) not in forced and a is not stop and self._fusable(a)]
+            if not cands:
+                if snap[0] == 0:
+                    raise RuntimeError("fuser: a single operation does not fit the region limits")  # cannot happen: <= 4 instructions
+                return self._as_leaf(node)  # the region was already nearly full: this node starts a region of its own
+            forced.add(id(builtins.max(cands, key=lambda a: _subtree_size(a, self.shape))))
 
     def _as_leaf(self, node):
         ix = self.leaf(node)
@@ -193,44 +353,78 @@ class _Region:
 
 def _find_reduce(node, shape, seen=None):
     """First fusable reduce reachable from `node` through elementwise nodes of the output shape."""
-    if node._buf is not None:
+    seen = set() if seen is None else seen
+    if id(node) in seen or node._buf is not None:
         return None
+    seen.add(id(node))
     if node.op in ("sum", "mean", "max_reduce") and node.shape == shape:
         return node
     if node.op in _ELEMENTWISE and node.shape == shape:
         for a in node.args:
-            r = _find_reduce(a, shape)
+            r = _find_reduce(a, shape, seen)
             if r is not None:
                 return r
-    if node.op == "broadcast_to" and node.args[0].op == "fill":
-        return None
     return None
+
+
+def _eval_elementwise(nodes, mode):
+    """One fused elementwise kernel for `nodes` (same shape; more than one = the sibling outputs of a region,
+    csrc/compiler/scheduler.cpp:229-256). Returns the nodes that did not fit and must be evaluated on their own."""
+    reg = _Region(nodes[0].shape, mode)
+    outs, left = [], []
+    for n in nodes:
+        snap = reg._snapshot()
+        try:
+            ix = reg.emit(n)
+        except RuntimeError:
+            ix = None
+        if ix is None or not reg.fits() or len(outs) >= 4:
+            reg._restore(snap)
+            left.append(n)
+            continue
+        outs.append((n, ix))
+    if not outs:
+        return left
+    bufs = K.fused_elementwise(reg.inputs, reg.prog, shape=nodes[0].shape, out_dtypes=[n.dtype for n, _ in outs], out_vals=[ix for _, ix in outs])
+    for (n, _), b in zip(outs, bufs):
+        n._buf = b
+    return left
+
+
+def _siblings(node):
+    """Other outputs of the same traced call that can share a kernel with `node`: unevaluated elementwise results of
+    the same shape with no reduce of their own."""
+    sib = [s for s in getattr(node, "_siblings", ()) if s is not node and s._buf is None and s.shape == node.shape
+           and s.op in _ELEMENTWISE and s.op != "fill" and _find_reduce(s, s.shape) is None and _match_linear(s, JIT) is None]
+    return sib[:3]
 
 
 def _eval_fused(node: T.Tensor, mode: int = JIT):
     red = node if node.op in _REDUCES else _find_reduce(node, node.shape)
-    if red is None:
-        reg = _Region(node.shape, mode)
-        reg.emit(node)
-        if not reg.inputs:  # constants only
-            (out,) = K.fused_elementwise([], reg.prog, shape=node.shape, out_dtypes=[node.dtype])
-        else:
-            (out,) = K.fused_elementwise(reg.inputs, reg.prog, shape=node.shape, out_dtypes=[node.dtype])
-        node._buf = out
-        return
-    x = red.args[0]
-    pro = _Region(x.shape, mode)
-    pro.emit(x)
-    epi_prog, epi_inputs = [], []
-    if red is not node:
-        epi = _Region(node.shape, mode)
-        epi.emit(node, stop=red)
-        epi_prog = epi.prog
-        keep = K.reduced_shape(x.shape, red.attrs["axes"], True)
-        epi_inputs = [b.reshape(keep) if b.dim() != len(keep) else b for b in epi.inputs]
-    out = K.fused_reduce(pro.inputs, T.REDUCE[red.op], red.attrs["axes"], red.attrs["keepdims"], pro.prog, epi_prog, epi_inputs,
-                         out_dtype=node.dtype)
-    node._buf = out.view(node.shape)
+    if red is not None:
+        x = red.args[0]
+        pro = _Region(x.shape, mode)
+        pro.emit(x)
+        epi_prog, epi_inputs = [], []
+        fused_epilogue = True
+        if red is not node:
+            epi = _Region(node.shape, mode)
+            epi.emit(node, stop=red)
+            # the reduce may have been cut out of the epilogue by the region limits: then it is a plain leaf of `node`
+            fused_epilogue = any(i[0] == "ACC" for i in epi.prog)
+            epi_prog = epi.prog
+            keep = K.reduced_shape(x.shape, red.attrs["axes"], True)
+            epi_inputs = [b.reshape(keep) if b.dim() != len(keep) else b for b in epi.inputs]
+        if fused_epilogue and red._buf is None:
+            out = K.fused_reduce(pro.inputs, T.REDUCE[red.op], red.attrs["axes"], red.attrs["keepdims"], pro.prog, epi_prog, epi_inputs,
+                                 out_dtype=node.dtype)
+            node._buf = out.view(node.shape)
+            return
+    left = _eval_elementwise([node] + _siblings(node), mode)
+    for n in left:
+        if n is node:
+            raise RuntimeError("fuser: could not place the output in a region")
+    # siblings that did not fit are evaluated when they are asked for
 
 
 def _eval_eager(node: T.Tensor):
@@ -272,12 +466,15 @@ def evaluate(node: T.Tensor, fuse: bool = False):
     elif node.op == "attention":
         q, k, v = (_emit_leaf(a, fuse) for a in node.args)
         node._buf = K.attention(q, k, v, scale=node.attrs["scale"], causal=node.attrs["causal"])
-    elif node.op == "softmax_rows":
-        node._buf = K.softmax_rows(_emit_leaf(node.args[0], fuse).contiguous(), node.attrs.get("causal", False))
-    elif node.op == "layernorm_rows":
-        x, g, b = (None if a is None else _emit_leaf(a, fuse) for a in node.attrs["operands"])
-        rows = x.reshape(-1, node.attrs["n"])
-        node._buf = K.layernorm_rows(rows, g if g is None else g.reshape(-1), b if b is None else b.reshape(-1), node.attrs["eps"]).view(node.shape)
+    elif fuse and _match_softmax(node) is not None:
+        # a softmax written from primitives: one row kernel instead of a region per reduce
+        x = _emit_leaf(_match_softmax(node), fuse)
+        node._buf = K.softmax_rows(_rows_of(x, x.shape[-1])).view(node.shape)
+    elif fuse and _match_layernorm(node) is not None:
+        xn, w, b, eps, n = _match_layernorm(node)
+        x, g, be = (None if a is None else _emit_leaf(a, fuse) for a in (xn, w, b))
+        node._buf = K.layernorm_rows(_rows_of(x, n), g if g is None else g.reshape(-1).contiguous(), be if be is None else be.reshape(-1).contiguous(),
+                                     eps).view(node.shape)
     elif fuse:
         _eval_fused(node, fuse)
     else:
@@ -290,9 +487,10 @@ def _traced(f, mode):
         with fusing_composites():
             out = f(*args, **kwargs)
         outs = out if isinstance(out, (tuple, list)) else (out,)
-        for o in outs:
-            if isinstance(o, T.Tensor):
-                o._jit = mode
+        tens = [o for o in outs if isinstance(o, T.Tensor)]
+        for o in tens:
+            o._jit = mode
+            o._siblings = tens  # outputs of one call may come out of one kernel (multi-output regions)
         return out
     return wrapped
 

@@ -246,23 +246,18 @@ def sqrt(x): return x ** 0.5  # pequegrad/ops.py:508-509
 
 
 def softmax(x: Tensor, dim=-1) -> Tensor:
-    """Composite exactly as pequegrad/ops.py:259-267; under `jit` the last-axis case maps to the one-kernel row softmax."""
-    from . import fuser
-    if fuser._fuse_composites and dim in (-1, x.ndim - 1):
-        return Tensor(op="softmax_rows", args=(x,), attrs={"causal": False}, shape=x.shape, dtype=x.dtype)
+    """Composite exactly as pequegrad/ops.py:259-267. Under `jit` the fuser recognises the chain (over the last axis)
+    in the graph, however it was written, and runs it as the one-kernel row softmax."""
     m = x.max_reduce(dim, keepdim=True)
     e = (x - m).exp()
     return e / e.sum(dim, keepdim=True)
 
 
 def layer_norm(x: Tensor, normalized_shape, eps=1e-5, weight=None, bias=None) -> Tensor:
-    """Composite exactly as pequegrad/ops.py:515-551 (biased variance, eps before the square root)."""
+    """Composite exactly as pequegrad/ops.py:515-551 (biased variance, eps before the square root). Under `jit` the
+    fuser recognises the chain in the graph and runs it as the one-kernel row LayerNorm."""
     ns = (normalized_shape,) if isinstance(normalized_shape, int) else tuple(normalized_shape)
     dims = tuple(range(x.ndim - len(ns), x.ndim))
-    from . import fuser
-    if fuser._fuse_composites and tuple(x.shape[-len(ns):]) == ns:
-        return Tensor(op="layernorm_rows", args=(x,) + tuple(t for t in (weight, bias) if t is not None),
-                      attrs={"operands": (x, weight, bias), "n": int(np.prod(ns)), "eps": float(eps)}, shape=x.shape, dtype=x.dtype)
     mu = x.mean(dims, keepdim=True)
     n = float(np.prod(ns))
     var = ((x - mu) ** 2.0).sum(dims, keepdim=True) / n

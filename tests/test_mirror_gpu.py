@@ -219,3 +219,103 @@ def test_sdpa_composite_and_its_fused_form():
     assert_close(full, ref(False), 2e-2, 2e-2)
     with pytest.raises(NotImplementedError, match="use a mask"):
         pg.scaled_dot_product_attention(pg.Tensor(q), pg.Tensor(k), pg.Tensor(v), is_causal=True)
+
+
+def test_multi_reduce_chains_written_from_primitives_are_one_kernel():
+    """The reference's scheduler allows one reduce per fused kernel (csrc/compiler/scheduler.cpp:62-66), so a softmax or
+    a LayerNorm written out by hand costs a kernel per reduce there. Here the fuser recognises both chains in the graph:
+    one launch each, same numbers as eager."""
+    (x,) = ref_test_inputs([(64, 1024)], np.float32)
+    x = (x - 0.7) * 10
+
+    def my_softmax(t):
+        m = t.max_reduce(-1, True)
+        e = (t - m).exp()
+        return e / e.sum(-1, True)
+
+    want = torch.softmax(torch.from_numpy(x), -1).numpy()
+    out = {}
+    assert launches(lambda: out.setdefault("j", fuser.jit(my_softmax)(pg.Tensor(x)).numpy())) == 1
+    assert launches(lambda: out.setdefault("e", my_softmax(pg.Tensor(x)).numpy())) >= 5
+    assert_close(out["j"], want, 1e-5)
+    assert_close(out["e"], want, 1e-5)
+    # through a permuted view: the rows are made contiguous by one copy kernel, then the row kernel
+    xt = np.ascontiguousarray(x.T)
+    n = launches(lambda: out.setdefault("p", fuser.jit(lambda t: my_softmax(t.permute(1, 0)))(pg.Tensor(xt)).numpy()))
+    assert n == 2
+    assert_close(out["p"], want, 1e-5)
+
+    w, b = ref_test_inputs([(1024,), (1024,)], np.float32)
+
+    def my_layernorm(t, g, c):
+        mu = t.mean(-1, True)
+        var = ((t - mu) ** 2.0).sum(-1, True) / 1024.0
+        return (t - mu) / (var + 1e-5) ** 0.5 * g + c
+
+    want = torch.nn.functional.layer_norm(torch.from_numpy(x), (1024,), torch.from_numpy(w), torch.from_numpy(b), 1e-5).numpy()
+    assert launches(lambda: out.setdefault("lj", fuser.jit(my_layernorm)(pg.Tensor(x), pg.Tensor(w), pg.Tensor(b)).numpy())) == 1
+    assert launches(lambda: out.setdefault("le", my_layernorm(pg.Tensor(x), pg.Tensor(w), pg.Tensor(b)).numpy())) >= 8
+    assert_close(out["lj"], want, 1e-4)
+    assert_close(out["le"], want, 1e-4)
+    # not LayerNorm's variance (divided by n - 1): stays a sequence of fused regions, and still agrees with eager
+    def other(t):
+        mu = t.mean(-1, True)
+        return (t - mu) / (((t - mu) ** 2.0).sum(-1, True) / 1023.0 + 1e-5) ** 0.5
+    assert_close(fuser.jit(other)(pg.Tensor(x)).numpy(), other(pg.Tensor(x)).numpy(), 1e-5)
+
+
+def test_regions_larger_than_the_kernel_limits_are_split_not_refused():
+    """A fused kernel takes at most 6 operands and 32 instructions. Larger expressions are cut into several regions;
+    jit must agree with eager on them."""
+    arrs = ref_test_inputs([(33, 40)] * 10, np.float32)
+
+    def ten_sum(*ts):
+        acc = ts[0]
+        for t in ts[1:]:
+            acc = acc + t * 0.5
+        return acc
+
+    got = {}
+    n = launches(lambda: got.setdefault("v", fuser.jit(ten_sum)(*[pg.Tensor(a) for a in arrs]).numpy()))
+    assert 2 <= n <= 6  # 10 operands and 37 instructions: at least two regions; eager would be 27 kernels
+    assert_close(got["v"], ten_sum(*[pg.Tensor(a) for a in arrs]).numpy(), 1e-6)
+    assert_close(got["v"], arrs[0] + 0.5 * np.sum(arrs[1:], axis=0), 1e-5)
+
+    def long_chain(t):
+        for i in range(40):
+            t = (t * 0.9 + 0.1) if i % 3 else (t + 1.0).log()
+        return t
+
+    n = launches(lambda: got.setdefault("c", fuser.jit(long_chain)(pg.Tensor(arrs[0])).numpy()))
+    assert 6 <= n <= 12  # about 146 instructions in regions of at most 28; eager would be 120 kernels
+    assert_close(got["c"], long_chain(pg.Tensor(arrs[0])).numpy(), 1e-5)
+    # the same with a reduce on top: prologue and epilogue each cut where needed
+    def reduced(*ts):
+        return (ten_sum(*ts).sum(1) * 2.0).exp()
+    assert_close(fuser.jit(reduced)(*[pg.Tensor(a * 0.01) for a in arrs]).numpy(), reduced(*[pg.Tensor(a * 0.01) for a in arrs]).numpy(), 1e-5)
+
+
+def test_outputs_of_one_call_share_a_kernel():
+    """Sibling outputs of a fused region (csrc/compiler/scheduler.cpp:229-256, csrc/compiler/ir.cpp:667-675): the
+    elementwise results of one traced call come out of ONE multi-output kernel, common subexpressions computed once."""
+    a, b, c = ref_test_inputs([(17, 130)] * 3, np.float32)
+
+    def f(x, y, z):
+        t = x * y + z
+        return t, t * 2.0 - x, (y > z), (x - y).astype(pg.float16)
+
+    outs = fuser.jit(f)(pg.Tensor(a), pg.Tensor(b), pg.Tensor(c))
+    n = launches(lambda: [o.eval() for o in outs])
+    assert n == 1
+    t = a * b + c
+    assert_close(outs[0].numpy(), t, 1e-6)
+    assert_close(outs[1].numpy(), t * 2 - a, 1e-6)
+    assert np.array_equal(outs[2].numpy(), (b > c).astype(np.float32))
+    assert outs[3].numpy().dtype == np.float16 and np.array_equal(outs[3].numpy(), (a - b).astype(np.float16))
+    # an output with a reduce, or of another shape, is a kernel of its own
+    def g(x, y):
+        return x + y, (x * y).sum(1), x.permute(1, 0) * 2.0
+    outs = fuser.jit(g)(pg.Tensor(a), pg.Tensor(b))
+    assert launches(lambda: [o.eval() for o in outs]) == 3
+    assert_close(outs[1].numpy(), (a * b).sum(1), 1e-5)
+    assert_close(outs[2].numpy(), a.T * 2, 1e-6)

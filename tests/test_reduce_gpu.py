@@ -318,8 +318,8 @@ def test_ragged_row_split_across_ctas():
 @pytest.mark.parametrize("shape", [(7, 100, 20), (3, 5, 33, 6), (40, 9, 128), (2, 300, 7), (1000, 12, 3)])
 def test_short_reduced_axis_with_operands_of_opposite_orientation(shape):
     """x read through a permute of its last two dims against a plain y (the README case's shape of problem): the
-    (kept, reduced) plane of each operand is contiguous, one as [k][j], the other as [j][k]; every op, a chain
-    prologue and an epilogue, odd sizes and planes that 128-bit loads cannot fetch."""
+    operands disagree on which of the innermost kept axis and the short reduced axis is contiguous; every op, a
+    chain prologue and an epilogue, odd sizes and rows that 128-bit loads cannot fetch."""
     rng = np.random.default_rng(31)
     *lead, J, Kr = shape
     xbuf = rng.standard_normal(tuple(lead) + (Kr, J)).astype(np.float32)
@@ -331,7 +331,7 @@ def test_short_reduced_axis_with_operands_of_opposite_orientation(shape):
     xd, yd = dev(x), dev(y)
     out_shape = K.reduced_shape(shape, [ax], False)
     od = torch.empty(out_shape, device="cuda")
-    assert K.describe_reduce([K.desc(xd), K.desc(yd)], K.desc(od), L.SUM, [ax], pro).startswith("plane")
+    assert K.describe_reduce([K.desc(xd), K.desc(yd)], K.desc(od), L.SUM, [ax], pro).startswith("short")
     for op in ("sum", "max", "mean"):
         run_case([x, y], op, [ax], False, pro, epi, what=f"plane {shape} {op}")
         run_case([y, x], op, [ax], True, pro, (), what=f"plane swapped {shape} {op}")
