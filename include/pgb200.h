@@ -38,6 +38,7 @@ extern "C" {
 #define PGB_MAX_INPUTS 6
 #define PGB_MAX_INSTRS 32
 #define PGB_MAX_OUTPUTS 4
+#define PGB_MAX_PEERS 16
 
 /* dtype codes: 0..3 follow the reference enum order (csrc/dtype.hpp:9-14);
  * 4 and 5 are additions the int8 and bf16 paths need. */
@@ -336,6 +337,31 @@ PGB_API int pgb_gemm_pair_mode(int mode);
  * kernel records the error word above, frees its tensor memory and returns; nothing faults or hangs. Used by the
  * tests to exercise the timeout path; no counterpart in the reference. */
 PGB_API int pgb_gemm_wait_drill(unsigned int polls, int skip_loads);
+
+/* ---- Collectives of the batch-sharded path over peer memory (one process per GPU of one box) -------------------
+ * The reference's pequegrad/distrib runs its "devices" one after another on one GPU and reduces in a Python loop
+ * (pequegrad/distrib/__init__.py:4-62); these entry points have no counterpart there. They serve the two exchanges
+ * the sharded workloads need (a max of one float, a gather of small slabs) as single kernels that store into the
+ * peers' memory and poll their own, instead of a library collective per exchange.
+ *
+ * Set-up, once: every rank allocates a control block of pgb_peer_ctrl_bytes() bytes (and, for gathers, a receive
+ * buffer of world x slab bytes) with pgb_peer_alloc, exports both with pgb_peer_export, passes the 64-byte handles
+ * to the other ranks by any host channel, and opens the others' with pgb_peer_open. peer_ctrl[r] / peer_dst[r] are
+ * then rank r's control block / receive buffer as mapped in THIS process (its own allocation for r == rank).
+ * Every rank must issue the same sequence of collective calls. A rank whose peer does not arrive within about half a
+ * second records the error word of pgb_device_error (roles 10 and 11) and its kernel returns. */
+PGB_API size_t pgb_peer_ctrl_bytes(void);
+PGB_API int pgb_peer_alloc(size_t bytes, void **ptr);   /* zero-filled device memory that other processes can map */
+PGB_API int pgb_peer_free(void *ptr);
+PGB_API int pgb_peer_export(const void *ptr, unsigned char handle[64]);
+PGB_API int pgb_peer_open(const unsigned char handle[64], void **ptr);
+PGB_API int pgb_peer_close(void *ptr);
+/* *value (a non-negative float in this rank's memory) becomes the maximum over all ranks. */
+PGB_API int pgb_peer_allreduce_max_f32(float *value, void *const *peer_ctrl, int rank, int world, void *stream);
+/* Every rank's `bytes` at `src` land at offset rank * bytes of every rank's receive buffer; when the kernel has
+ * finished on a rank, all slabs have arrived there. src 16-byte aligned, bytes a multiple of 16. */
+PGB_API int pgb_peer_allgather(const void *src, size_t bytes, void *const *peer_dst, void *const *peer_ctrl, int rank,
+                               int world, void *stream);
 
 #ifdef __cplusplus
 }

@@ -4,8 +4,8 @@
 // is k (README.md:59-63). No single thread mapping reads both with 128-byte requests, so the row and column kernels
 // refuse it, and the generic kernel pays 64-bit div / mod and the interpreter per element.
 //
-// Here thread (plane, j) walks k with every address precomputed: 32-bit offsets, four k steps in flight (eight
-// loads for two inputs), 128-bit loads for an operand whose k axis is contiguous, the prologue as a decoded chain.
+// Here thread (plane, j) walks k with every address precomputed: 32-bit offsets, eight k steps in flight, 128-bit
+// loads for an operand whose k axis is contiguous, the prologue as a decoded chain.
 // Consecutive threads read consecutive j of the j-contiguous operand (full requests) and neighbouring short rows of
 // the k-contiguous one, whose sectors the L1 serves on the following steps; every byte is fetched from L2 once.
 // A shared-memory staging of whole (j, k) planes was tried first and took 26 us on the README case, three times
@@ -50,23 +50,28 @@ __global__ void __launch_bounds__(kShortThreads, 4) reduce_short_kernel(const __
   if (LITE) chain_decode<float>(p.pro, cr);
   Acc<float, ROP> acc;
   acc.init();
+  constexpr int B = 8;  // k steps in flight: their loads are all issued before the first is used
 #pragma unroll 1
-  for (int k0 = 0; k0 < K; k0 += 4) {
-    float w[NIN][4], run[4];
+  for (int k0 = 0; k0 < K; k0 += B) {
+    float w[NIN][B], run[B];
 #pragma unroll
     for (int k = 0; k < NIN; ++k) {
       if (p.vec4[k]) {
-        const float4 t = __ldg(reinterpret_cast<const float4 *>(base[k] + k0));  // K % 4 == 0 here: never past the row
-        w[k][0] = t.x; w[k][1] = t.y; w[k][2] = t.z; w[k][3] = t.w;
+#pragma unroll
+        for (int v = 0; v < B; v += 4) {
+          // K % 4 == 0 here; a vector wholly past the row is clamped onto its last vector and ignored below
+          const float4 t = __ldg(reinterpret_cast<const float4 *>(base[k] + min(k0 + v, K - 4)));
+          w[k][v] = t.x; w[k][v + 1] = t.y; w[k][v + 2] = t.z; w[k][v + 3] = t.w;
+        }
       } else {
 #pragma unroll
-        for (int e = 0; e < 4; ++e) w[k][e] = __ldg(base[k] + (int64_t)min(k0 + e, K - 1) * p.kstr[k]);
+        for (int e = 0; e < B; ++e) w[k][e] = __ldg(base[k] + (int64_t)min(k0 + e, K - 1) * p.kstr[k]);
       }
     }
-    if (LITE) chain_eval_fast<float, NIN, 4>(cr, w, run);
-    else chain_eval<float, NIN, 4>(p.pro, w, run);
+    if (LITE) chain_eval_fast<float, NIN, B>(cr, w, run);
+    else chain_eval<float, NIN, B>(p.pro, w, run);
 #pragma unroll
-    for (int e = 0; e < 4; ++e)
+    for (int e = 0; e < B; ++e)
       if (k0 + e < K) acc.add_stream(run[e], k0 + e);
   }
   finish_output<float>(p.epi, o, acc.v, acc.i);

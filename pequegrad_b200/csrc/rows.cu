@@ -7,16 +7,12 @@
 // 480-501). Here a warp keeps its row in registers: one read and one write of
 // the tensor. The arithmetic follows the composites step by step (true
 // division, biased variance, eps added before the square root).
-#include <cstdlib>
 #include <type_traits>
 
 #include "reduce_common.cuh"
 #include "vec.cuh"
 
 namespace pgb {
-
-int launch_layernorm_stream_f32(const float *x, float *y, const float *gamma, const float *beta, int64_t rows, int64_t C, float eps,
-                                cudaStream_t stream);
 
 struct RowsParams {
   const void *x;
@@ -418,12 +414,6 @@ __global__ void __launch_bounds__(256) layernorm_cta_kernel(const __grid_constan
 // ---------------------------------------------------------------------------
 static bool aligned16(const void *p) { return (reinterpret_cast<uintptr_t>(p) & 15) == 0; }
 
-static size_t ln_pad_smem() {  // EXPERIMENT: residency limit through unused dynamic shared memory
-  const char *var = getenv("PGB_LN_VARIANT");
-  const int v = var ? atoi(var) : 0;
-  return v == 3 ? 45 * 1024 : (v == 4 ? 37 * 1024 : 0);
-}
-
 template <typename IoT, bool SOFTMAX>
 static int rows_launch(const RowsParams &p, cudaStream_t stream) {
   constexpr int V = 16 / (int)sizeof(IoT);
@@ -436,7 +426,7 @@ static int rows_launch(const RowsParams &p, cudaStream_t stream) {
   if constexpr (SOFTMAX && sizeof(IoT) == 2) softmax_warp16_kernel<IoT, NV><<<wgrid, 256, 0, stream>>>(p); \
   else if constexpr (SOFTMAX) softmax_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p); \
   else if constexpr (sizeof(IoT) == 2) layernorm_warp16_kernel<IoT, NV><<<wgrid, 256, 0, stream>>>(p); \
-  else layernorm_warp_kernel<IoT, V, NV><<<wgrid, 256, ln_pad_smem(), stream>>>(p)
+  else layernorm_warp_kernel<IoT, V, NV><<<wgrid, 256, 0, stream>>>(p)
   if (vec && per_lane_vecs <= 16) {
     if (per_lane_vecs <= 1) { PGB_ROWS_CASE(1); }
     else if (per_lane_vecs <= 2) { PGB_ROWS_CASE(2); }
@@ -504,12 +494,7 @@ int run_layernorm_rows(const pgb_tensor *x, const pgb_tensor *gamma, const pgb_t
   p.beta = beta ? beta->data : nullptr;
   p.eps = eps;
   if (p.rows == 0 || p.C == 0) return PGB_OK;
-  if (x->dtype == PGB_F32) {
-    // many rows: the persistent kernel that streams row blocks through shared memory (rows_stream.cu)
-    const int r = launch_layernorm_stream_f32((const float *)p.x, (float *)p.y, (const float *)p.gamma, (const float *)p.beta, p.rows, p.C, eps, stream);
-    if (r != 0) return r == 1 ? PGB_OK : r;
-    return rows_launch<float, false>(p, stream);
-  }
+  if (x->dtype == PGB_F32) return rows_launch<float, false>(p, stream);
   if (x->dtype == PGB_F16) return rows_launch<__half, false>(p, stream);
   return rows_launch<__nv_bfloat16, false>(p, stream);
 }

@@ -278,6 +278,91 @@ class GatherBucket:
         return copy_out
 
 
+class _DevMem:
+    """A raw device allocation seen by torch through the CUDA array interface (no copy)."""
+
+    def __init__(self, ptr: int, nbytes: int):
+        self.__cuda_array_interface__ = {"shape": (nbytes,), "typestr": "|u1", "data": (ptr, False), "version": 3}
+
+
+class PeerGroup:
+    """Peer-memory collectives between the processes of one box (one GPU each): the kernels of
+    `pgb_peer_allreduce_max_f32` / `pgb_peer_allgather` store straight into the other ranks' memory over
+    NVLink and wait for the others' stores, one small launch per exchange, instead of a library collective
+    (tens of microseconds each, as long as a whole layer of an 8192-row MLP shard). Set-up maps every rank's
+    control block and receive buffer into this process with CUDA IPC; the handles travel through the
+    process group's host channel. Only for NCCL groups with one shard per process; every rank must issue
+    the same sequence of calls."""
+
+    def __init__(self, gather_bytes: int = 0):
+        import ctypes as C
+
+        from . import _lib as L
+        self.rank, self.world = rank_world()
+        if self.world < 2 or self.world > 16 or not torch.cuda.is_available():
+            raise RuntimeError("PeerGroup needs 2 to 16 processes with one GPU each")
+        lib = L.lib()
+        self._lib, self._C = lib, C
+        self.gather_bytes = (int(gather_bytes) + 255) // 256 * 256
+        self._own, self._opened = [], []
+
+        def alloc(nbytes):
+            p = C.c_void_p()
+            L.check(lib.pgb_peer_alloc(nbytes, C.byref(p)))
+            self._own.append(p.value)
+            h = C.create_string_buffer(64)
+            L.check(lib.pgb_peer_export(p, h))
+            return p.value, h.raw
+
+        ctrl, h_ctrl = alloc(lib.pgb_peer_ctrl_bytes())
+        recv, h_recv = alloc(self.gather_bytes * self.world) if self.gather_bytes else (None, b"")
+        handles = [None] * self.world
+        dist.all_gather_object(handles, (h_ctrl, h_recv))
+
+        def open_(h):
+            p = C.c_void_p()
+            L.check(lib.pgb_peer_open(h, C.byref(p)))
+            self._opened.append(p.value)
+            return p.value
+
+        ctrls = [ctrl if r == self.rank else open_(handles[r][0]) for r in range(self.world)]
+        recvs = [recv if r == self.rank else (open_(handles[r][1]) if self.gather_bytes else None) for r in range(self.world)]
+        self._ctrl = (C.c_void_p * self.world)(*ctrls)
+        self._recv = (C.c_void_p * self.world)(*[r or 0 for r in recvs])
+        self.recv = torch.as_tensor(_DevMem(recv, self.gather_bytes * self.world), device="cuda") if self.gather_bytes else None
+        dist.barrier()  # every mapping exists before anyone's first kernel stores through one
+
+    def allreduce_max(self, value: torch.Tensor) -> torch.Tensor:
+        """`value` (one non-negative float32 on this rank's GPU) becomes the maximum over all ranks, in place."""
+        from . import _lib as L
+        L.check(self._lib.pgb_peer_allreduce_max_f32(value.data_ptr(), self._ctrl, self.rank, self.world, torch.cuda.current_stream().cuda_stream))
+        return value
+
+    def allgather(self, local: torch.Tensor) -> torch.Tensor:
+        """Every rank's `local` (same shape everywhere, contiguous) stacked along a new dim 0: a view of this
+        rank's receive buffer, valid until the next allgather."""
+        from . import _lib as L
+        nbytes = local.numel() * local.element_size()
+        if nbytes > self.gather_bytes or not local.is_contiguous():
+            raise ValueError("PeerGroup.allgather: the slab must be contiguous and fit the receive buffer")
+        padded = (nbytes + 15) // 16 * 16
+        L.check(self._lib.pgb_peer_allgather(local.data_ptr(), padded, self._recv, self._ctrl, self.rank, self.world,
+                                             torch.cuda.current_stream().cuda_stream))
+        out = self.recv[: padded * self.world].view(self.world, padded)[:, :nbytes]
+        return out.view(local.dtype).view((self.world,) + tuple(local.shape)) if padded == nbytes else \
+            out.contiguous().view(local.dtype).view((self.world,) + tuple(local.shape))
+
+    def close(self):
+        torch.cuda.synchronize()
+        if dist.is_initialized():
+            dist.barrier()  # nobody unmaps while a peer's kernel may still store
+        for p in self._opened:
+            self._lib.pgb_peer_close(p)
+        for p in self._own:
+            self._lib.pgb_peer_free(p)
+        self._opened, self._own = [], []
+
+
 def all_reduce(tensors, op: str = "sum") -> torch.Tensor:
     """All-reduce over every shard (distrib/__init__.py:4-29): `tensors` is this process's list of per-shard
     tensors (or a single tensor); each of them ends up holding the result, which is also returned.

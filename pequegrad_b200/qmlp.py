@@ -59,12 +59,14 @@ class QuantizedMLP:
         out = self.forward_sharded([x], keep)[0]
         return out
 
-    def forward_sharded(self, xs, keep: bool = False):
+    def forward_sharded(self, xs, keep: bool = False, peers=None):
         """The same forward over row shards of ONE batch: `xs` is this process's list of shards (or a
         `distrib.ShardedTensor` split along dim 0). "Per tensor" keeps meaning the whole batch: after every
         absmax the shards' maxima are combined (`distrib.all_reduce(.., "max")`: one float per layer, across the
         shards held here and across processes), so the int8 activations and the outputs have the same bits
-        however the rows are split. Returns one output per local shard."""
+        however the rows are split. With `peers` (a `distrib.PeerGroup`, one shard per process) the maxima are
+        exchanged by the peer-memory kernel, one small launch, instead of a library collective. Returns one output
+        per local shard."""
         from . import distrib as D
         xs = xs.shards if isinstance(xs, D.ShardedTensor) else list(xs)
         S = len(xs)
@@ -74,7 +76,11 @@ class QuantizedMLP:
             b["amax"][1:].zero_()  # slot i holds max|input of layer i|; the GEMM epilogues fold into slots 1..
 
         def combine(i):
-            if not lone:
+            if lone:
+                return
+            if peers is not None and S == 1:
+                peers.allreduce_max(bufs[0]["amax"][i:i + 1])
+            else:
                 D.all_reduce([b["amax"][i:i + 1] for b in bufs], "max")
 
         for x, b in zip(xs, bufs):

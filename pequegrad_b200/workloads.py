@@ -303,8 +303,8 @@ class Mlp:
     GPUs. The per-tensor activation scale stays global: one all-reduce(max) of a float per layer."""
     name, metric, unit, dtype = "mlp", "int8-MLP rows/s", "rows/s", "i8"
 
-    def __init__(self, rows=MLP_ROWS):
-        self.rows = rows
+    def __init__(self, rows=MLP_ROWS, use_peers=True):
+        self.rows, self.use_peers = rows, use_peers
         self.desc = (f"quantized MLP inference 784->1024->1024->10 with ReLU, batch {rows} row-sharded over the GPUs; weights N(0,0.05) int8 per "
                      "output channel, activations uniform[0,1) fp32 quantized per tensor on the device (absmax over the whole batch); int32 "
                      "accumulate, fused dequant+bias+ReLU")
@@ -321,24 +321,42 @@ class Mlp:
         self.X = D.shard_tensor(X, world, 0, _devices(world)).shards[0]
         del X
         self.full = torch.empty((self.rows, MLP_DIMS[-1]), dtype=torch.float32, device=dev) if world > 1 else None
+        # the exchanges of a step (three maxima of one float, one gather of [rows / P, 10] slabs) go through the
+        # peer-memory kernels when the ranks can map one another's memory, else through NCCL
+        self.peers, self.peer_note = None, "NCCL"
+        if world > 1 and self.use_peers:
+            try:
+                self.peers = D.PeerGroup(gather_bytes=self.X.shape[0] * MLP_DIMS[-1] * 4)
+                self.peer_note = "peer-memory kernels over NVLink (CUDA IPC mappings)"
+            except Exception as e:  # noqa: BLE001 - any failure of the mapping leaves the NCCL path
+                self.peer_note = f"NCCL (peer mapping unavailable: {type(e).__name__}: {e})"
+            flags = [None] * world
+            import torch.distributed as dist
+            dist.all_gather_object(flags, self.peers is not None)
+            if not all(flags):  # all ranks or none
+                if self.peers is not None:
+                    self.peers.close()
+                self.peers = None
         self.units_per_step = self.rows
         self.ops_per_row = 2 * sum(MLP_DIMS[i] * MLP_DIMS[i + 1] for i in range(3))
         self.config = {"rows_total": self.rows, "rows_per_gpu": self.rows // world, "int8_ops_per_step": self.ops_per_row * self.rows,
-                       "collectives_per_step": 0 if world == 1 else "3 x all_reduce(max) of one float + 1 all_gather of [rows,10] fp32",
+                       "collectives_per_step": 0 if world == 1 else "3 x all_reduce(max) of one float + 1 all_gather of [rows,10] fp32, by " + self.peer_note,
                        "l2": "activations per layer (51 to 268 MB over all GPUs) against a 126 MB L2; each layer reads what the one before "
                              "wrote, as the pipeline does in use"}
 
     def step_compute(self):
-        self.out = self.mlp.forward_sharded([self.X])[0]
+        self.out = self.mlp.forward_sharded([self.X], peers=self.peers)[0]
 
     def step(self):
         import torch.distributed as dist
         self.step_compute()
-        if self.world > 1:
+        if self.world == 1:
+            self.out_full = self.out
+        elif self.peers is not None:
+            self.out_full = self.peers.allgather(self.out).view(self.rows, MLP_DIMS[-1])
+        else:
             dist.all_gather_into_tensor(self.full, self.out)
             self.out_full = self.full
-        else:
-            self.out_full = self.out
 
     def e2e_setup(self):
         import torch

@@ -102,10 +102,33 @@ def _worker(rank, world, port, q):
         del wl, T, got
         torch.cuda.empty_cache()
 
-        # the int8 MLP split by rows: the bits of the single-GPU forward over the whole batch
+        # the peer-memory collectives: a max of one float and a gather of small slabs, many calls in a row
+        pg = D.PeerGroup(gather_bytes=3 * 1000 * 4)
+        for i in range(50):
+            v = torch.tensor([float(rank * 7 + i)], device=dev)
+            pg.allreduce_max(v)
+            assert float(v) == float((world - 1) * 7 + i), (i, float(v))
+            slab = torch.full((3, 1000), float(rank + 10 * i), device=dev)
+            got_all = pg.allgather(slab)
+            torch.cuda.synchronize()
+            assert got_all.shape == (world, 3, 1000)
+            assert all(bool((got_all[r] == float(r + 10 * i)).all()) for r in range(world)), i
+        assert K.device_error() == 0
+        pg.close()
+
+        # the int8 MLP split by rows: the bits of the single-GPU forward over the whole batch,
+        # with the exchanges through NCCL and through the peer-memory kernels
+        m0 = W.Mlp(rows=16384, use_peers=False)
+        m0.setup(dev, rank, world)
+        m0.step()
+        nccl_out = m0.out_full.clone()
+        del m0
         m = W.Mlp(rows=16384)
         m.setup(dev, rank, world)
+        assert m.peers is not None, m.peer_note
         m.step()
+        m.step()
+        assert torch.equal(m.out_full, nccl_out)
         g3 = torch.Generator(device=dev).manual_seed(3)
         X = torch.rand((16384, 784), generator=g3, device=dev)
         whole = m.mlp.forward_sharded([X])[0]  # one shard per process holding ALL rows: both ranks compute the same thing
