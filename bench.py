@@ -222,6 +222,7 @@ def cpu_sample_readme(budget_s, threads):
 
 
 _CACHE: dict = {}
+USE_GRAPHS = True
 CPU_SAMPLES = {"sweep": cpu_sample_sweep, "mlp": cpu_sample_mlp, "gpt2": cpu_sample_gpt2, "rows": cpu_sample_rows, "readme": cpu_sample_readme}
 
 
@@ -350,6 +351,7 @@ def quick_other(name, dev, rank, world, pk, barrier):
     wl.setup(dev, rank, world)
     for _ in range(3):
         wl.step()
+    graphs = bool(USE_GRAPHS and hasattr(wl, "enable_graphs") and wl.enable_graphs())
     n = 5
     ms = timed_steps(wl.step, n, barrier) / n
     ms_c = timed_steps(wl.step_compute, n, barrier) / n
@@ -361,7 +363,7 @@ def quick_other(name, dev, rank, world, pk, barrier):
     else:
         out = {"metric": wl.metric, "value": round(wl.units_per_step / (ms * 1e-3), 1), "unit": wl.unit, "ms_per_step": round(ms, 4),
                "compute_only": {"value": round(wl.units_per_step / (ms_c * 1e-3), 1), "ms_per_step": round(ms_c, 4)},
-               "n_gpus": world, "scaling": "strong", "timing": "max over ranks", "roofline": rf}
+               "n_gpus": world, "scaling": "strong", "timing": "max over ranks", "cuda_graphs": graphs, "roofline": rf}
     if name == "gpt2":
         out["model_tflops_per_gpu"] = round(wl.flops_per_token * wl.units_per_step / world / (ms * 1e-3) / 1e12, 1)
     if name == "mlp":
@@ -379,6 +381,7 @@ def main():
     ap.add_argument("--impl", default="pgb200", choices=["pgb200", "reference"])
     ap.add_argument("--workload", default="sweep", choices=["sweep", "mlp", "gpt2", "rows", "readme"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
+    ap.add_argument("--no-graph", action="store_true", help="launch every kernel of a step separately instead of replaying CUDA graphs")
     ap.add_argument("--no-others", action="store_true", help="sweep only: skip the short runs of the other workloads")
     ap.add_argument("--only", default="", help="sweep: comma-separated tensor names (A,B,Bp) to restrict the sweep, for profiling")
     ap.add_argument("--bare", action="store_true", help="sweep diagnostic: no prologue / epilogue (not the benchmark workload)")
@@ -419,12 +422,19 @@ def main():
     for _ in range(args.warmup):
         wl.step()
     barrier()
+    launches0 = L.lib().pgb_launch_count()
+    wl.step()  # one more untimed step, kernel by kernel, to count this library's launches per step
+    launches = (L.lib().pgb_launch_count() - launches0) * args.steps
+    global USE_GRAPHS
+    USE_GRAPHS = not args.no_graph
+    # the launches of a step as CUDA graphs (what the reference's jit(use_cuda_graph=True) asks for): the same kernels,
+    # one launch per graph; matters where a rank's shard makes the kernels as short as their launch overhead
+    graphs = bool(USE_GRAPHS and hasattr(wl, "enable_graphs") and wl.enable_graphs())
+    barrier()
     sampler = ClockSampler(local_rank)
     sampler.start()
     time.sleep(0.2)
-    launches0 = L.lib().pgb_launch_count()
     ms_total = timed_steps(wl.step, args.steps, barrier, nvtx="pgb_timed")
-    launches = L.lib().pgb_launch_count() - launches0
     ms_compute = timed_steps(wl.step_compute, args.steps, barrier)
     roofline = wl.roofline(pk, max(5, min(args.steps, 20))) if rank == 0 else None  # per-kernel device times, still under the clock sampler
     barrier()
@@ -477,7 +487,7 @@ def main():
                     "ms_per_step": round(e2e_ms, 4),
                     "what": "pinned host inputs copied to every rank's shards, the step with its gather, the result read back by rank 0; "
                             "h2d bytes are the sum over ranks"},
-            "gpu_launches": int(launches),
+            "gpu_launches": int(launches), "cuda_graphs": graphs,
             "roofline": roofline,
             "cpu_baseline": cpu,
         }

@@ -37,15 +37,17 @@ struct ShortParams {
 
 template <int NIN, int ROP, bool LITE>
 __global__ void __launch_bounds__(kShortThreads, 4) reduce_short_kernel(const __grid_constant__ ShortParams<NIN> p) {
-  const int64_t o = (int64_t)blockIdx.x * kShortThreads + threadIdx.x;
-  if (o >= p.n_out) return;
+  // 32-bit index arithmetic (the host checks that the output count fits): a 64-bit division costs more than the loop
+  const uint32_t o = blockIdx.x * kShortThreads + threadIdx.x;
+  if (o >= (uint32_t)p.n_out) return;
   const int J = p.J, K = p.K;
-  const int64_t plane = o / J;
-  const int j = (int)(o - plane * J);
-  const int64_t b1 = plane % p.bsize1, b0 = plane / p.bsize1;
+  const uint32_t plane = o / (uint32_t)J;
+  const int j = (int)(o - plane * (uint32_t)J);
+  const uint32_t bs1 = (uint32_t)p.bsize1;
+  const uint32_t b0 = plane / bs1, b1 = plane - b0 * bs1;
   const float *base[NIN];
 #pragma unroll
-  for (int k = 0; k < NIN; ++k) base[k] = p.in[k] + b0 * p.bstr[k][0] + b1 * p.bstr[k][1] + (int64_t)j * p.jstr[k];
+  for (int k = 0; k < NIN; ++k) base[k] = p.in[k] + (int64_t)b0 * p.bstr[k][0] + (int64_t)b1 * p.bstr[k][1] + (int64_t)j * p.jstr[k];
   ChainRegs<float> cr;
   if (LITE) chain_decode<float>(p.pro, cr);
   Acc<float, ROP> acc;
@@ -102,7 +104,7 @@ int launch_short(ReduceJob &j, const ChainProg<float> &chain) {
     p.vec4[k] = v4 ? 1 : 0;
   }
   const int64_t grid = (c.n_out + kShortThreads - 1) / kShortThreads;
-  if (grid > 2147483647LL) return 0;
+  if (c.n_out > 2147483647LL - kShortThreads) return 0;
   char buf[160];
   snprintf(buf, sizeof buf, "short nin=%d J=%lld K=%lld outputs=%lld grid=%lld %s", NIN, (long long)J, (long long)K, (long long)c.n_out, (long long)grid,
            chain.lite ? "chain" : "chain-full");

@@ -85,6 +85,25 @@ class _L2Flush:
         self.sink = self.buf[1:2].amax()
 
 
+def capture_graph(fn):
+    """`fn()` (kernels of this library on the current stream, torch allocations allowed) as a CUDA graph: a step
+    then costs one launch instead of one per kernel, which is what bounds the small per-GPU shards of a partitioned
+    problem (the reference's `jit(use_cuda_graph=True)` is the same idea, pequegrad/transforms/compile.py:85-118).
+    Returns the graph, or None when the capture failed (the caller keeps launching kernel by kernel)."""
+    import torch
+    try:
+        fn()
+        torch.cuda.synchronize()
+        g = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(g):
+            fn()
+        torch.cuda.synchronize()
+        return g
+    except Exception:  # noqa: BLE001 - any capture problem leaves the eager path in charge
+        torch.cuda.synchronize()
+        return None
+
+
 def _devices(world):
     from . import distrib as D
     return D.default_devices(world)
@@ -155,21 +174,39 @@ class Sweep:
                        "l2": ("each rank's shards (%s MB) against a 126 MB L2; consecutive launches alternate tensors, so a case never "
                               "finds its own input in L2 unless the shard is smaller than what ran in between" % "/".join(map(str, shard_mb.values())))}
 
+    graphs = None
+
     def _launch(self, lo, hi):
         for *_, pr in self.prepared[lo:hi]:
-            pr(self.stream)
+            pr()
+
+    def enable_graphs(self):
+        """The launches of a step as two CUDA graphs (the axis-0 cases, then the rest), with the gathers between them."""
+        n = len(self.prepared)
+        g = [capture_graph(lambda: self._launch(0, self.n_first)), capture_graph(lambda: self._launch(self.n_first, n))]
+        self.graphs = g if all(x is not None for x in g) else None
+        return self.graphs is not None
+
+    def _part(self, i):
+        if self.graphs is not None:
+            self.graphs[i].replay()
+        elif i == 0:
+            self._launch(0, self.n_first)
+        else:
+            self._launch(self.n_first, len(self.prepared))
 
     def step_compute(self):
-        self._launch(0, len(self.prepared))
+        self._part(0)
+        self._part(1)
 
     def step(self):
         from . import kernels as K
         if self.world == 1:
             return self.step_compute()
         b0, b1 = self.buckets
-        self._launch(0, self.n_first)
+        self._part(0)
         b0.gather()
-        self._launch(self.n_first, len(self.prepared))
+        self._part(1)
         b1.gather()
         b0.wait()
         b1.wait()
@@ -230,9 +267,9 @@ class Sweep:
             evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
             for a, b in evs:
                 for o in self._flushers(pr):  # nothing of this case's input is left in L2
-                    o(self.stream)
+                    o()
                 a.record()
-                pr(self.stream)
+                pr()
                 b.record()
             torch.cuda.synchronize()
             t = statistics.median(a.elapsed_time(b) for a, b in evs)
@@ -344,11 +381,43 @@ class Mlp:
                        "l2": "activations per layer (51 to 268 MB over all GPUs) against a 126 MB L2; each layer reads what the one before "
                              "wrote, as the pipeline does in use"}
 
-    def step_compute(self):
+    graphs = None
+
+    def _compute(self):
         self.out = self.mlp.forward_sharded([self.X], peers=self.peers)[0]
+
+    def _full(self):
+        self._compute()
+        if self.peers is not None:
+            self.out_full = self.peers.allgather(self.out).view(self.rows, MLP_DIMS[-1])
+
+    def enable_graphs(self):
+        """Whole steps as CUDA graphs when no library collective is inside (one GPU, or the peer-memory kernels)."""
+        if self.world > 1 and self.peers is None:
+            return False
+        g = [capture_graph(self._compute), capture_graph(self._full)]
+        ok = all(x is not None for x in g)
+        if self.world > 1:  # all ranks or none: the peer kernels of a step must be launched by everyone
+            import torch.distributed as dist
+            flags = [None] * self.world
+            dist.all_gather_object(flags, ok)
+            ok = all(flags)
+        self.graphs = g if ok else None
+        return ok
+
+    def step_compute(self):
+        if self.graphs is not None:
+            self.graphs[0].replay()
+        else:
+            self._compute()
 
     def step(self):
         import torch.distributed as dist
+        if self.graphs is not None and (self.world == 1 or self.peers is not None):
+            self.graphs[1].replay()
+            if self.world == 1:
+                self.out_full = self.out
+            return
         self.step_compute()
         if self.world == 1:
             self.out_full = self.out
@@ -448,8 +517,20 @@ class Gpt2:
                        "gathered_bytes_per_step": self.full.numel() * 2 if world > 1 else 0,
                        "l2": "activations of a layer (50 to 805 MB over all GPUs) and the 3.3 GB of logits against a 126 MB L2"}
 
-    def step_compute(self):
+    graph = None
+
+    def _compute(self):
         self.logits = self.model.forward(self.idx, logits_out=self.logits_buf)
+
+    def enable_graphs(self):
+        self.graph = capture_graph(self._compute)
+        return self.graph is not None
+
+    def step_compute(self):
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._compute()
 
     def step(self):
         import torch.distributed as dist

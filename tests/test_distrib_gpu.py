@@ -129,6 +129,14 @@ def _worker(rank, world, port, q):
         m.step()
         m.step()
         assert torch.equal(m.out_full, nccl_out)
+        # the same step replayed as a CUDA graph (peer kernels included): same bits, call after call
+        assert m.enable_graphs()
+        for _ in range(3):
+            m.step()
+            m.step_compute()
+        m.step()
+        torch.cuda.synchronize()
+        assert torch.equal(m.out_full, nccl_out)
         g3 = torch.Generator(device=dev).manual_seed(3)
         X = torch.rand((16384, 784), generator=g3, device=dev)
         whole = m.mlp.forward_sharded([X])[0]  # one shard per process holding ALL rows: both ranks compute the same thing
