@@ -328,8 +328,10 @@ PGB_API int pgb_quantize_i8(const pgb_tensor *x, const float *absmax_dev, float 
 PGB_API int pgb_device_error(int *code, int reset);
 
 /* Which GEMMs run on CTA pairs (tcgen05.mma.cta_group::2, 256 x 256 tiles): 0 = none, 1 = the measured default
- * (large aligned f16 / bf16 / tf32 problems), negative = only query. Returns the previous mode. A tuning switch in
- * the manner of cublasSetMathMode; the reference has no counterpart. */
+ * (large aligned f16 / bf16 / tf32 problems), 2 = also the absmax-only pass of int8 layers, 3 = also every int8
+ * pass (both measured slower than the one-CTA kernel on 65536 x 1024 x 1024: 73.9 vs 65.6 us and 88.1 vs 80.0 us;
+ * kept for measurement and for the tests that compare the two kernels bit for bit), negative = only query.
+ * Returns the previous mode. A tuning switch in the manner of cublasSetMathMode; the reference has no counterpart. */
 PGB_API int pgb_gemm_pair_mode(int mode);
 
 /* Failure-detection drill: the NEXT tensor-core GEMM launched from this host thread polls each of its waits at most

@@ -138,8 +138,10 @@ __global__ void __launch_bounds__(kGemmThreads, 1)
           tc_fence_after();
           const uint32_t sa = smem_u32(tiles + s * kPairStageBytes);
           const uint64_t da = make_kmajor_sw128_desc(sa), db = make_kmajor_sw128_desc(sa + kTileABytes);
+          const int n_mma = kb == p.num_kb - 1 ? p.last_mmas : kSlabBytes / 32;
 #pragma unroll
-          for (int kk = 0; kk < kSlabBytes / 32; ++kk) tc_mma_pair<KIND>(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
+          for (int kk = 0; kk < kSlabBytes / 32; ++kk)
+            if (kk < n_mma) tc_mma_pair<KIND>(tmem_d, da + 2 * kk, db + 2 * kk, idesc, (kb | kk) != 0);
           // frees the stage in both CTAs when these MMAs have read it
           tc_commit_pair(my_empty + 8u * (uint32_t)s);
           tc_commit_pair(peer_empty + 8u * (uint32_t)s);

@@ -200,9 +200,14 @@ extern template int launch_gemm_pair<GEMM_TF32>(const CUtensorMap &, const CUten
 static std::atomic<int> g_pair_mode{1};
 int set_gemm_pair_mode(int mode) {
   if (mode < 0) return g_pair_mode.load();
-  return g_pair_mode.exchange(mode > 0 ? 1 : 0);
+  return g_pair_mode.exchange(mode > 3 ? 1 : mode);
 }
 static bool pair_enabled() { return g_pair_mode.load(std::memory_order_relaxed) != 0; }
+// modes 2 / 3 (measurement only): int8 layers too, 2 = their absmax-only pass, 3 = every pass
+static bool pair_int8(bool absmax_only) {
+  const int m = g_pair_mode.load(std::memory_order_relaxed);
+  return m == 3 || (m == 2 && absmax_only);
+}
 
 // A test hook: the next launch of the one-CTA kernel on this thread uses this many polls per wait instead of the
 // default and, if `skip_loads`, its producer issues no loads, so that the first wait runs out (nothing faults, nothing
@@ -279,7 +284,7 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   // contractions of 768 with wide outputs (qkv, lm_head), level (+-3 %) for long contractions and heavy epilogues,
   // 40 % slower when a tile is a single K slab (attention scores, K = 64), and 6-9 % slower for the int8 layers,
   // whose short tiles are bound by the epilogue's arithmetic and suffer from the coupling of two CTAs' epilogues.
-  if (fast && bn == 256 && M % (2 * kBM) == 0 && kind != GEMM_I8 && p.num_kb >= 4 && pair_enabled() && !p.skip_loads) {
+  if (fast && bn == 256 && M % (2 * kBM) == 0 && (kind != GEMM_I8 || pair_int8(absmax_only)) && p.num_kb >= 4 && pair_enabled() && !p.skip_loads) {
     CUtensorMap mb_half;
     if (make_operand_map(&mb_half, b, kind, N, K, ldb, nb0, nb1, b_bs0, b_bs1, bn / 2, "B") == PGB_OK) {
       GemmParams pp = p;

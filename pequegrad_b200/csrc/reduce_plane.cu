@@ -4,7 +4,7 @@
 // is k (README.md:59-63). No single thread mapping reads both with 128-byte requests, so the row and column kernels
 // refuse it, and the generic kernel pays 64-bit div / mod and the interpreter per element.
 //
-// Here thread (plane, j) walks k with every address precomputed: 32-bit offsets, eight k steps in flight, 128-bit
+// Here thread (plane, j) walks k with every address precomputed: 32-bit offsets, 8 or 16 k steps in flight, 128-bit
 // loads for an operand whose k axis is contiguous, the prologue as a decoded chain.
 // Consecutive threads read consecutive j of the j-contiguous operand (full requests) and neighbouring short rows of
 // the k-contiguous one, whose sectors the L1 serves on the following steps; every byte is fetched from L2 once.
@@ -35,8 +35,10 @@ struct ShortParams {
   EpiParams<float> epi;
 };
 
-template <int NIN, int ROP, bool LITE>
-__global__ void __launch_bounds__(kShortThreads, 4) reduce_short_kernel(const __grid_constant__ ShortParams<NIN> p) {
+// B = reduced steps whose loads are all issued before the first is used: 16 for short axes with a cheap prologue
+// (more would cost so many registers that the README case's 100 000 threads no longer fit the GPU in one wave), else 8.
+template <int NIN, int ROP, bool LITE, int B>
+__global__ void __launch_bounds__(kShortThreads, B > 8 ? 3 : 4) reduce_short_kernel(const __grid_constant__ ShortParams<NIN> p) {
   // 32-bit index arithmetic (the host checks that the output count fits): a 64-bit division costs more than the loop
   const uint32_t o = blockIdx.x * kShortThreads + threadIdx.x;
   if (o >= (uint32_t)p.n_out) return;
@@ -52,7 +54,6 @@ __global__ void __launch_bounds__(kShortThreads, 4) reduce_short_kernel(const __
   if (LITE) chain_decode<float>(p.pro, cr);
   Acc<float, ROP> acc;
   acc.init();
-  constexpr int B = 8;  // k steps in flight: their loads are all issued before the first is used
 #pragma unroll 1
   for (int k0 = 0; k0 < K; k0 += B) {
     float w[NIN][B], run[B];
@@ -116,8 +117,9 @@ int launch_short(ReduceJob &j, const ChainProg<float> &chain) {
   if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
   auto go = [&](auto rop_c) {
     constexpr int ROP = decltype(rop_c)::value;
-    if (chain.lite) reduce_short_kernel<NIN, ROP, true><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
-    else reduce_short_kernel<NIN, ROP, false><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    if (chain.lite && K <= 32) reduce_short_kernel<NIN, ROP, true, 16><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    else if (chain.lite) reduce_short_kernel<NIN, ROP, true, 8><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    else reduce_short_kernel<NIN, ROP, false, 8><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
   };
   if (j.rop == ROP_SUM) go(std::integral_constant<int, ROP_SUM>{});
   else if (j.rop == ROP_MAX) go(std::integral_constant<int, ROP_MAX>{});

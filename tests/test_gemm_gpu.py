@@ -298,10 +298,15 @@ class one_cta_kernel:
         K.gemm_pair_mode(self.old)
 
 
-def both_kernels(fn):
+def both_kernels(fn, pair_mode=1):
     """fn() through the CTA-pair kernel and through the one-CTA kernel: same MMAs in the same order, same epilogue,
-    so the results must be the same bits."""
-    got = fn()
+    so the results must be the same bits. pair_mode 3 sends int8 layers to the pair kernel too (they default to the
+    one-CTA kernel, which measured faster for them)."""
+    old = K.gemm_pair_mode(pair_mode)
+    try:
+        got = fn()
+    finally:
+        K.gemm_pair_mode(old)
     assert K.device_error() == 0
     with one_cta_kernel():
         want = fn()
@@ -320,7 +325,7 @@ def test_int8_layers_same_bits_with_and_without_the_pair_switch(M, N, K_):
     w = torch.randint(-127, 128, (N, K_), generator=g, device="cuda", dtype=torch.int8)
     ws = torch.rand(N, generator=g, device="cuda") * 0.01 + 0.001
     b = torch.randn(N, generator=g, device="cuda")
-    out, = both_kernels(lambda: K.qlinear_i8(a, w, ws, a_scale=0.02, bias=b, relu=True)[0])
+    out, = both_kernels(lambda: K.qlinear_i8(a, w, ws, a_scale=0.02, bias=b, relu=True)[0], pair_mode=3)
     acc = a[:300].cpu().numpy().astype(np.int32) @ w.cpu().numpy().astype(np.int32).T  # int32 accumulators on the CPU
     want = np.maximum(acc.astype(np.float32) * (np.float32(0.02) * ws.cpu().numpy())[None, :] + b.cpu().numpy()[None, :], 0)
     assert np.array_equal(out[:300].cpu().numpy(), want)
@@ -331,7 +336,7 @@ def test_int8_layers_same_bits_with_and_without_the_pair_switch(M, N, K_):
         q = torch.empty((M, N), dtype=torch.int8, device="cuda")
         K.qlinear_i8(a, w, ws, a_scale=0.02, bias=b, relu=True, out=q, out_absmax=am)
         return am, q
-    am, q = both_kernels(two_pass)
+    am, q = both_kernels(two_pass, pair_mode=3)
     assert float(am) == float(out.max())
 
 
