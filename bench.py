@@ -108,6 +108,18 @@ class ClockSampler:
                 "samples": len(sm), "reasons": sorted(reasons)}
 
 
+def library_record() -> dict:
+    """Which native library this process loaded: path inside the repository, size, modification time and a short
+    hash, so that a reader of the line can tell a freshly built library from a stale one."""
+    import hashlib
+    from pequegrad_b200 import _lib as L
+    p = L.LIB_PATH
+    h = hashlib.sha256(p.read_bytes()).hexdigest()[:16]
+    st = p.stat()
+    return {"path": str(p.relative_to(ROOT)), "sha16": h, "bytes": st.st_size, "mtime": int(st.st_mtime),
+            "version": L.lib().pgb_version().decode()}
+
+
 def host_threads() -> int:
     """All host cores this process may use; torchrun pins OMP_NUM_THREADS to 1 per rank, which the CPU arm (rank 0 only) undoes."""
     n = len(os.sched_getaffinity(0))
@@ -488,6 +500,7 @@ def main():
                     "what": "pinned host inputs copied to every rank's shards, the step with its gather, the result read back by rank 0; "
                             "h2d bytes are the sum over ranks"},
             "gpu_launches": int(launches), "cuda_graphs": graphs,
+            "library": library_record(),
             "roofline": roofline,
             "cpu_baseline": cpu,
         }
