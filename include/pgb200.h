@@ -350,9 +350,13 @@ PGB_API int pgb_gemm_wait_drill(unsigned int polls, int skip_loads);
  * buffer of world x slab bytes) with pgb_peer_alloc, exports both with pgb_peer_export, passes the 64-byte handles
  * to the other ranks by any host channel, and opens the others' with pgb_peer_open. peer_ctrl[r] / peer_dst[r] are
  * then rank r's control block / receive buffer as mapped in THIS process (its own allocation for r == rank).
- * Every rank must issue the same sequence of collective calls. A rank whose peer does not arrive within about half a
- * second records the error word of pgb_device_error (roles 10 and 11) and its kernel returns. */
+ * Every rank must issue the same sequence of collective calls. A rank whose peer does not arrive within the poll
+ * limit (one to two seconds by default) records the error word of pgb_device_error (roles 10 and 11) and its kernel
+ * returns. */
 PGB_API size_t pgb_peer_ctrl_bytes(void);
+/* Polls per wait of the two collective kernels below (default 2^21, one to two seconds); 0 only queries. Returns the
+ * previous value. Captured graphs keep the limit they were captured with. */
+PGB_API unsigned int pgb_peer_poll_limit(unsigned int polls);
 PGB_API int pgb_peer_alloc(size_t bytes, void **ptr);   /* zero-filled device memory that other processes can map */
 PGB_API int pgb_peer_free(void *ptr);
 PGB_API int pgb_peer_export(const void *ptr, unsigned char handle[64]);

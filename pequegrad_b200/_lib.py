@@ -59,7 +59,7 @@ EXPORTS = [
     "pgb_softmax_rows", "pgb_layernorm_rows", "pgb_fused_reduce_noalloc",
     "pgb_embedding_rows", "pgb_matmul", "pgb_attention", "pgb_qlinear_i8", "pgb_absmax_f32", "pgb_quantize_i8", "pgb_device_error",
     "pgb_gemm_pair_mode", "pgb_gemm_wait_drill",
-    "pgb_peer_ctrl_bytes", "pgb_peer_alloc", "pgb_peer_free", "pgb_peer_export", "pgb_peer_open", "pgb_peer_close",
+    "pgb_peer_ctrl_bytes", "pgb_peer_poll_limit", "pgb_peer_alloc", "pgb_peer_free", "pgb_peer_export", "pgb_peer_open", "pgb_peer_close",
     "pgb_peer_allreduce_max_f32", "pgb_peer_allgather",
 ]
 NOALLOC_SCRATCH_BYTES = 4 << 20  # PGB_NOALLOC_SCRATCH_BYTES
@@ -101,6 +101,8 @@ def lib() -> C.CDLL:
     L.pgb_gemm_pair_mode.argtypes = [C.c_int]
     L.pgb_gemm_wait_drill.argtypes = [C.c_uint, C.c_int]
     L.pgb_peer_ctrl_bytes.restype = C.c_size_t
+    L.pgb_peer_poll_limit.restype = C.c_uint
+    L.pgb_peer_poll_limit.argtypes = [C.c_uint]
     L.pgb_peer_alloc.argtypes = [C.c_size_t, C.POINTER(C.c_void_p)]
     L.pgb_peer_free.argtypes = [C.c_void_p]
     L.pgb_peer_export.argtypes = [C.c_void_p, C.c_char_p]

@@ -11,8 +11,10 @@
 // Every rank runs the same sequence of these calls. A contribution carries the number of the call it belongs to
 // (the epoch), packed with the value into one 64-bit store, so a reader can never take a stale value for a fresh
 // one; two banks alternate by epoch parity, and a rank cannot be two calls ahead of a peer (it needs the peer's
-// contribution to finish a call), so a bank is never overwritten before it was read. Every wait is bounded (about
-// half a second): a rank whose peer never arrives records the error word that pgb_device_error() reads and returns.
+// contribution to finish a call), so a bank is never overwritten before it was read. Every wait is bounded (2^21
+// polls with a 100 ns sleep, one to two seconds; pgb_peer_poll_limit changes it): a rank whose peer never arrives
+// records the error word that pgb_device_error() reads and returns.
+#include <atomic>
 #include <cstring>
 
 #include "reduce_common.cuh"
@@ -23,7 +25,7 @@ namespace pgb {
 namespace {
 
 constexpr int kMaxPeers = PGB_MAX_PEERS;
-constexpr unsigned kPeerPolls = 1u << 22;  // x ~100 ns of sleep per poll
+std::atomic<unsigned> g_peer_polls{1u << 21};  // x (~100 ns of sleep + one system-scope load) per poll
 
 struct PeerCtrl {
   unsigned long long max_slot[2][kMaxPeers];     // [epoch parity][source rank]: (epoch << 32) | float bits
@@ -48,8 +50,8 @@ __device__ __forceinline__ void st_sys(unsigned long long *p, unsigned long long
 }
 
 // Waits (bounded) until the local slot carries `epoch` in its upper half. Returns false on a timeout.
-__device__ __forceinline__ bool wait_epoch(const unsigned long long *slot, unsigned epoch, unsigned long long &v) {
-  for (unsigned i = 0; i < kPeerPolls; ++i) {
+__device__ __forceinline__ bool wait_epoch(const unsigned long long *slot, unsigned epoch, unsigned long long &v, unsigned polls) {
+  for (unsigned i = 0; i < polls; ++i) {
     v = ld_sys(slot);
     if ((unsigned)(v >> 32) == epoch) return true;
     __nanosleep(100);
@@ -57,7 +59,8 @@ __device__ __forceinline__ bool wait_epoch(const unsigned long long *slot, unsig
   return false;
 }
 
-__global__ void __launch_bounds__(32) peer_max_kernel(float *value, const __grid_constant__ PeerPtrs pp, int rank, int world, int *err) {
+__global__ void __launch_bounds__(32) peer_max_kernel(float *value, const __grid_constant__ PeerPtrs pp, int rank, int world, unsigned polls,
+                                                      int *err) {
   if (*(volatile int *)err != 0) return;
   PeerCtrl *me = pp.ctrl[rank];
   const int t = threadIdx.x;
@@ -71,7 +74,7 @@ __global__ void __launch_bounds__(32) peer_max_kernel(float *value, const __grid
   bool ok = true;
   if (t < world) {
     unsigned long long v = 0;
-    ok = wait_epoch(&me->max_slot[bank][t], epoch, v);
+    ok = wait_epoch(&me->max_slot[bank][t], epoch, v, polls);
     m = __uint_as_float((unsigned)(v & 0xffffffffu));
   }
   if (!__all_sync(0xffffffffu, ok)) {
@@ -86,7 +89,7 @@ __global__ void __launch_bounds__(32) peer_max_kernel(float *value, const __grid
 // grid = world x chunks CTAs: CTA (peer, chunk) copies a chunk of this rank's slab into the peer's buffer at
 // rank * bytes; the last CTA to finish announces the slab to every peer and waits for theirs.
 __global__ void __launch_bounds__(256) peer_gather_kernel(const uint4 *__restrict__ src, size_t bytes, const __grid_constant__ PeerPtrs pp,
-                                                          int rank, int world, int chunks, int *err) {
+                                                          int rank, int world, int chunks, unsigned polls, int *err) {
   if (*(volatile int *)err != 0) return;
   PeerCtrl *me = pp.ctrl[rank];
   const int peer = blockIdx.x / chunks, chunk = blockIdx.x - peer * chunks;
@@ -113,7 +116,7 @@ __global__ void __launch_bounds__(256) peer_gather_kernel(const uint4 *__restric
   bool ok = true;
   if (t < world) {
     unsigned long long v = 0;
-    ok = wait_epoch(&me->gather_flag[bank][t], epoch, v);
+    ok = wait_epoch(&me->gather_flag[bank][t], epoch, v, polls);
   }
   if (!__all_sync(0xffffffffu, ok) && t == 0) atomicCAS(err, 0, (11 << 16) | (rank & 0xffff));
 }
@@ -141,6 +144,10 @@ using namespace pgb;
 extern "C" {
 
 PGB_API size_t pgb_peer_ctrl_bytes(void) { return sizeof(PeerCtrl); }
+
+PGB_API unsigned int pgb_peer_poll_limit(unsigned int polls) {
+  return polls ? g_peer_polls.exchange(polls) : g_peer_polls.load();
+}
 
 PGB_API int pgb_peer_alloc(size_t bytes, void **ptr) {
   if (!ptr || bytes == 0) { set_error("peer_alloc: null result pointer or zero size"); return PGB_ERR_INVALID_ARG; }
@@ -201,7 +208,7 @@ PGB_API int pgb_peer_allreduce_max_f32(float *value, void *const *peer_ctrl, int
   if (st != PGB_OK) return st;
   int *err = gemm_error_word();
   if (!err) { set_error("peer_allreduce_max: cannot resolve the device error word"); return PGB_ERR_CUDA; }
-  peer_max_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(value, pp, rank, world, err);
+  peer_max_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(value, pp, rank, world, g_peer_polls.load(), err);
   count_launch();
   return check_launch("peer_max_kernel");
 }
@@ -218,7 +225,8 @@ PGB_API int pgb_peer_allgather(const void *src, size_t bytes, void *const *peer_
   // CTAs per peer (a 1.3 MB slab from 32 CTAs took 25 us)
   int chunks = (int)((bytes + (16 << 10) - 1) / (16 << 10));
   chunks = chunks < 1 ? 1 : (chunks > 64 ? 64 : chunks);
-  peer_gather_kernel<<<world * chunks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4 *>(src), bytes, pp, rank, world, chunks, err);
+  peer_gather_kernel<<<world * chunks, 256, 0, (cudaStream_t)stream>>>(static_cast<const uint4 *>(src), bytes, pp, rank, world, chunks,
+                                                                             g_peer_polls.load(), err);
   count_launch();
   return check_launch("peer_gather_kernel");
 }

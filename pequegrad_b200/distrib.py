@@ -190,6 +190,44 @@ def unshard_tensor(x: ShardedTensor, dim: int | None = 0, dev=None) -> torch.Ten
     return full.movedim(0, dim).contiguous()
 
 
+def reshard_tensor(x: ShardedTensor, dim: int, staging: torch.Tensor | None = None, out: torch.Tensor | None = None,
+                   copy_fn: Callable | None = None) -> ShardedTensor:
+    """The same tensor split along another dim, by ONE all-to-all: every process sends each peer the part of its
+    shard that falls into the peer's new slab (data that is already on the GPUs crosses NVLink once, instead of
+    being uploaded from the host a second time). One shard per process, even splits, and the old split dim must be
+    dim 0, so that the received blocks line up as the new shard without a copy. `staging` / `out` are optional
+    preallocated buffers of the shard's size; `copy_fn(dst, src)` replaces the torch copy that packs the blocks."""
+    rank, world = rank_world()
+    if x.dim is None or len(x.shards) != 1 or x.num_shards != world:
+        raise ValueError("reshard_tensor: needs a tensor split along one dim with one shard per process")
+    old = x.dim[0]
+    nd = x.shards[0].dim()
+    dim = dim + nd if dim < 0 else dim
+    if old != 0 or not 0 < dim < nd:
+        raise ValueError("reshard_tensor: the tensor must be split along dim 0 and the new dim must be another one")
+    local = x.shards[0]
+    if x.shape[0] % world or x.shape[dim] % world:
+        raise ValueError("reshard_tensor: both dims must divide evenly by the number of processes")
+    if world == 1:
+        return ShardedTensor([local], [dim], 1, x.shape)
+    n_new = x.shape[dim] // world
+    blk = list(local.shape)
+    blk[dim] = n_new
+    if staging is None:
+        staging = torch.empty([world] + blk, dtype=local.dtype, device=local.device)
+    send = staging.view([world] + blk)
+    # block s of the send buffer = this shard's rows, new-dim slab s
+    src = local.unflatten(dim, (world, n_new)).movedim(dim, 0)
+    if copy_fn is None:
+        send.copy_(src)
+    else:
+        copy_fn(send, src)
+    if out is None:
+        out = torch.empty([world * blk[0]] + blk[1:], dtype=local.dtype, device=local.device)
+    dist.all_to_all_single(out.view(-1), send.view(-1))
+    return ShardedTensor([out.view([world * blk[0]] + blk[1:])], [dim], world, x.shape)
+
+
 class GatherBucket:
     """Several sharded outputs gathered by ONE collective. Kernels write their output slabs into views of
     one flat buffer (`local_view`); `gather()` all-gathers that buffer; `full(i)` is output i assembled

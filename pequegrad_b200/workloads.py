@@ -171,6 +171,8 @@ class Sweep:
         shard_mb = {k: round(v.numel() * 4 / 1e6) for k, v in S.items()}
         self.config = {"cases": len(self.cases), "bytes_per_step": self.bytes_per_step, "partition": "kept axis of every case split over the GPUs",
                        "shard_MB_per_gpu": shard_mb, "gathered_bytes_per_step": self.gather_bytes if world > 1 else 0,
+                       "e2e_note": "each rank uploads its row shards of A and B once per step; the second sharding (column slabs of A, dim 1 of B) "
+                                   "is made on the devices by one all-to-all each" if world > 1 else "one GPU: A and B uploaded once per step",
                        "l2": ("each rank's shards (%s MB) against a 126 MB L2; consecutive launches alternate tensors, so a case never "
                               "finds its own input in L2 unless the shard is smaller than what ran in between" % "/".join(map(str, shard_mb.values())))}
 
@@ -227,18 +229,30 @@ class Sweep:
 
     def e2e_setup(self):
         import torch
-        self.host_in = {k: torch.empty(v.shape, dtype=torch.float32).pin_memory() for k, v in self.S.items()
-                        if self.world > 1 or k.endswith("0")}  # on one GPU both shardings are the same buffer
+        # Host buffers hold this rank's ROW shards only (dim 0 of A and of B). The second sharding of each tensor
+        # (column slabs of A, dim 1 of B, which the axis-0 cases need) is made on the devices from the row shards by
+        # one all-to-all each: the bytes cross NVLink once instead of PCIe a second time.
+        self.host_in = {k: torch.empty(v.shape, dtype=torch.float32).pin_memory() for k, v in self.S.items() if k.endswith("0")}
         for k, h in self.host_in.items():
             h.copy_(self.S[k])
+        self.staging = {k: torch.empty_like(v) for k, v in self.S.items() if k.endswith("0")} if self.world > 1 else {}
         self.host_out = [torch.empty(b.recv.numel(), dtype=torch.uint8).pin_memory() for b in self.buckets] if self.rank == 0 else []
         self.host_out += [torch.empty(dst.shape, dtype=dst.dtype).pin_memory() for _, _, dst in self.copies] if self.rank == 0 else []
         self.h2d = sum(v.numel() * 4 for v in self.host_in.values()) * self.world
         self.d2h = sum(o.numel() * o.element_size() for o in self.host_out)
 
     def e2e_step(self):
+        from . import distrib as D
+        from . import kernels as K
         for k, h in self.host_in.items():
             self.S[k].copy_(h, non_blocking=True)
+        if self.world > 1:
+            devs = _devices(self.world)
+            for name, shape in (("A", SHAPES["A"]), ("B", SHAPES["B"])):
+                if name + "0" in self.S:
+                    st = D.ShardedTensor([self.S[name + "0"]], [0], self.world, shape)
+                    D.reshard_tensor(st, 1, staging=self.staging[name + "0"], out=self.S[name + "1"],
+                                     copy_fn=lambda d, s_: K.fused_elementwise([s_], [("LOAD", 0)], outs=[d]))
         self.step()
         if self.rank == 0:  # the caller's process reads the gathered results
             srcs = [b.recv for b in self.buckets] + [dst for _, _, dst in self.copies]

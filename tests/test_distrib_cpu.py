@@ -74,6 +74,18 @@ def _worker(rank, world, port, scenario, q):
             with pytest.raises(ValueError):
                 D.all_reduce(torch.ones(3, dtype=torch.int32), "avg")
             q.put((rank, "ok"))
+        elif scenario == "reshard":
+            # rows -> column slabs (and a middle dim of a 3-D tensor) by one all-to-all
+            a = torch.randn((8, 6), generator=g)
+            cols = D.reshard_tensor(D.shard_tensor(a, world, 0, devs), 1)
+            assert cols.dim == [1] and torch.equal(cols.shards[0], D.shard_tensor(a, world, 1, devs).shards[0])
+            assert torch.equal(D.unshard_tensor(cols, 1), a)
+            b3 = torch.randn((4, 6, 5), generator=g)
+            mid = D.reshard_tensor(D.shard_tensor(b3, world, 0, devs), 1)
+            assert torch.equal(mid.shards[0], D.shard_tensor(b3, world, 1, devs).shards[0])
+            with pytest.raises(ValueError):
+                D.reshard_tensor(D.shard_tensor(a, world, 1, devs), 0)
+            q.put((rank, "ok"))
         elif scenario == "bucket":
             # several outputs behind one collective: slabs along dim 0 come back as views, other dims as one copy
             bk = D.GatherBucket("cpu")
@@ -135,7 +147,7 @@ def _run(scenario, world=2):
     return res
 
 
-@pytest.mark.parametrize("scenario", ["roundtrip", "pmap", "bucket", "matmul"])
+@pytest.mark.parametrize("scenario", ["roundtrip", "pmap", "reshard", "bucket", "matmul"])
 def test_two_ranks(scenario):
     assert _run(scenario) == {0: "ok", 1: "ok"}
 

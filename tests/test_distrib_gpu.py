@@ -84,7 +84,7 @@ def _worker(rank, world, port, q):
         wl.step()
         wl.step()
         torch.cuda.synchronize()
-        got = dict(wl.results())
+        got = {k_: v_.clone() for k_, v_ in wl.results()}  # the results are views of buffers the next step reuses
         g2 = torch.Generator(device=dev).manual_seed(2)
         T = {"A": torch.randn(W.SHAPES["A"], generator=g2, device=dev)}
         T["B"] = torch.randn(W.SHAPES["B"], generator=g2, device=dev)
@@ -99,7 +99,20 @@ def _worker(rank, world, port, q):
             else:
                 both_inf = torch.isinf(have) & torch.isinf(want)
                 assert torch.allclose(torch.where(both_inf, 0, have), torch.where(both_inf, 0, want), rtol=2e-5, atol=0), (name, op, ax)
-        del wl, T, got
+        # the end-to-end step: row shards uploaded from the host, the second sharding made by an all-to-all on the
+        # devices; the shards it rebuilds must be the ones the set-up made, and the results the same
+        b1_before, a1_before = wl.S["B1"].clone(), wl.S["A1"].clone()
+        wl.e2e_setup()
+        wl.S["B1"].zero_()
+        wl.S["A1"].zero_()
+        wl.e2e_step()
+        torch.cuda.synchronize()
+        assert torch.equal(wl.S["B1"], b1_before) and torch.equal(wl.S["A1"], a1_before)
+        again = dict(wl.results())
+        for k_, v_ in again.items():
+            if ".max." in k_ or ".argmax." in k_:
+                assert torch.equal(v_, got[k_]), k_
+        del wl, T, got, again
         torch.cuda.empty_cache()
 
         # the peer-memory collectives: a max of one float and a gather of small slabs, many calls in a row
@@ -167,3 +180,39 @@ def test_two_processes_over_nccl():
         if p.is_alive():
             p.kill()
     assert res == {0: "ok", 1: "ok"}, res
+
+
+def test_a_peer_that_never_arrives_is_reported_not_waited_for_forever():
+    """Failure detection on the device without a fault: rank 0 of a made-up group of two runs the max exchange, but
+    the control block standing in for rank 1 is a plain local allocation that nobody ever writes to. The kernel's
+    wait for rank 1's contribution must run out (a short poll limit keeps it to about a millisecond), the error
+    word must name the peer exchange (role 10), the value must be left alone, and the device must stay usable."""
+    import ctypes as C
+    lib = L.lib()
+    assert K.device_error() == 0
+    blocks = []
+    for _ in range(2):
+        p = C.c_void_p()
+        L.check(lib.pgb_peer_alloc(lib.pgb_peer_ctrl_bytes(), C.byref(p)))
+        blocks.append(p.value)
+    ctrl = (C.c_void_p * 2)(*blocks)
+    old = lib.pgb_peer_poll_limit(1 << 12)
+    try:
+        v = torch.tensor([3.5], device="cuda")
+        L.check(lib.pgb_peer_allreduce_max_f32(v.data_ptr(), ctrl, 0, 2, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()  # returns: the wait was bounded
+        code = C.c_int(0)
+        assert lib.pgb_device_error(C.byref(code), 1) == L.ERR_TIMEOUT
+        assert code.value >> 16 == 10 and (code.value & 0xffff) == 0
+        assert float(v) == 3.5
+        # with a group of one (this rank alone) the same kernel completes: its own contribution is all it needs
+        solo = (C.c_void_p * 1)(blocks[0])
+        L.check(lib.pgb_peer_allreduce_max_f32(v.data_ptr(), solo, 0, 1, torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert K.device_error() == 0 and float(v) == 3.5
+    finally:
+        lib.pgb_peer_poll_limit(old)
+        for b in blocks:
+            lib.pgb_peer_free(b)
+    x = torch.randn((64, 4096), device="cuda")
+    assert torch.equal(K.fused_reduce([x], L.MAX, [1]), x.amax(1))
