@@ -245,15 +245,17 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const __grid_consta
   const int lane = threadIdx.x & 31;
   const int64_t row = (int64_t)blockIdx.x * 8 + (threadIdx.x >> 5);
   if (row >= p.rows) return;
-  const IoT *xr = (const IoT *)p.x + row * p.C;
-  IoT *yr = (IoT *)p.y + row * p.C;
+  const int C = (int)p.C;  // at most 16 * 32 * V here: 32-bit column arithmetic
+  const IoT *xr = (const IoT *)p.x + row * C + lane * V;
+  IoT *yr = (IoT *)p.y + row * C + lane * V;
+  // vector u of this lane covers columns (u * 32 + lane) * V ..: inside the row for u < nu (C is a multiple of V)
+  const int nu = max(0, (C / V - lane + 31) >> 5);
   float v[NV][V];
   float s = 0.f;
 #pragma unroll
   for (int u = 0; u < NV; ++u) {
-    const int64_t c = ((int64_t)u * 32 + lane) * V;
-    if (c < p.C) {
-      load_vec<float, IoT, V>(xr + c, v[u]);
+    if (u < nu) {
+      load_vec<float, IoT, V>(xr + u * 32 * V, v[u]);
 #pragma unroll
       for (int e = 0; e < V; ++e) s += v[u][e];
     } else {
@@ -261,13 +263,12 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const __grid_consta
       for (int e = 0; e < V; ++e) v[u][e] = 0.f;
     }
   }
-  const float n = (float)p.C;
+  const float n = (float)C;
   const float mean = warp_sum(s) / n;
   float q = 0.f;
 #pragma unroll
   for (int u = 0; u < NV; ++u) {
-    const int64_t c = ((int64_t)u * 32 + lane) * V;
-    if (c < p.C) {
+    if (u < nu) {
 #pragma unroll
       for (int e = 0; e < V; ++e) {
         v[u][e] = v[u][e] - mean;
@@ -277,26 +278,27 @@ __global__ void __launch_bounds__(256) layernorm_warp_kernel(const __grid_consta
   }
   const float var = warp_sum(q) / n;
   const float rsd = 1.0f / sqrtf(var + p.eps);  // d * (1/sd) is within 1 ulp of the composite's d / sd
+  const IoT *gp = p.gamma ? (const IoT *)p.gamma + lane * V : nullptr;
+  const IoT *bp = p.beta ? (const IoT *)p.beta + lane * V : nullptr;
 #pragma unroll
   for (int u = 0; u < NV; ++u) {
-    const int64_t c = ((int64_t)u * 32 + lane) * V;
-    if (c < p.C) {
+    if (u < nu) {
       float o[V];
 #pragma unroll
       for (int e = 0; e < V; ++e) o[e] = v[u][e] * rsd;
-      if (p.gamma) {
+      if (gp) {
         float g[V];
-        load_vec_cached<float, IoT, V>((const IoT *)p.gamma + c, g);
+        load_vec_cached<float, IoT, V>(gp + u * 32 * V, g);
 #pragma unroll
         for (int e = 0; e < V; ++e) o[e] = o[e] * g[e];
       }
-      if (p.beta) {
+      if (bp) {
         float b[V];
-        load_vec_cached<float, IoT, V>((const IoT *)p.beta + c, b);
+        load_vec_cached<float, IoT, V>(bp + u * 32 * V, b);
 #pragma unroll
         for (int e = 0; e < V; ++e) o[e] = o[e] + b[e];
       }
-      store_vec<IoT, float, V>(yr + c, o);
+      store_vec<IoT, float, V>(yr + u * 32 * V, o);
     }
   }
 }

@@ -236,6 +236,7 @@ class Sweep:
         for k, h in self.host_in.items():
             h.copy_(self.S[k])
         self.staging = {k: torch.empty_like(v) for k, v in self.S.items() if k.endswith("0")} if self.world > 1 else {}
+        self.reshard_ok = True
         self.host_out = [torch.empty(b.recv.numel(), dtype=torch.uint8).pin_memory() for b in self.buckets] if self.rank == 0 else []
         self.host_out += [torch.empty(dst.shape, dtype=dst.dtype).pin_memory() for _, _, dst in self.copies] if self.rank == 0 else []
         self.h2d = sum(v.numel() * 4 for v in self.host_in.values()) * self.world
@@ -246,13 +247,24 @@ class Sweep:
         from . import kernels as K
         for k, h in self.host_in.items():
             self.S[k].copy_(h, non_blocking=True)
-        if self.world > 1:
-            devs = _devices(self.world)
-            for name, shape in (("A", SHAPES["A"]), ("B", SHAPES["B"])):
-                if name + "0" in self.S:
-                    st = D.ShardedTensor([self.S[name + "0"]], [0], self.world, shape)
-                    D.reshard_tensor(st, 1, staging=self.staging[name + "0"], out=self.S[name + "1"],
-                                     copy_fn=lambda d, s_: K.fused_elementwise([s_], [("LOAD", 0)], outs=[d]))
+        if self.world > 1 and self.reshard_ok:
+            try:
+                for name, shape in (("A", SHAPES["A"]), ("B", SHAPES["B"])):
+                    if name + "0" in self.S:
+                        st = D.ShardedTensor([self.S[name + "0"]], [0], self.world, shape)
+                        D.reshard_tensor(st, 1, staging=self.staging[name + "0"], out=self.S[name + "1"],
+                                         copy_fn=lambda d, s_: K.fused_elementwise([s_], [("LOAD", 0)], outs=[d]))
+            except (RuntimeError, ValueError) as e:  # the same refusal on every rank: upload the second sharding too
+                import torch
+                self.reshard_ok = False
+                self.config["e2e_note"] = f"re-sharding on the devices refused ({e}); both shardings are uploaded from the host"
+                self.host_in1 = {k: torch.empty(v.shape, dtype=torch.float32).pin_memory() for k, v in self.S.items() if k.endswith("1")}
+                for k, h in self.host_in1.items():
+                    h.copy_(self.S[k])
+                self.h2d += sum(v.numel() * 4 for v in self.host_in1.values()) * self.world
+        if self.world > 1 and not self.reshard_ok:
+            for k, h in self.host_in1.items():
+                self.S[k].copy_(h, non_blocking=True)
         self.step()
         if self.rank == 0:  # the caller's process reads the gathered results
             srcs = [b.recv for b in self.buckets] + [dst for _, _, dst in self.copies]
