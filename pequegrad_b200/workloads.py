@@ -71,6 +71,65 @@ def _event_us(fn, reps, flush=None):
     return statistics.median(a.elapsed_time(b) for a, b in evs) * 1e3
 
 
+def _graph_us(fns, launches=48):
+    """Mean device time per call, in microseconds, of `launches` calls cycling through `fns`, replayed as ONE CUDA
+    graph between one pair of events. For kernels of a few tens of microseconds: a single launch between two events
+    is read with the granularity of the event timestamps (about 2 us here: every single-launch figure of a short
+    kernel came out as a multiple of 2.05 us), and kernel-by-kernel launches from Python leave the GPU idle between
+    calls. A ring of buffer sets larger than the L2 in `fns` makes every call a cold one. Falls back to
+    single-launch timing when the capture fails."""
+    import torch
+    n = len(fns)
+
+    def run():
+        for i in range(launches):
+            fns[i % n]()
+    g = capture_graph(run)
+    if g is None:
+        return _event_us(fns[0], 20)
+    ts = []
+    for _ in range(5):
+        a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        a.record()
+        g.replay()
+        b.record()
+        torch.cuda.synchronize()
+        ts.append(a.elapsed_time(b) * 1e3 / launches)
+    return statistics.median(ts)
+
+
+def _graph_us_flushed(fn, flush, rounds=6):
+    """Device time of fn() in microseconds when every call comes right after `flush()` (kernels that leave nothing of
+    fn's operands in L2): `rounds` x (flush, fn) replayed as one graph, minus `rounds` x flush replayed as another,
+    divided by `rounds`. The event pair then brackets milliseconds, not one short kernel, so the timestamps'
+    granularity (about 2 us) and the event overhead drop out. Falls back to single-launch timing if a capture fails."""
+    import torch
+
+    def both():
+        for _ in range(rounds):
+            flush()
+            fn()
+
+    def only_flush():
+        for _ in range(rounds):
+            flush()
+    g1, g0 = capture_graph(both), capture_graph(only_flush)
+    if g1 is None or g0 is None:
+        return _event_us(fn, 10, flush)
+
+    def t(g):
+        ts = []
+        for _ in range(5):
+            a, b = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            a.record()
+            g.replay()
+            b.record()
+            torch.cuda.synchronize()
+            ts.append(a.elapsed_time(b) * 1e3)
+        return statistics.median(ts)
+    return max(0.0, (t(g1) - t(g0)) / rounds)
+
+
 class _L2Flush:
     """201 MB written, then another 201 MB read: the L2 (126 MB) ends up holding clean lines of unrelated data, as it
     would after the kernels that run between two uses of a buffer. Writing alone leaves the L2 full of dirty lines,
@@ -286,20 +345,17 @@ class Sweep:
         return picked
 
     def roofline(self, pk, reps):
-        """Per-case device time on this rank's shards (CUDA events around each launch), grouped by kernel family."""
-        import torch
+        """Per-case device time on this rank's shards (each case right after kernels over other buffers, six rounds
+        replayed as one graph, the flushing kernels' own time subtracted), grouped by kernel family."""
         prepared, per_case = self.prepared, []
         for name, op, ax, nbytes, pr in prepared:
-            evs = [(torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)) for _ in range(reps)]
-            for a, b in evs:
-                for o in self._flushers(pr):  # nothing of this case's input is left in L2
+            fl = self._flushers(pr)  # cases over other buffers: nothing of this case's input is left in L2
+
+            def flush(fl=fl):
+                for o in fl:
                     o()
-                a.record()
-                pr()
-                b.record()
-            torch.cuda.synchronize()
-            t = statistics.median(a.elapsed_time(b) for a, b in evs)
-            per_case.append({"case": f"{name}.{op}.ax{ax}", "us": round(t * 1e3, 2), "gbs": round(nbytes / t / 1e6, 1),
+            us = _graph_us_flushed(pr, flush)
+            per_case.append({"case": f"{name}.{op}.ax{ax}", "us": round(us, 2), "gbs": round(nbytes / us / 1e3, 1),
                              "kernel": pr.plan.split()[0], "bytes": nbytes})
         self.per_case = per_case
         fam = {}
@@ -478,20 +534,20 @@ class Mlp:
         b = self.mlp._buffers(rows, self.X.device)
         xq, amax = b["q"][1], b["amax"]
         flush = _L2Flush(self.X.device)  # nothing of the operands stays in L2
-        t_abs = _event_us(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, want_out=False, out_absmax=amax[2:3]), reps, flush)
-        t_q = _event_us(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, out=b["q"][2], out_absmax=amax[2:3]), reps, flush)
-        t_f = _event_us(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, out=b["h"][1]), reps, flush)
-        t_in = _event_us(lambda: K.qlinear_i8(b["q"][0], self.mlp.layers[0][0], self.mlp.layers[0][1], a_absmax=amax[0:1], bias=self.mlp.layers[0][2],
-                                              relu=True, out=b["q"][1], out_absmax=amax[1:2]), reps, flush)
+        t_abs = _graph_us_flushed(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, want_out=False, out_absmax=amax[2:3]), flush)
+        t_q = _graph_us_flushed(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, out=b["q"][2], out_absmax=amax[2:3]), flush)
+        t_f = _graph_us_flushed(lambda: K.qlinear_i8(xq, wq, ws, a_absmax=amax[1:2], bias=bias, relu=True, out=b["h"][1]), flush)
+        t_in = _graph_us_flushed(lambda: K.qlinear_i8(b["q"][0], self.mlp.layers[0][0], self.mlp.layers[0][1], a_absmax=amax[0:1], bias=self.mlp.layers[0][2],
+                                                      relu=True, out=b["q"][1], out_absmax=amax[1:2]), flush)
         ops = 2.0 * rows * 1024 * 1024
         i8 = measure_int8_peak(self.X.device)
         peak = i8["burst"]
         us = max(t_abs, t_q)
         ach = ops / (us * 1e-6) / 1e12
         tops = lambda t, o=ops: round(o / (t * 1e-6) / 1e12, 1)  # noqa: E731
-        other = {"absmax_f32_us": round(_event_us(lambda: K.absmax(self.X, out=amax[0:1]), reps, flush), 1),
-                 "quantize_input_us": round(_event_us(lambda: K.quantize_i8(self.X, absmax_dev=amax[0:1], out=b["q"][0]), reps, flush), 1),
-                 "quantize_hidden_us (materialising route only)": round(_event_us(lambda: K.quantize_i8(b["h"][1], absmax_dev=amax[2:3], out=b["q"][2]), reps, flush), 1)}
+        other = {"absmax_f32_us": round(_graph_us_flushed(lambda: K.absmax(self.X, out=amax[0:1]), flush), 1),
+                 "quantize_input_us": round(_graph_us_flushed(lambda: K.quantize_i8(self.X, absmax_dev=amax[0:1], out=b["q"][0]), flush), 1),
+                 "quantize_hidden_us (materialising route only)": round(_graph_us_flushed(lambda: K.quantize_i8(b["h"][1], absmax_dev=amax[2:3], out=b["q"][2]), flush), 1)}
         del flush
         x_bytes = self.X.numel() * 4
         other["absmax_f32_gbs"] = round(x_bytes / other["absmax_f32_us"] / 1e3, 1)
@@ -700,13 +756,27 @@ class Rows:
         flush = _L2Flush(self.dev)
         w = self.world
         sm_us = _event_us(lambda: K.softmax_rows(self.S, causal=True), reps, flush=flush if w > 1 else None)
-        ln_us = _event_us(lambda: K.layernorm_rows(self.X, self.gamma, self.beta, 1e-5), reps, flush=flush)
-        # yardstick: the vendor's device copy of the same tensor (the same bytes read and written, no arithmetic, no
-        # row dependency), timed the same way; a 100 MB kernel pays launch, ramp and tail out of 15 us
+        ln_single_us = _event_us(lambda: K.layernorm_rows(self.X, self.gamma, self.beta, 1e-5), reps, flush=flush)
+        # The LayerNorm launch is short enough for the event timestamps' granularity to matter: time 48 launches in one
+        # graph over a ring of five input / output pairs (500 MB over all GPUs' worth of rows: no launch finds its rows
+        # in L2). Yardstick: the vendor's device copy of the same tensors (the same bytes, no arithmetic, no row
+        # dependency), timed the same way.
         import torch
-        y = torch.empty_like(self.X)
-        copy_us = _event_us(lambda: y.copy_(self.X), reps, flush=flush)
-        del flush, y
+        ring = [(self.X if i == 0 else self.X.clone(), torch.empty_like(self.X)) for i in range(5 if w == 1 else 9)]
+        xd = [(K.desc(a), K.desc(b)) for a, b in ring]
+        from . import _lib as L_
+        import ctypes as C_
+        gd, bd = K.desc(self.gamma), K.desc(self.beta)
+        lib = L_.lib()
+
+        def ln_call(i):
+            def f():
+                L_.check(lib.pgb_layernorm_rows(C_.byref(xd[i][0]), C_.byref(gd), C_.byref(bd), 1e-5, C_.byref(xd[i][1]),
+                                                torch.cuda.current_stream().cuda_stream))
+            return f
+        ln_us = _graph_us([ln_call(i) for i in range(len(ring))])
+        copy_us = _graph_us([(lambda a=a, b=b: b.copy_(a)) for a, b in ring])
+        del flush, ring
         ach = self.sm_bytes / w / (sm_us * 1e-6) / 1e9
         tri = self.sm_bytes_triangle / w / (sm_us * 1e-6) / 1e9
         ln = self.ln_bytes / w / (ln_us * 1e-6) / 1e9
@@ -714,8 +784,10 @@ class Rows:
                 "frac": round(ach / pk["hbm"], 4), "peak_source": pk["source"], "traffic": None, "us": round(sm_us, 1),
                 "algorithmic_bytes_per_launch": self.sm_bytes // w,
                 "counting_only_the_triangle_read": {"bytes": self.sm_bytes_triangle // w, "gbs": round(tri, 1), "frac": round(tri / pk["hbm"], 4)},
-                "layernorm": {"gbs": round(ln, 1), "frac": round(ln / pk["hbm"], 4), "us": round(ln_us, 1), "bytes": self.ln_bytes // w,
-                              "device_copy_of_the_same_tensor_us": round(copy_us, 1)}}
+                "layernorm": {"gbs": round(ln, 1), "frac": round(ln / pk["hbm"], 4), "us": round(ln_us, 2), "bytes": self.ln_bytes // w,
+                              "timing": "mean of 48 launches replayed as one CUDA graph over a ring of buffers larger than the L2",
+                              "single_launch_between_two_events_us": round(ln_single_us, 1),
+                              "device_copy_of_the_same_tensor_us": round(copy_us, 2)}}
 
 
 class Readme:
@@ -739,14 +811,27 @@ class Readme:
         self.calls = [K.PreparedReduce([x.permute(0, 2, 1), y], L.SUM, [2], False, README_PRO, README_EPI) for x, y in self.pairs]
         self.stream = torch.cuda.current_stream().cuda_stream
         self.bytes = 8_000_000 + 8_000_000 + 400_000
-        self.units_per_step = 1.0
-        self.i = 0
+        self.units_per_step = float(self.RING)  # calls per step
         self.config = {"algorithmic_bytes": self.bytes, "kernel": self.calls[0].plan,
-                       "l2": f"timed step = the cold case: a ring of {self.RING} buffer pairs (262 MB) so no call finds its inputs in L2; warm time in roofline"}
+                       "l2": f"a timed step = {self.RING} calls, one per buffer pair of a ring (262 MB in all), so no call finds its inputs in L2; "
+                             "value = microseconds per call; the warm time is in roofline"}
+
+    graph = None
+
+    def _ring(self):
+        for c in self.calls:
+            self.out = c()
+
+    def enable_graphs(self):
+        self.graph = capture_graph(self._ring)
+        return self.graph is not None
 
     def step_compute(self):
-        self.i = (self.i + 1) % self.RING
-        self.out = self.calls[self.i](self.stream)
+        """One pass over the ring: RING calls, each on a buffer pair that has left the L2 since its last turn."""
+        if self.graph is not None:
+            self.graph.replay()
+        else:
+            self._ring()
 
     step = step_compute  # 16 MB, launch-latency bound: not partitioned; with several GPUs every rank runs the whole case
 
@@ -763,12 +848,12 @@ class Readme:
         x, y = self.pairs[0]
         x.copy_(self.host_x, non_blocking=True)
         y.copy_(self.host_y, non_blocking=True)
-        self.host_out.copy_(self.calls[0](self.stream), non_blocking=True)
+        self.host_out.copy_(self.calls[0](), non_blocking=True)
 
     def roofline(self, pk, reps):
-        reps = max(reps, 20)
-        warm = _event_us(lambda: self.calls[0](self.stream), reps)
-        cold = _event_us(self.step_compute, reps)
+        # 48 launches per graph: a single launch of a 10 us kernel is below what two events resolve
+        warm = _graph_us([lambda: self.calls[0]()])
+        cold = _graph_us([(lambda c=c: c()) for c in self.calls])
         gbs = self.bytes / (cold * 1e-6) / 1e9
         return {"bound": "hbm", "kernel": self.calls[0].plan.split()[0], "achieved": round(gbs, 1), "peak": pk["hbm"], "unit": "GB/s",
                 "frac": round(gbs / pk["hbm"], 4), "peak_source": pk["source"], "traffic": None,
