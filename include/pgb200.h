@@ -319,11 +319,11 @@ PGB_API int pgb_absmax_f32(const pgb_tensor *x, float *absmax_dev, void *stream)
 PGB_API int pgb_quantize_i8(const pgb_tensor *x, const float *absmax_dev, float scale, const pgb_tensor *q,
                             void *stream);
 
-/* Error word of the kernels' bounded device-side waits (every mbarrier wait of the tensor-core GEMMs, the fused
- * attention and the streaming LayerNorm gives up after a fixed number of polls instead of hanging). Synchronises
- * with the device. *code = 0 and PGB_OK when no wait ran out; else *code = (role << 16) | block (roles: 1 producer,
- * 2 MMA issuer, 3 epilogue, 4-7 other roles of the GEMM / attention kernels, 8-9 streaming LayerNorm) and the
- * return value is PGB_ERR_TIMEOUT. While the word is set, later launches of those kernels return at once without
+/* Error word of the kernels' bounded device-side waits (every mbarrier wait of the tensor-core GEMMs and of the fused
+ * attention gives up after a fixed number of polls instead of hanging). Synchronises with the device. *code = 0 and
+ * PGB_OK when no wait ran out; else *code = (role << 16) | block (roles: 1 producer, 2 MMA issuer, 3 epilogue of the
+ * GEMM kernels; 10, 11 the peer collectives; 16-26 the attention kernel's producer, MMA issuer and softmax waits) and
+ * the return value is PGB_ERR_TIMEOUT. While the word is set, later launches of those kernels return at once without
  * computing; `reset` clears it. Replaces nothing in the reference, whose kernels never wait on one another. */
 PGB_API int pgb_device_error(int *code, int reset);
 
