@@ -445,9 +445,17 @@ def main():
     time.sleep(0.2)
     ms_total = timed_steps(wl.step, args.steps, barrier, nvtx="pgb_timed")
     ms_compute = timed_steps(wl.step_compute, args.steps, barrier)
-    roofline = wl.roofline(pk, max(5, min(args.steps, 20))) if rank == 0 else None  # per-kernel device times, still under the clock sampler
     barrier()
     clocks = sampler.stop()
+    # per-kernel device times, under a clock record of their own (the peak measurements inside run for seconds at the
+    # power cap and would otherwise decide the median of the timed steps' record)
+    roofline = None
+    if rank == 0:
+        sampler = ClockSampler(local_rank)
+        sampler.start()
+        roofline = wl.roofline(pk, max(5, min(args.steps, 20)))
+        roofline["clocks"] = sampler.stop()
+    barrier()
 
     # end to end through the public call: pinned host inputs -> device, the step, results -> host
     wl.e2e_setup()

@@ -650,7 +650,9 @@ class Gpt2:
             self.host_ids.copy_(ids, non_blocking=True)
 
     def roofline(self, pk, reps):
-        """The MLP up-projection GEMM (tokens x 3072 x 768, + bias + tanh GELU, fp16 out) timed alone, and per-kernel shares of a layer."""
+        """The MLP up-projection GEMM (tokens x 3072 x 768, + bias + tanh GELU, fp16 out) timed alone, and per-kernel shares of a
+        layer: each kernel eight times back to back in one graph replay (activations of 50 to 200 MB per kernel against a
+        126 MB L2; no launch gaps, as inside the step)."""
         import torch
         from . import kernels as K
         dev = self.idx.device
@@ -660,7 +662,7 @@ class Gpt2:
         g = torch.Generator(device=dev).manual_seed(7)
         h = (torch.randn((M, C), generator=g, device=dev) * 0.5).half()
         out = torch.empty((M, 4 * C), dtype=torch.float16, device=dev)
-        us = _event_us(lambda: K.matmul(h, blk["fc_wt"].T, bias=blk["fc_b"], act=2, out=out), reps)
+        us = _graph_us([lambda: K.matmul(h, blk["fc_wt"].T, bias=blk["fc_b"], act=2, out=out)], 8)
         flops = 2.0 * M * C * 4 * C
         ach = flops / (us * 1e-6) / 1e12
         parts = {}
@@ -669,14 +671,14 @@ class Gpt2:
         H, D = self.cfg.n_head, C // self.cfg.n_head
         q, k, v = (qkv[:, :, i * C:(i + 1) * C].view(Bl, self.T, H, D).permute(0, 2, 1, 3) for i in range(3))
         y = torch.empty((Bl, self.T, C), dtype=torch.float16, device=dev)
-        parts["layernorm"] = _event_us(lambda: K.layernorm_rows(x3, blk["ln1_g"], blk["ln1_b"], 1e-5), reps)
-        parts["qkv_gemm"] = _event_us(lambda: K.matmul(x3, blk["attn_wt"].T, bias=blk["attn_b"], out=qkv), reps)
+        parts["layernorm"] = _graph_us([lambda: K.layernorm_rows(x3, blk["ln1_g"], blk["ln1_b"], 1e-5)], 8)
+        parts["qkv_gemm"] = _graph_us([lambda: K.matmul(x3, blk["attn_wt"].T, bias=blk["attn_b"], out=qkv)], 8)
         y_heads = y.view(Bl, self.T, H, D).permute(0, 2, 1, 3)
-        parts["fused_attention"] = _event_us(lambda: K.attention(q, k, v, scale=0.125, causal=True, out=y_heads), reps)
-        parts["proj_gemm"] = _event_us(lambda: K.matmul(y, blk["proj_wt"].T, bias=blk["proj_b"], residual=x3, out=y), reps)
+        parts["fused_attention"] = _graph_us([lambda: K.attention(q, k, v, scale=0.125, causal=True, out=y_heads)], 8)
+        parts["proj_gemm"] = _graph_us([lambda: K.matmul(y, blk["proj_wt"].T, bias=blk["proj_b"], residual=x3, out=y)], 8)
         parts["fc_gemm_gelu"] = us
-        parts["fc2_gemm"] = _event_us(lambda: K.matmul(out.view(Bl, self.T, 4 * C), blk["fc2_wt"].T, bias=blk["fc2_b"], residual=x3, out=y), reps)
-        parts["lm_head_gemm"] = _event_us(lambda: K.matmul(x3, self.model.lm_head_t.T, out=self.logits_buf[:, :, : self.cfg.vocab_size]), max(3, reps // 2))
+        parts["fc2_gemm"] = _graph_us([lambda: K.matmul(out.view(Bl, self.T, 4 * C), blk["fc2_wt"].T, bias=blk["fc2_b"], residual=x3, out=y)], 8)
+        parts["lm_head_gemm"] = _graph_us([lambda: K.matmul(x3, self.model.lm_head_t.T, out=self.logits_buf[:, :, : self.cfg.vocab_size])], 3)
         att_flops = 2.0 * 2.0 * Bl * H * self.T * ((self.T + 1) / 2.0) * D
         return {"bound": "tensor", "kernel": "gemm_tc_kernel<f16> %dx3072x768 + bias + GELU epilogue" % M, "achieved": round(ach, 1),
                 "peak": pk["f16_sustained"], "unit": "TFLOP/s", "frac": round(ach / pk["f16_sustained"], 4),
