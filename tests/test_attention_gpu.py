@@ -63,6 +63,27 @@ def test_heads_inside_packed_buffers_and_cross_lengths():
     check(K.attention(q3, k3, v3), composite(q3, k3, v3, False, 0.125), "cross lengths")
 
 
+@pytest.mark.parametrize("B,H,T,Tk,causal,dtype", [(4, 12, 1024, 1024, True, torch.float16), (50, 12, 128, 128, True, torch.float16),
+                                                   (3, 40, 300, 384, False, torch.bfloat16), (7, 12, 200, 200, True, torch.float16),
+                                                   (40, 16, 1, 130, False, torch.float16)])
+def test_more_work_items_than_resident_ctas(B, H, T, Tk, causal, dtype):
+    # The kernel is persistent (two CTAs per SM): with more (batch, head, query block) items than CTAs every CTA walks
+    # several items back to back, with its loads and MMAs already in the next item while the softmax of the current one
+    # finishes and the previous item's result written out inside the next item's first block. Items of one key block,
+    # of several, ragged last blocks and a different mix per CTA.
+    g = torch.Generator(device="cuda").manual_seed(11)
+    q = torch.randn((B, H, T, 64), generator=g, device="cuda").to(dtype)
+    k, v = (torch.randn((B, H, Tk, 64), generator=g, device="cuda").to(dtype) for _ in range(2))
+    out = torch.full((B, H, T, 64), float("nan"), device="cuda", dtype=dtype)
+    K.attention(q, k, v, causal=causal, out=out)
+    for lo in range(0, B, 8):  # the composite materialises [b, H, T, Tk] fp32 scores: a few batches at a time
+        check(out[lo:lo + 8], composite(q[lo:lo + 8], k[lo:lo + 8], v[lo:lo + 8], causal, 0.125), f"batches {lo}..")
+    # the same call again gives the same bits (nothing depends on which CTA took which item)
+    out2 = torch.empty_like(out)
+    K.attention(q, k, v, causal=causal, out=out2)
+    assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
+
+
 def test_attention_errors():
     q = torch.zeros((1, 1, 16, 32), device="cuda", dtype=torch.float16)
     with pytest.raises(RuntimeError, match="head dim of 64"):
