@@ -293,7 +293,9 @@ def reference_cuda_leg(wl, reps=10):
 def make_workload(args):
     from pequegrad_b200 import workloads as W
     if args.workload == "sweep":
-        return W.Sweep(args.only, args.bare)
+        wl = W.Sweep(args.only, args.bare)
+        wl.lanes = max(1, args.lanes)
+        return wl
     if args.workload == "mlp":
         return W.Mlp(args.rows or W.MLP_ROWS)
     if args.workload == "gpt2":
@@ -393,6 +395,7 @@ def main():
     ap.add_argument("--no-graph", action="store_true", help="launch every kernel of a step separately instead of replaying CUDA graphs")
     ap.add_argument("--no-others", action="store_true", help="sweep only: skip the short runs of the other workloads")
     ap.add_argument("--only", default="", help="sweep: comma-separated tensor names (A,B,Bp) to restrict the sweep, for profiling")
+    ap.add_argument("--lanes", type=int, default=2, help="sweep: streams the independent cases of a step alternate over (1 = one after another)")
     ap.add_argument("--bare", action="store_true", help="sweep diagnostic: no prologue / epilogue (not the benchmark workload)")
     ap.add_argument("--rows", type=int, default=0, help="mlp: rows in total (default 65536; smaller for profiling)")
     ap.add_argument("--batch", type=int, default=0, help="gpt2: sequences in total (default 32; smaller for profiling)")

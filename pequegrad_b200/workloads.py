@@ -229,6 +229,7 @@ class Sweep:
         self.gather_bytes = sum(b.nbytes for b in self.buckets) * world
         shard_mb = {k: round(v.numel() * 4 / 1e6) for k, v in S.items()}
         self.config = {"cases": len(self.cases), "bytes_per_step": self.bytes_per_step, "partition": "kept axis of every case split over the GPUs",
+                       "streams": "the independent cases of a step alternate over %d streams that fork from and join the timed one" % self.lanes,
                        "shard_MB_per_gpu": shard_mb, "gathered_bytes_per_step": self.gather_bytes if world > 1 else 0,
                        "e2e_note": "each rank uploads its row shards of A and B once per step; the second sharding (column slabs of A, dim 1 of B) "
                                    "is made on the devices by one all-to-all each" if world > 1 else "one GPU: A and B uploaded once per step",
@@ -237,9 +238,35 @@ class Sweep:
 
     graphs = None
 
+    lanes = 2
+
     def _launch(self, lo, hi):
-        for *_, pr in self.prepared[lo:hi]:
-            pr()
+        """The cases lo..hi, which do not depend on one another, alternating over `lanes` streams that fork from and
+        join the current one: the ramp and the last partial wave of one kernel run under its neighbour's full waves
+        (on a shard of an eighth of A a kernel is all ramp and tail)."""
+        import torch
+        if self.lanes <= 1 or hi - lo < 2:
+            for *_, pr in self.prepared[lo:hi]:
+                pr()
+            return
+        main = torch.cuda.current_stream()
+        if getattr(self, "_side", None) is None:
+            self._side = [torch.cuda.Stream(device=self.dev) for _ in range(self.lanes - 1)]
+        fork = torch.cuda.Event()
+        fork.record(main)
+        for st in self._side:
+            st.wait_event(fork)
+        for i, (*_, pr) in enumerate(self.prepared[lo:hi]):
+            lane = i % self.lanes
+            if lane == 0:
+                pr()
+            else:
+                with torch.cuda.stream(self._side[lane - 1]):
+                    pr()
+        for st in self._side:
+            join = torch.cuda.Event()
+            join.record(st)
+            main.wait_event(join)
 
     def enable_graphs(self):
         """The launches of a step as two CUDA graphs (the axis-0 cases, then the rest), with the gathers between them."""
