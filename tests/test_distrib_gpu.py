@@ -59,6 +59,31 @@ def test_one_process_holding_every_shard():
     assert torch.equal(D.unshard_tensor(outs, 0), _reduce(L.ARGMAX, 0)(x))
 
 
+def test_sweep_on_two_streams_and_as_graphs_gives_the_same_bits():
+    # the benchmark launches the independent cases of a step alternately on two streams that fork from and join the
+    # timed one, inside CUDA graphs: same results, bit for bit, as one kernel after another
+    from pequegrad_b200 import workloads as W
+    torch.cuda.set_device(0)
+    res = {}
+    for lanes, graphs in ((1, False), (2, False), (2, True), (3, True)):
+        wl = W.Sweep(only="A,Bp")
+        wl.lanes = lanes
+        wl.setup(torch.device("cuda:0"), 0, 1)
+        if graphs:
+            assert wl.enable_graphs()
+        wl.step()
+        wl.step()
+        torch.cuda.synchronize()
+        res[(lanes, graphs)] = {k_: v_.clone() for k_, v_ in wl.results()}
+        del wl
+        torch.cuda.empty_cache()
+    base = res[(1, False)]
+    assert len(base) == 24
+    for key, r in res.items():
+        for name, t in r.items():
+            assert torch.equal(t.view(torch.int32), base[name].view(torch.int32)), (key, name)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
