@@ -337,10 +337,10 @@ PGB_API int pgb_device_error(int *code, int reset);
  * Returns the previous mode. A tuning switch in the manner of cublasSetMathMode; the reference has no counterpart. */
 PGB_API int pgb_gemm_pair_mode(int mode);
 
-/* Failure-detection drill: the NEXT tensor-core GEMM launched from this host thread polls each of its waits at most
- * `polls` times and, with skip_loads != 0, its producer issues no loads, so the wait of its MMA warp runs out: the
- * kernel records the error word above, frees its tensor memory and returns; nothing faults or hangs. Used by the
- * tests to exercise the timeout path; no counterpart in the reference. */
+/* Failure-detection drill: the NEXT tensor-core GEMM or fused attention launched from this host thread polls each of
+ * its waits at most `polls` times and, with skip_loads != 0, its producer issues no loads, so the wait of its MMA
+ * warp runs out: the kernel records the error word above, frees its tensor memory and returns; nothing faults or
+ * hangs. Used by the tests to exercise the timeout path; no counterpart in the reference. */
 PGB_API int pgb_gemm_wait_drill(unsigned int polls, int skip_loads);
 
 /* ---- Collectives of the batch-sharded path over peer memory (one process per GPU of one box) -------------------

@@ -61,6 +61,8 @@ struct AttnParams {
   void *out;
   int64_t o_row, o_head, o_batch;  // output strides in elements
   int *err;
+  uint32_t polls;   // polls per wait before a role gives up
+  int skip_loads;   // failure-detection drill: the producer loads nothing
 };
 
 // f16 / bf16 instruction descriptor, M = 128, fp32 accumulate; bit 16 = B operand is MN-major
@@ -151,9 +153,9 @@ __device__ __forceinline__ void tmem_st16(uint32_t taddr, const uint32_t (&v)[16
 }
 // Bounded wait. try_wait lets the hardware park the thread for a short while instead of spinning through the issue
 // slots that the softmax warps need. (A suspend-time hint of 2 us was measured and is slower.)
-__device__ __forceinline__ bool attn_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag) {
+__device__ __forceinline__ bool attn_wait(uint64_t *bar, uint32_t parity, volatile int *abort_flag, uint32_t polls) {
   const uint32_t addr = smem_u32(bar);
-  for (uint32_t i = 0; i < kAttnPolls; ++i) {
+  for (uint32_t i = 0; i < polls; ++i) {
     uint32_t ok;
     asm volatile(
         "{\n\t.reg .pred p;\n\t"
@@ -251,7 +253,7 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
   if (*dead) {
     // an earlier kernel's wait ran out and nobody has cleared the word: nothing runs (one decision for the whole CTA)
   } else if (warp == 4) {
-    if (lane == 0) {
+    if (lane == 0 && !p.skip_loads) {
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_q) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_k) : "memory");
       asm volatile("prefetch.tensormap [%0];" ::"l"(&map_v) : "memory");
@@ -261,17 +263,17 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
         const AttnTile t = attn_tile(p, id);
         if (t.n_kb == 0) continue;
         // the single Q buffer is free once the previous item's last S = Q K^T has been computed
-        if (!attn_wait(q_empty, (it & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 0); break; }
+        if (!attn_wait(q_empty, (it & 1) ^ 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 0); break; }
         mbar_expect_tx(q_full, kQBytes);
         tma_load_4d(q_s, &map_q, 0, t.q0, t.h, t.b, q_full);
         ++it;
         for (int j = 0; j < t.n_kb; ++j, ++g) {
           const uint32_t ks = g % kKStages;
-          if (!attn_wait(&k_empty[ks], ((g / kKStages) & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 1); ok = false; break; }
+          if (!attn_wait(&k_empty[ks], ((g / kKStages) & 1) ^ 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 1); ok = false; break; }
           mbar_expect_tx(&k_full[ks], kKVBytes);
           tma_load_4d(k_s + ks * kKVBytes, &map_k, 0, j * kKB, t.h, t.b, &k_full[ks]);
           const uint32_t vs = g % kVStages;
-          if (!attn_wait(&v_empty[vs], ((g / kVStages) & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 2); ok = false; break; }
+          if (!attn_wait(&v_empty[vs], ((g / kVStages) & 1) ^ 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 2); ok = false; break; }
           mbar_expect_tx(&v_full[vs], kKVBytes);
           tma_load_4d(v_s + vs * kKVBytes, &map_v, 0, j * kKB, t.h, t.b, &v_full[vs]);
         }
@@ -295,10 +297,10 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
       s_seek();
       // S(g) = Q K(g)^T; the single S buffer is free once the softmax warps hold S(g-1) in registers
       auto issue_s = [&]() -> bool {
-        if (s_j == 0 && !attn_wait(q_full, s_it & 1, abort_flag)) { attn_fail(p, abort_flag, 3); return false; }
+        if (s_j == 0 && !attn_wait(q_full, s_it & 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 3); return false; }
         const uint32_t ks = s_g % kKStages;
-        if (!attn_wait(&k_full[ks], (s_g / kKStages) & 1, abort_flag)) { attn_fail(p, abort_flag, 4); return false; }
-        if (!attn_wait(s_free, (s_g & 1) ^ 1, abort_flag)) { attn_fail(p, abort_flag, 5); return false; }
+        if (!attn_wait(&k_full[ks], (s_g / kKStages) & 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 4); return false; }
+        if (!attn_wait(s_free, (s_g & 1) ^ 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 5); return false; }
         tc_fence_after();
         const uint64_t dk = make_kmajor_sw128_desc(smem_u32(k_s + ks * kKVBytes));
 #pragma unroll
@@ -329,9 +331,9 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
           }
           // P(g) arrives only after the softmax warps have read the previous item's O and row sums, so the first
           // PV of an item may overwrite them
-          if (!attn_wait(p_full, g & 1, abort_flag)) { attn_fail(p, abort_flag, 6); ok = false; break; }
+          if (!attn_wait(p_full, g & 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 6); ok = false; break; }
           const uint32_t vs = g % kVStages;
-          if (!attn_wait(&v_full[vs], (g / kVStages) & 1, abort_flag)) { attn_fail(p, abort_flag, 7); ok = false; break; }
+          if (!attn_wait(&v_full[vs], (g / kVStages) & 1, abort_flag, p.polls)) { attn_fail(p, abort_flag, 7); ok = false; break; }
           tc_fence_after();
 #pragma unroll
           for (int kk = 0; kk < 8; ++kk)  // 16 keys per MMA: 8 columns of P (two keys each), 16 rows of V
@@ -397,7 +399,7 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
       for (int j = 0; j < t.n_kb; ++j, ++g) {
         if (ok) {
           // every lane polls (one broadcast read of the barrier per poll): no shuffle, no divergent branch
-          ok = __all_sync(0xffffffffu, attn_wait(s_full, g & 1, abort_flag));
+          ok = __all_sync(0xffffffffu, attn_wait(s_full, g & 1, abort_flag, p.polls));
           if (!ok && lane == 0) attn_fail(p, abort_flag, 8);
         }
         if (!ok) continue;
@@ -445,7 +447,7 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
         m = m_new;
         if (g > 0) {
           // PV(g-1) must have consumed P and updated O before either is touched (it was released a whole block ago)
-          ok = __all_sync(0xffffffffu, attn_wait(pv_done, (g - 1) & 1, abort_flag));
+          ok = __all_sync(0xffffffffu, attn_wait(pv_done, (g - 1) & 1, abort_flag, p.polls));
           if (!ok) { if (lane == 0) attn_fail(p, abort_flag, 9); continue; }
           tc_fence_after();
           if (j == 0 && prev_id >= 0) {
@@ -493,7 +495,7 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
       l_prev = l;
     }
     if (prev_id >= 0 && ok) {  // the last item's epilogue
-      ok = __all_sync(0xffffffffu, attn_wait(pv_done, (g - 1) & 1, abort_flag));
+      ok = __all_sync(0xffffffffu, attn_wait(pv_done, (g - 1) & 1, abort_flag, p.polls));
       if (!ok && lane == 0) attn_fail(p, abort_flag, 10);
       if (ok) {
         tc_fence_after();
@@ -566,6 +568,9 @@ int run_attention(const void *q, const void *k, const void *v, void *out, int is
   p.o_head = o_str[1];
   p.o_row = o_str[2];
   p.err = gemm_error_word();
+  uint32_t drill_polls = 0;
+  take_next_wait_test(&drill_polls, &p.skip_loads);
+  p.polls = drill_polls ? drill_polls : kAttnPolls;
   if (!p.err) { set_error("attention: cannot resolve the device error word"); return PGB_ERR_CUDA; }
   const unsigned grid = (unsigned)std::min<int64_t>(B * H * n_qblk, (int64_t)kAttnCtasPerSm * sm_count());
   if (is_half) attention_fwd_kernel<true><<<grid, kAttnThreads, kAttnSmem, stream>>>(mq, mk, mv, p);

@@ -55,6 +55,8 @@ int run_quantize_i8(const float *x, int64_t n, const float *absmax_dev, float sc
 int read_gemm_error(int *out, bool reset);
 int set_gemm_pair_mode(int mode);  // < 0: query; returns the previous mode
 void set_next_gemm_wait_test(uint32_t spin_limit, int skip_loads);
+// Reads and clears the drill of this host thread (0 polls = none): the next tensor-core GEMM or attention launch takes it.
+void take_next_wait_test(uint32_t *spin_limit, int *skip_loads);
 // The device error word of the current device (set by a kernel whose bounded wait ran out), or null.
 int *gemm_error_word();
 // 4-D tensor map with a 128B-swizzled box (dims innermost first, strides in bytes for dims 1..3). False on failure.

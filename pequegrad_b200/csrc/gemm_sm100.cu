@@ -218,6 +218,12 @@ void set_next_gemm_wait_test(uint32_t spin_limit, int skip_loads) {
   t_next_spin_limit = spin_limit;
   t_next_skip_loads = skip_loads;
 }
+void take_next_wait_test(uint32_t *spin_limit, int *skip_loads) {
+  *spin_limit = t_next_spin_limit;
+  *skip_loads = t_next_skip_loads;
+  t_next_spin_limit = 0;
+  t_next_skip_loads = 0;
+}
 
 // a: [nb0, nb1, M, K], b: [nb0, nb1, N, K], both K contiguous; strides in elements.
 int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_bs1, const void *b, int64_t ldb, int64_t b_bs0, int64_t b_bs1,
@@ -244,10 +250,9 @@ int run_gemm_tc(int kind, const void *a, int64_t lda, int64_t a_bs0, int64_t a_b
   p.num_kb = (int)((K * es + kSlabBytes - 1) / kSlabBytes);
   // MMAs (32 bytes of K each) that the last slab needs: the zero fill beyond K is not worth multiplying
   p.last_mmas = (int)((K * es - (int64_t)(p.num_kb - 1) * kSlabBytes + 31) / 32);
-  p.spin_limit = t_next_spin_limit ? t_next_spin_limit : kSpinLimit;
-  p.skip_loads = t_next_skip_loads;
-  t_next_spin_limit = 0;
-  t_next_skip_loads = 0;
+  uint32_t drill_polls = 0;
+  take_next_wait_test(&drill_polls, &p.skip_loads);
+  p.spin_limit = drill_polls ? drill_polls : kSpinLimit;
   p.tiles_m = (int)tiles_m;
   p.tiles_n = (int)tiles_n;
   p.batch = (int)batch;

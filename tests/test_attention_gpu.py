@@ -84,6 +84,39 @@ def test_more_work_items_than_resident_ctas(B, H, T, Tk, causal, dtype):
     assert torch.equal(out.view(torch.int16), out2.view(torch.int16))
 
 
+def test_a_wait_that_runs_out_is_reported_and_the_device_stays_usable():
+    """Failure detection without a fault: the next attention launch's producer is told to load nothing and every wait
+    to give up after 1024 polls. Every CTA must record who gave up, drain its roles, free its tensor memory and return;
+    while the error word is set further launches do nothing; after the reset the same call is right again."""
+    import ctypes as C
+
+    from pequegrad_b200 import _lib as L
+    g = torch.Generator(device="cuda").manual_seed(17)
+    q, k, v = (torch.randn((2, 3, 384, 64), generator=g, device="cuda").half() for _ in range(3))
+    want = composite(q, k, v, True, 0.125)
+    check(K.attention(q, k, v, causal=True), want, "before the drill")
+    K.gemm_wait_drill(1024, skip_loads=True)
+    out = torch.full(q.shape, 7.0, device="cuda", dtype=torch.float16)
+    K.attention(q, k, v, causal=True, out=out)
+    torch.cuda.synchronize()  # returns: nothing hangs
+    code = C.c_int(0)
+    st = L.lib().pgb_device_error(C.byref(code), 0)
+    assert st == L.ERR_TIMEOUT and "wait ran out" in L.lib().pgb_last_error().decode()
+    assert 16 <= (code.value >> 16) <= 26 and (code.value & 0xffff) < 2 * 3 * 3  # an attention role of one of the 18 CTAs
+    assert (out == 7).all()  # nothing was computed, nothing was written
+    # the word is still set: the next launch returns at once and leaves its output alone
+    K.attention(q, k, v, causal=True, out=out)
+    torch.cuda.synchronize()
+    assert (out == 7).all()
+    assert K.device_error(reset=True) == code.value
+    assert K.device_error() == 0
+    # the drill applied to one launch only, and the device is as good as before
+    check(K.attention(q, k, v, causal=True), want, "after the drill")
+    x = torch.randn((256, 512), generator=g, device="cuda").half()
+    y = torch.randn((384, 512), generator=g, device="cuda").half()
+    assert torch.allclose(K.matmul(x, y.T).float(), x.float() @ y.float().T, rtol=2e-2, atol=2e-2)
+
+
 def test_attention_errors():
     q = torch.zeros((1, 1, 16, 32), device="cuda", dtype=torch.float16)
     with pytest.raises(RuntimeError, match="head dim of 64"):
