@@ -295,6 +295,7 @@ def make_workload(args):
     if args.workload == "sweep":
         wl = W.Sweep(args.only, args.bare)
         wl.lanes = max(1, args.lanes)
+        wl.peer_gather = not args.no_peer_gather
         return wl
     if args.workload == "mlp":
         return W.Mlp(args.rows or W.MLP_ROWS)
@@ -396,6 +397,7 @@ def main():
     ap.add_argument("--no-others", action="store_true", help="sweep only: skip the short runs of the other workloads")
     ap.add_argument("--only", default="", help="sweep: comma-separated tensor names (A,B,Bp) to restrict the sweep, for profiling")
     ap.add_argument("--lanes", type=int, default=2, help="sweep: streams the independent cases of a step alternate over (1 = one after another)")
+    ap.add_argument("--no-peer-gather", action="store_true", help="sweep on several GPUs: gather the small results with NCCL too, not with the peer-memory kernel")
     ap.add_argument("--bare", action="store_true", help="sweep diagnostic: no prologue / epilogue (not the benchmark workload)")
     ap.add_argument("--rows", type=int, default=0, help="mlp: rows in total (default 65536; smaller for profiling)")
     ap.add_argument("--batch", type=int, default=0, help="gpt2: sequences in total (default 32; smaller for profiling)")

@@ -232,14 +232,18 @@ class GatherBucket:
     """Several sharded outputs gathered by ONE collective. Kernels write their output slabs into views of
     one flat buffer (`local_view`); `gather()` all-gathers that buffer; `full(i)` is output i assembled
     from every process. An output whose slabs are concatenated along dim 0 is returned as a view of the
-    receive buffer (strided across processes, no copy); other dims take one permuting copy."""
+    receive buffer (strided across processes, no copy); other dims take one permuting copy. With
+    `peer_memory=True` the gather is one launch of the peer-memory kernel (`PeerGroup.allgather`, stream-ordered
+    on the caller's stream) instead of a library collective: a fraction of its latency, which is what counts for
+    a few megabytes at the end of a step; `peer_note` says which of the two is in use."""
 
     ALIGN = 256
 
-    def __init__(self, device, async_op: bool = False):
-        self.device, self.async_op = device, async_op
+    def __init__(self, device, async_op: bool = False, peer_memory: bool = False):
+        self.device, self.async_op, self.peer_memory = device, async_op, peer_memory
         self.specs, self.nbytes = [], 0
-        self.local = self.recv = self.work = None
+        self.local = self.recv = self.work = self.peers = None
+        self.peer_note = "NCCL"
 
     def add(self, local_shape: Sequence[int], dtype: torch.dtype, dim: int = 0) -> int:
         if self.local is not None:
@@ -256,7 +260,23 @@ class GatherBucket:
         if self.local is None:
             _, world = rank_world()
             self.local = torch.empty(max(self.nbytes, self.ALIGN), dtype=torch.uint8, device=self.device)
-            self.recv = self.local if world == 1 else torch.empty(world * self.local.numel(), dtype=torch.uint8, device=self.device)
+            if world > 1 and self.peer_memory:
+                # every rank comes here at the same point of its set-up: all of them map one another's buffers, or none
+                try:
+                    self.peers = PeerGroup(gather_bytes=self.local.numel())
+                    self.peer_note = "peer-memory kernel over NVLink (CUDA IPC mappings)"
+                except Exception as e:  # noqa: BLE001 - any failure of the mapping leaves the NCCL path
+                    self.peer_note = f"NCCL (peer mapping unavailable: {type(e).__name__}: {e})"
+                flags = [None] * world
+                dist.all_gather_object(flags, self.peers is not None)
+                if not all(flags):
+                    if self.peers is not None:
+                        self.peers.close()
+                    self.peers = None
+            if self.peers is not None:
+                self.recv = self.peers.recv[: world * self.local.numel()]
+            else:
+                self.recv = self.local if world == 1 else torch.empty(world * self.local.numel(), dtype=torch.uint8, device=self.device)
 
     def local_view(self, i: int) -> torch.Tensor:
         self._alloc()
@@ -271,7 +291,9 @@ class GatherBucket:
         """Enqueue the all-gather of everything written to the local views so far (stream-ordered)."""
         self._alloc()
         _, world = rank_world()
-        if world > 1:
+        if world > 1 and self.peers is not None:
+            self.peers.allgather(self.local)  # lands in self.recv, a view of the group's receive buffer
+        elif world > 1:
             self.work = dist.all_gather_into_tensor(self.recv, self.local, async_op=self.async_op)
 
     def wait(self):

@@ -201,7 +201,9 @@ class Sweep:
         torch.cuda.empty_cache()
         self.cases = [c for c in sweep_cases() if not only or c[0] in only]
         opcode = {"sum": L.SUM, "max": L.MAX, "mean": L.MEAN, "argmax": L.ARGMAX}
-        self.buckets = [D.GatherBucket(dev, async_op=True), D.GatherBucket(dev, async_op=True)]
+        # the first bucket (the large axis-0 results) is gathered by NCCL under the remaining kernels; the second (11 MB)
+        # comes after the last kernel, where latency is all that counts: one launch of the peer-memory kernel
+        self.buckets = [D.GatherBucket(dev, async_op=True), D.GatherBucket(dev, async_op=True, peer_memory=self.peer_gather)]
         plan = []
         for name, op, ax, nbytes in self.cases:
             base = S[("A" if name == "A" else "B") + ("1" if ax == 0 else "0")]
@@ -230,6 +232,7 @@ class Sweep:
         shard_mb = {k: round(v.numel() * 4 / 1e6) for k, v in S.items()}
         self.config = {"cases": len(self.cases), "bytes_per_step": self.bytes_per_step, "partition": "kept axis of every case split over the GPUs",
                        "streams": "the independent cases of a step alternate over %d streams that fork from and join the timed one" % self.lanes,
+                       "gathers": "none (one GPU)" if world == 1 else "axis-0 results: NCCL all-gather under the remaining kernels; the rest: " + self.buckets[1].peer_note,
                        "shard_MB_per_gpu": shard_mb, "gathered_bytes_per_step": self.gather_bytes if world > 1 else 0,
                        "e2e_note": "each rank uploads its row shards of A and B once per step; the second sharding (column slabs of A, dim 1 of B) "
                                    "is made on the devices by one all-to-all each" if world > 1 else "one GPU: A and B uploaded once per step",
@@ -239,6 +242,7 @@ class Sweep:
     graphs = None
 
     lanes = 2
+    peer_gather = True
 
     def _launch(self, lo, hi):
         """The cases lo..hi, which do not depend on one another, alternating over `lanes` streams that fork from and
