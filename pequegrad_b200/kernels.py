@@ -141,8 +141,8 @@ def fused_elementwise(inputs: Sequence[torch.Tensor], prog, shape=None, out_dtyp
     return outs
 
 
-def softmax_rows(x: torch.Tensor, causal: bool = False) -> torch.Tensor:
-    y = torch.empty_like(x, memory_format=torch.contiguous_format)
+def softmax_rows(x: torch.Tensor, causal: bool = False, out: torch.Tensor | None = None) -> torch.Tensor:
+    y = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
     xd, yd = desc(x), desc(y)
     with torch.cuda.device(x.device):
         st = L.lib().pgb_softmax_rows(C.byref(xd), C.byref(yd), 1 if causal else 0, _stream())
@@ -150,8 +150,9 @@ def softmax_rows(x: torch.Tensor, causal: bool = False) -> torch.Tensor:
     return y
 
 
-def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor | None, beta: torch.Tensor | None, eps: float = 1e-5) -> torch.Tensor:
-    y = torch.empty_like(x, memory_format=torch.contiguous_format)
+def layernorm_rows(x: torch.Tensor, gamma: torch.Tensor | None, beta: torch.Tensor | None, eps: float = 1e-5,
+                   out: torch.Tensor | None = None) -> torch.Tensor:
+    y = torch.empty_like(x, memory_format=torch.contiguous_format) if out is None else out
     xd, yd = desc(x), desc(y)
     gd = desc(gamma) if gamma is not None else None
     bd = desc(beta) if beta is not None else None

@@ -65,12 +65,14 @@ def test_heads_inside_packed_buffers_and_cross_lengths():
 
 @pytest.mark.parametrize("B,H,T,Tk,causal,dtype", [(4, 12, 1024, 1024, True, torch.float16), (50, 12, 128, 128, True, torch.float16),
                                                    (3, 40, 300, 384, False, torch.bfloat16), (7, 12, 200, 200, True, torch.float16),
-                                                   (40, 16, 1, 130, False, torch.float16)])
+                                                   (40, 16, 1, 130, False, torch.float16), (12, 12, 1024, 1024, True, torch.float16),
+                                                   (100, 12, 100, 100, True, torch.bfloat16)])
 def test_more_work_items_than_resident_ctas(B, H, T, Tk, causal, dtype):
     # The kernel is persistent (two CTAs per SM): with more (batch, head, query block) items than CTAs every CTA walks
     # several items back to back, with its loads and MMAs already in the next item while the softmax of the current one
     # finishes and the previous item's result written out inside the next item's first block. Items of one key block,
-    # of several, ragged last blocks and a different mix per CTA.
+    # of several, ragged last blocks and a different mix per CTA; up to three items per CTA are handed out in rounds of
+    # alternating direction, more in the plain order (the last two cases).
     g = torch.Generator(device="cuda").manual_seed(11)
     q = torch.randn((B, H, T, 64), generator=g, device="cuda").to(dtype)
     k, v = (torch.randn((B, H, Tk, 64), generator=g, device="cuda").to(dtype) for _ in range(2))

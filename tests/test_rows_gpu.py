@@ -89,3 +89,16 @@ def test_softmax_configured_shape_slices_and_errors():
         K.softmax_rows(s.permute(0, 1, 3, 2))  # non-contiguous rows are refused, not silently copied
     with pytest.raises(RuntimeError):
         K.softmax_rows(torch.zeros(4, 4, dtype=torch.int32, device="cuda"))
+
+
+def test_rows_workload_on_two_streams_gives_the_kernels_bits():
+    # the benchmark runs the LayerNorm on a stream that forks from and joins the timed one, under the softmax
+    from pequegrad_b200 import workloads as W
+    wl = W.Rows()
+    wl.SM_SHAPE, wl.LN_SHAPE = (2, 12, 1024, 1024), (4096, 768)
+    wl.setup(torch.device("cuda:0"), 0, 1)
+    for _ in range(3):
+        wl.step()
+    torch.cuda.synchronize()
+    assert torch.equal(wl.sm_out, K.softmax_rows(wl.S, causal=True))
+    assert torch.equal(wl.ln_out, K.layernorm_rows(wl.X, wl.gamma, wl.beta, 1e-5))
