@@ -54,29 +54,35 @@ __global__ void __launch_bounds__(kShortThreads, B > 8 ? 3 : 4) reduce_short_ker
   if (LITE) chain_decode<float>(p.pro, cr);
   Acc<float, ROP> acc;
   acc.init();
-#pragma unroll 1
-  for (int k0 = 0; k0 < K; k0 += B) {
-    float w[NIN][B], run[B];
+  // whole chunks of B steps without any clamping, then the remainder four steps at a time (K = 20: 16 + 4 exactly)
+  auto chunk = [&](auto cb_c, int k0) {
+    constexpr int CB = decltype(cb_c)::value;
+    float w[NIN][CB], run[CB];
 #pragma unroll
     for (int k = 0; k < NIN; ++k) {
       if (p.vec4[k]) {
 #pragma unroll
-        for (int v = 0; v < B; v += 4) {
-          // K % 4 == 0 here; a vector wholly past the row is clamped onto its last vector and ignored below
-          const float4 t = __ldg(reinterpret_cast<const float4 *>(base[k] + min(k0 + v, K - 4)));
+        for (int v = 0; v < CB; v += 4) {
+          // K % 4 == 0 here, so a vector never straddles the end of the row
+          const float4 t = __ldg(reinterpret_cast<const float4 *>(base[k] + (k0 + v)));
           w[k][v] = t.x; w[k][v + 1] = t.y; w[k][v + 2] = t.z; w[k][v + 3] = t.w;
         }
       } else {
 #pragma unroll
-        for (int e = 0; e < B; ++e) w[k][e] = __ldg(base[k] + (int64_t)min(k0 + e, K - 1) * p.kstr[k]);
+        for (int e = 0; e < CB; ++e) w[k][e] = __ldg(base[k] + (int64_t)min(k0 + e, K - 1) * p.kstr[k]);
       }
     }
-    if (LITE) chain_eval_fast<float, NIN, B>(cr, w, run);
-    else chain_eval<float, NIN, B>(p.pro, w, run);
+    if (LITE) chain_eval_fast<float, NIN, CB>(cr, w, run);
+    else chain_eval<float, NIN, CB>(p.pro, w, run);
 #pragma unroll
-    for (int e = 0; e < B; ++e)
+    for (int e = 0; e < CB; ++e)
       if (k0 + e < K) acc.add_stream(run[e], k0 + e);
-  }
+  };
+  int k0 = 0;
+#pragma unroll 1
+  for (; k0 + B <= K; k0 += B) chunk(std::integral_constant<int, B>{}, k0);
+#pragma unroll 1
+  for (; k0 < K; k0 += 4) chunk(std::integral_constant<int, 4>{}, k0);
   finish_output<float>(p.epi, o, acc.v, acc.i);
 }
 
@@ -117,7 +123,12 @@ int launch_short(ReduceJob &j, const ChainProg<float> &chain) {
   if (!err.empty()) { set_error(err); return PGB_ERR_INVALID_ARG; }
   auto go = [&](auto rop_c) {
     constexpr int ROP = decltype(rop_c)::value;
-    if (chain.lite && K <= 32) reduce_short_kernel<NIN, ROP, true, 16><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    // a short axis that is a multiple of four goes in one pass, every load of the row in flight at once (K = 20: as
+    // many as the reference's fully unrolled generated kernel has)
+    if (chain.lite && K == 20) reduce_short_kernel<NIN, ROP, true, 20><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    else if (chain.lite && K == 24) reduce_short_kernel<NIN, ROP, true, 24><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    else if (chain.lite && K == 12) reduce_short_kernel<NIN, ROP, true, 12><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
+    else if (chain.lite && K <= 32) reduce_short_kernel<NIN, ROP, true, 16><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
     else if (chain.lite) reduce_short_kernel<NIN, ROP, true, 8><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
     else reduce_short_kernel<NIN, ROP, false, 8><<<(unsigned)grid, kShortThreads, 0, j.stream>>>(p);
   };

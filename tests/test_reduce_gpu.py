@@ -315,7 +315,8 @@ def test_ragged_row_split_across_ctas():
         check_ragged([z[:, :1000001]], op, (), 1e-5, f"ragged split {op}")
 
 
-@pytest.mark.parametrize("shape", [(7, 100, 20), (3, 5, 33, 6), (40, 9, 128), (2, 300, 7), (1000, 12, 3)])
+@pytest.mark.parametrize("shape", [(7, 100, 20), (3, 5, 33, 6), (40, 9, 128), (2, 300, 7), (1000, 12, 3), (5, 64, 12), (5, 64, 24),
+                                   (3, 52, 36), (4, 40, 22), (6, 16, 16)])
 def test_short_reduced_axis_with_operands_of_opposite_orientation(shape):
     """x read through a permute of its last two dims against a plain y (the README case's shape of problem): the
     operands disagree on which of the innermost kept axis and the short reduced axis is contiguous; every op, a
