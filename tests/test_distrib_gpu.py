@@ -84,6 +84,28 @@ def test_sweep_on_two_streams_and_as_graphs_gives_the_same_bits():
             assert torch.equal(t.view(torch.int32), base[name].view(torch.int32)), (key, name)
 
 
+def test_one_gpu_end_to_end_step_with_overlapped_copies_returns_the_steps_results():
+    # bench.py's e2e leg on one GPU: uploads on a copy stream, A's cases under B's upload, the axis-0 results copied back
+    # under the remaining kernels; the host buffers must hold exactly what a plain step leaves on the device
+    from pequegrad_b200 import workloads as W
+    torch.cuda.set_device(0)
+    wl = W.Sweep()
+    wl.setup(torch.device("cuda:0"), 0, 1)
+    wl.step()
+    torch.cuda.synchronize()
+    want = [b.recv.clone() for b in wl.buckets]
+    wl.e2e_setup()
+    for b in wl.buckets:
+        b.recv.zero_()
+    for _ in range(3):
+        wl.e2e_step()
+    torch.cuda.synchronize()
+    for have, w, b in zip(wl.host_out, want, wl.buckets):
+        assert torch.equal(b.recv, w)
+        assert torch.equal(have, w.cpu())
+    assert wl.h2d == 4 * (8192 * 8192 + 64 * 4096 * 1024) and wl.d2h == sum(w.numel() for w in want)
+
+
 def _free_port():
     s = socket.socket()
     s.bind(("127.0.0.1", 0))
