@@ -504,7 +504,9 @@ def main():
                            **wl.config),
             "clocks": clocks,
             "compute_only": {"value": round(ms_compute * 1e3 / wl.units_per_step if latency else wl.units_per_step / (ms_compute * 1e-3), 2 if latency else 1),
-                             "unit": wl.unit, "ms_per_step": round(ms_compute, 5), "what": "the same steps without the final gather"},
+                             "unit": wl.unit, "ms_per_step": round(ms_compute, 5),
+                             "what": "the same steps without the final gather" if world > 1 else
+                                     "one GPU: there is no gather; a second timing of the same steps, taken right after the first"},
             "e2e": {"value": round(e2e_value, 2), "unit": wl.unit, "h2d_bytes_per_step": int(h2d), "d2h_bytes_per_step": wl.d2h,
                     "ms_per_step": round(e2e_ms, 4),
                     "what": "pinned host inputs copied to every rank's shards, the step with its gather, the result read back by rank 0; "
