@@ -296,6 +296,7 @@ def make_workload(args):
         wl = W.Sweep(args.only, args.bare)
         wl.lanes = max(1, args.lanes)
         wl.peer_gather = not args.no_peer_gather
+        wl.skip = frozenset(filter(None, args.sweep_skip.split(",")))
         return wl
     if args.workload == "mlp":
         return W.Mlp(args.rows or W.MLP_ROWS)
@@ -398,6 +399,7 @@ def main():
     ap.add_argument("--only", default="", help="sweep: comma-separated tensor names (A,B,Bp) to restrict the sweep, for profiling")
     ap.add_argument("--lanes", type=int, default=2, help="sweep: streams the independent cases of a step alternate over (1 = one after another)")
     ap.add_argument("--no-peer-gather", action="store_true", help="sweep on several GPUs: gather the small results with NCCL too, not with the peer-memory kernel")
+    ap.add_argument("--sweep-skip", default="", help="sweep diagnostic on several GPUs: leave out parts of the step (b0, b1 = the gathers, copies) to see what they cost; not the benchmark workload")
     ap.add_argument("--bare", action="store_true", help="sweep diagnostic: no prologue / epilogue (not the benchmark workload)")
     ap.add_argument("--rows", type=int, default=0, help="mlp: rows in total (default 65536; smaller for profiling)")
     ap.add_argument("--batch", type=int, default=0, help="gpt2: sequences in total (default 32; smaller for profiling)")

@@ -44,7 +44,9 @@ struct EwGenParams {
   VmProg<T> prog;
 };
 
-template <typename T, typename InT, typename OutT, int NIN, int V, bool LITE>
+// IdxT: the type of the element index and its div / mod chain (uint32_t whenever the tensor has fewer than 2^31
+// elements: a 64-bit division costs several times the rest of the thread's work)
+template <typename T, typename InT, typename OutT, int NIN, int V, bool LITE, typename IdxT>
 __global__ void __launch_bounds__(256) ew_fast_kernel(const __grid_constant__ EwFastParams<T, NIN> p) {
   constexpr int B = LITE ? kBatch : V;
   constexpr int U = B / V;
@@ -54,15 +56,17 @@ __global__ void __launch_bounds__(256) ew_fast_kernel(const __grid_constant__ Ew
   for (int u = 0; u < U; ++u) {
     const int64_t vid = v0 + (int64_t)u * 256;
     if (vid < p.nvec) {
-      const int64_t e0 = vid * V;
-      int64_t c3 = e0, c2 = 0, c1 = 0, c0 = 0;
+      const IdxT e0 = (IdxT)(vid * V);
+      int64_t c3 = (int64_t)e0, c2 = 0, c1 = 0, c0 = 0;
       if (p.nd > 1) {
-        c3 = e0 % p.size[3];
-        int64_t r = e0 / p.size[3];
-        c2 = r % p.size[2];
-        r /= p.size[2];
-        c1 = r % p.size[1];
-        c0 = r / p.size[1];
+        const IdxT s3 = (IdxT)p.size[3], s2 = (IdxT)p.size[2], s1 = (IdxT)p.size[1];
+        IdxT r = e0 / s3;
+        c3 = (int64_t)(e0 - r * s3);
+        IdxT q = r / s2;
+        c2 = (int64_t)(r - q * s2);
+        r = q / s1;
+        c1 = (int64_t)(q - r * s1);
+        c0 = (int64_t)r;
       }
 #pragma unroll
       for (int k = 0; k < NIN; ++k) {
@@ -151,8 +155,11 @@ static int ew_fast_launch(const CanonEw &c, const pgb_tensor *in, const pgb_tens
   const int64_t per_cta = chain.lite ? 256 * (kBatch / V) : 256;
   const int64_t grid = (p.nvec + per_cta - 1) / per_cta;
   if (grid > 2147483647LL || grid == 0) return 0;
-  if (chain.lite) ew_fast_kernel<T, InT, OutT, NIN, V, true><<<(unsigned)grid, 256, 0, stream>>>(p);
-  else ew_fast_kernel<T, InT, OutT, NIN, V, false><<<(unsigned)grid, 256, 0, stream>>>(p);
+  const bool idx32 = c.numel < 2147483647LL;
+  if (chain.lite && idx32) ew_fast_kernel<T, InT, OutT, NIN, V, true, uint32_t><<<(unsigned)grid, 256, 0, stream>>>(p);
+  else if (chain.lite) ew_fast_kernel<T, InT, OutT, NIN, V, true, int64_t><<<(unsigned)grid, 256, 0, stream>>>(p);
+  else if (idx32) ew_fast_kernel<T, InT, OutT, NIN, V, false, uint32_t><<<(unsigned)grid, 256, 0, stream>>>(p);
+  else ew_fast_kernel<T, InT, OutT, NIN, V, false, int64_t><<<(unsigned)grid, 256, 0, stream>>>(p);
   count_launch();
   const int st = check_launch("ew_fast_kernel");
   return st == PGB_OK ? 1 : st;

@@ -245,15 +245,21 @@ class Sweep:
 
     lanes = 2
     peer_gather = True
+    skip = frozenset()
+    copy_graph = None
 
     def _launch(self, lo, hi):
         """The cases lo..hi, which do not depend on one another, alternating over `lanes` streams that fork from and
         join the current one: the ramp and the last partial wave of one kernel run under its neighbour's full waves
         (on a shard of an eighth of A a kernel is all ramp and tail)."""
+        self._on_lanes([pr for *_, pr in self.prepared[lo:hi]])
+
+    def _on_lanes(self, calls):
+        """Independent launches alternating over the lanes (see _launch)."""
         import torch
-        if self.lanes <= 1 or hi - lo < 2:
-            for *_, pr in self.prepared[lo:hi]:
-                pr()
+        if self.lanes <= 1 or len(calls) < 2:
+            for fn in calls:
+                fn()
             return
         main = torch.cuda.current_stream()
         if getattr(self, "_side", None) is None:
@@ -262,13 +268,13 @@ class Sweep:
         fork.record(main)
         for st in self._side:
             st.wait_event(fork)
-        for i, (*_, pr) in enumerate(self.prepared[lo:hi]):
+        for i, fn in enumerate(calls):
             lane = i % self.lanes
             if lane == 0:
-                pr()
+                fn()
             else:
                 with torch.cuda.stream(self._side[lane - 1]):
-                    pr()
+                    fn()
         for st in self._side:
             join = torch.cuda.Event()
             join.record(st)
@@ -279,7 +285,34 @@ class Sweep:
         n = len(self.prepared)
         g = [capture_graph(lambda: self._launch(0, self.n_first)), capture_graph(lambda: self._launch(self.n_first, n))]
         self.graphs = g if all(x is not None for x in g) else None
+        if self.graphs is not None and self.copies:
+            self._copy_pairs()
+            self.copy_graph = capture_graph(self._run_copies)  # None (not captured) leaves the separate launches
         return self.graphs is not None
+
+    def _copy_pairs(self):
+        """(source view, destination view) of the permuting copies, built once: the slabs that are not row blocks of
+        their result (the permuted view's axis-0 results, gathered along dim 1). int32 results travel as float32
+        bit patterns, so that every copy takes the vectorised elementwise kernel."""
+        import torch
+        if getattr(self, "_pairs", None) is None:
+            pairs = []
+
+            def keep(d, s_):
+                if d.dtype == torch.int32:
+                    d, s_ = d.view(torch.float32), s_.view(torch.float32)
+                pairs.append((s_, d))
+            for bk, idx, dst in self.copies:
+                bk.full(idx, copy_out=dst, copy_fn=keep)
+            self._pairs = pairs
+        return self._pairs
+
+    def _run_copies(self):
+        from . import kernels as K
+        if getattr(self, "copy_graph", None) is not None:
+            self.copy_graph.replay()
+            return
+        self._on_lanes([lambda s_=s_, d=d: K.fused_elementwise([s_], [("LOAD", 0)], outs=[d]) for s_, d in self._copy_pairs()])
 
     def _part(self, i):
         if self.graphs is not None:
@@ -298,14 +331,17 @@ class Sweep:
         if self.world == 1:
             return self.step_compute()
         b0, b1 = self.buckets
+        skip = self.skip  # diagnostic only (bench.py --sweep-skip): parts of the step left out to see what they cost
         self._part(0)
-        b0.gather()
+        if "b0" not in skip:
+            b0.gather()
         self._part(1)
-        b1.gather()
+        if "b1" not in skip:
+            b1.gather()
         b0.wait()
         b1.wait()
-        for bk, idx, dst in self.copies:  # slabs that are not row blocks of the result: one permuting copy each
-            bk.full(idx, copy_out=dst, copy_fn=lambda d, s: K.fused_elementwise([s], [("LOAD", 0)], outs=[d]))
+        if "copies" not in skip:
+            self._run_copies()
 
     def results(self):
         """Every case's whole result on this rank after step(): [(case name, tensor)]."""
