@@ -103,6 +103,16 @@ def _worker(rank, world, port, scenario, q):
             want1 = torch.cat([torch.arange(8, dtype=torch.int32).view(4, 2) + 10 * r for r in range(world)], 1)
             assert f1.shape == (4, 2 * world) and torch.equal(f1, want1)
             assert torch.equal(bk.full(i2), torch.arange(float(world)))
+            # asked for the peer-memory gather where no peer mapping can exist (CPU ranks): every rank falls back to the
+            # library collective together, and says so
+            bp = D.GatherBucket("cpu", peer_memory=True)
+            j0 = bp.add((2, 3), torch.float32, 0)
+            bp.local_view(j0).copy_(torch.arange(6.0).view(2, 3) + 7 * rank)
+            assert bp.peers is None and bp.peer_note.startswith("NCCL (peer mapping unavailable")
+            bp.gather()
+            bp.wait()
+            g0 = bp.full(j0)
+            assert all(torch.equal(g0[r], torch.arange(6.0).view(2, 3) + 7 * r) for r in range(world))
             q.put((rank, "ok"))
         elif scenario == "matmul":
             a, b = torch.randn((8, 6), generator=g), torch.randn((6, 10), generator=g)
