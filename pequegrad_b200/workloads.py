@@ -332,16 +332,32 @@ class Sweep:
             return self.step_compute()
         b0, b1 = self.buckets
         skip = self.skip  # diagnostic only (bench.py --sweep-skip): parts of the step left out to see what they cost
+        import torch
+        main = torch.cuda.current_stream()
         self._part(0)
         if "b0" not in skip:
             b0.gather()
+        copied = None
+        if self.copies and "copies" not in skip:
+            # the permuting copies (all of them slabs of the first bucket) wait for that bucket's gather on a stream of
+            # their own and run under the remaining kernels; the timed stream joins them at the end
+            if getattr(self, "_copy_stream", None) is None:
+                self._copy_stream = torch.cuda.Stream(device=self.dev)
+            start = torch.cuda.Event()
+            start.record(main)  # whoever read the copies' destinations in the step before is done
+            self._copy_stream.wait_event(start)
+            with torch.cuda.stream(self._copy_stream):
+                b0.wait()
+                self._run_copies()
+                copied = torch.cuda.Event()
+                copied.record(self._copy_stream)
         self._part(1)
         if "b1" not in skip:
             b1.gather()
         b0.wait()
         b1.wait()
-        if "copies" not in skip:
-            self._run_copies()
+        if copied is not None:
+            main.wait_event(copied)
 
     def results(self):
         """Every case's whole result on this rank after step(): [(case name, tensor)]."""
