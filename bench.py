@@ -251,7 +251,7 @@ def reference_cuda_leg(wl, reps=10):
     if not ref_cuda.available() or wl.world != 1:
         return None
     import torch
-    from pequegrad_b200.workloads import SHAPES, _event_us, _L2Flush
+    from pequegrad_b200.workloads import _event_us, _L2Flush
     dev = wl.dev
     if wl.name == "readme":
         x, y = wl.pairs[0]

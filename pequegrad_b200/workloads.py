@@ -327,7 +327,6 @@ class Sweep:
         self._part(1)
 
     def step(self):
-        from . import kernels as K
         if self.world == 1:
             return self.step_compute()
         b0, b1 = self.buckets
