@@ -252,10 +252,10 @@ __global__ void __launch_bounds__(kAttnThreads, kAttnCtasPerSm) attention_fwd_ke
   tc_fence_after();
   const uint32_t tmem_base = *tmem_slot;
 
-  // Every role walks the same list of items (blockIdx.x, + gridDim.x, ...) and, inside an item, its key blocks, with
-  // its own running block counter g: ring stages and barrier parities follow g, not the item, so the producer and
-  // the MMA thread run ahead into the next item while the softmax warps still finish the current one (the next
-  // Q arrives under the last block's softmax; its first S is ready when the epilogue ends).
+  // Every role walks the same list of items (attn_item) and, inside an item, its key blocks, with its own running
+  // block counter g: ring stages and barrier parities follow g, not the item, so the producer and the MMA thread run
+  // ahead into the next item while the softmax warps still finish the current one (the next Q arrives under the last
+  // block's softmax, and the next item's first S is ready when that softmax ends).
   if (*dead) {
     // an earlier kernel's wait ran out and nobody has cleared the word: nothing runs (one decision for the whole CTA)
   } else if (warp == 4) {
